@@ -1,0 +1,32 @@
+// Token embedding: hidden[t,:] = table[ids[t],:], widened to the float32
+// residual stream. An id outside the table writes zeros; the host rejects such
+// ids before launch (reference: crates/metal-backend/src/shaders/matrix.metal:94-103).
+#include "common.cuh"
+
+template <typename W>
+__global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  const W* row = table + static_cast<size_t>(ok ? id : 0) * hidden;
+  float* dst = out + static_cast<size_t>(t) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_f32(row[i]) : 0.f;
+}
+
+LRM_API int lrm_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                           int tokens, int hidden, int vocab, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (hidden <= 0 || vocab <= 0) return LRM_BAD_ARGUMENT;
+  const int threads = hidden >= 256 ? 256 : 64;
+  if (table_dtype == LRM_F32)
+    embed_rows_kernel<float><<<tokens, threads, 0, stream>>>(
+        static_cast<const float*>(table), ids, out, hidden, vocab);
+  else if (table_dtype == LRM_BF16)
+    embed_rows_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab);
+  else
+    return LRM_BAD_ARGUMENT;
+  LRM_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,124 @@
+// Position rotation of q and k, and the write of k and v into the paged cache,
+// in one pass over a step's fused q|k|v projection.
+//
+// Rotation (reference: crates/metal-backend/src/shaders/attention.metal:3-25,
+// split-half branch): for pair i < R/2 of a head,
+//   angle = float(position) * inv_freq[i]          (one float32 product)
+//   y[i]       = x[i] cos - x[i + R/2] sin
+//   y[i + R/2] = x[i] sin + x[i + R/2] cos
+// dims >= R pass through; v is never rotated. inv_freq already holds the
+// scaling (theta^(-2i/R) * scale / llama3 factor) and is built on the host.
+// With inv_freq == nullptr nothing is rotated (another position scheme ran
+// before, or none is used).
+//
+// Cache layout: pages [page][kv_head][page_size][d]; a sequence's position p
+// lives in page table[slot][p / page_size] at row p % page_size. A table entry
+// < 0 means that page is not kept (outside a windowed group's window): skipped.
+#include "common.cuh"
+
+template <typename A>
+__global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_out,
+                                  A* __restrict__ k_out, A* __restrict__ v_out,
+                                  A* __restrict__ k_pages, A* __restrict__ v_pages,
+                                  const int* __restrict__ page_table, int table_stride,
+                                  const int* __restrict__ positions,
+                                  const int* __restrict__ seq_of_token,
+                                  const int* __restrict__ slots,
+                                  const float* __restrict__ inv_freq, int rotary, int q_heads,
+                                  int kv_heads, int d, int page_size) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rotary / 2, dh = d / 2;
+  const size_t row = static_cast<size_t>(q_heads + 2 * kv_heads) * d;
+  const A* src = qkv + static_cast<size_t>(t) * row;
+  long long page = -1;
+  if (k_pages != nullptr) {
+    const int slot = slots[seq_of_token[t]];
+    page = page_table[static_cast<size_t>(slot) * table_stride + pos / page_size];
+  }
+  const int in_page = pos % page_size;
+  const float fpos = static_cast<float>(pos);
+  // rotated heads: q heads then k heads; one work item = one (head, i < d/2)
+  const int rot_items = (q_heads + kv_heads) * dh;
+  for (int item = threadIdx.x; item < rot_items; item += blockDim.x) {
+    const int head = item / dh, i = item % dh;
+    int a, b;  // the two elements this item produces
+    float ya, yb;
+    const A* x = src + static_cast<size_t>(head) * d;
+    if (i < half) {
+      a = i;
+      b = i + half;
+      const float xa = to_f32(x[a]), xb = to_f32(x[b]);
+      if (inv_freq != nullptr) {
+        const float angle = __fmul_rn(fpos, inv_freq[i]);
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        ya = fmaf(xa, cs, -__fmul_rn(xb, sn));
+        yb = fmaf(xa, sn, __fmul_rn(xb, cs));
+      } else {
+        ya = xa;
+        yb = xb;
+      }
+    } else {
+      a = rotary + 2 * (i - half);
+      b = a + 1;
+      ya = to_f32(x[a]);
+      yb = to_f32(x[b]);
+    }
+    const A oa = from_f32<A>(ya), ob = from_f32<A>(yb);
+    if (head < q_heads) {
+      A* dst = q_out + (static_cast<size_t>(t) * q_heads + head) * d;
+      dst[a] = oa;
+      dst[b] = ob;
+    } else {
+      const int kh = head - q_heads;
+      if (k_out != nullptr) {
+        A* dst = k_out + (static_cast<size_t>(t) * kv_heads + kh) * d;
+        dst[a] = oa;
+        dst[b] = ob;
+      }
+      if (page >= 0) {
+        A* dst = k_pages + ((static_cast<size_t>(page) * kv_heads + kh) * page_size + in_page) * d;
+        dst[a] = oa;
+        dst[b] = ob;
+      }
+    }
+  }
+  // v heads: copy
+  const A* vsrc = src + static_cast<size_t>(q_heads + kv_heads) * d;
+  for (int item = threadIdx.x; item < kv_heads * d; item += blockDim.x) {
+    const int kh = item / d, j = item % d;
+    const A val = vsrc[item];
+    if (v_out != nullptr) v_out[(static_cast<size_t>(t) * kv_heads + kh) * d + j] = val;
+    if (page >= 0)
+      v_pages[((static_cast<size_t>(page) * kv_heads + kh) * page_size + in_page) * d + j] = val;
+  }
+}
+
+LRM_API int lrm_rope_store(const void* qkv, int dtype, void* q_out, void* k_out, void* v_out,
+                           void* k_pages, void* v_pages, const int* page_table, int table_stride,
+                           const int* positions, const int* seq_of_token, const int* slots,
+                           const float* inv_freq, int rotary, int tokens, int q_heads,
+                           int kv_heads, int d, int page_size, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (d <= 0 || d % 2 != 0 || rotary < 0 || rotary > d || rotary % 2 != 0 || q_heads <= 0 ||
+      kv_heads < 0 || page_size <= 0)
+    return LRM_BAD_ARGUMENT;
+  if ((k_pages == nullptr) != (v_pages == nullptr)) return LRM_BAD_ARGUMENT;
+  if (k_pages != nullptr && (page_table == nullptr || slots == nullptr || seq_of_token == nullptr))
+    return LRM_BAD_ARGUMENT;
+  const int work = (q_heads + kv_heads) * d / 2;
+  const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+#define LRM_ROPE(A)                                                                              \
+  rope_store_kernel<A><<<tokens, threads, 0, stream>>>(                                          \
+      static_cast<const A*>(qkv), static_cast<A*>(q_out), static_cast<A*>(k_out),               \
+      static_cast<A*>(v_out), static_cast<A*>(k_pages), static_cast<A*>(v_pages), page_table,    \
+      table_stride, positions, seq_of_token, slots, inv_freq, rotary, q_heads, kv_heads, d,      \
+      page_size)
+  if (dtype == LRM_F32) LRM_ROPE(float);
+  else if (dtype == LRM_BF16) LRM_ROPE(__nv_bfloat16);
+  else return LRM_BAD_ARGUMENT;
+#undef LRM_ROPE
+  LRM_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,96 @@
+// Token choice on the device, one block per row of float32 logits.
+//
+// Greedy: the largest logit, lowest id on ties; a row with any non-finite
+// logit yields -1 (reference: crates/metal-backend/src/shaders/sampling.metal:39-80,
+// whose sentinel is 0xffffffff).
+//
+// Temperature: Gumbel-max. id = argmax_i( logit_i / T + g_i ), g_i =
+// -log(-log u_i), u_i from a counter-based hash of (seed, key, i). `key` is
+// given per row by the caller (it encodes request and step), so a row's choice
+// does not depend on what else is in the batch, and no ordered prefix sum over
+// the vocabulary is needed. The draw is distributed as softmax(logits / T).
+#include "common.cuh"
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+
+// uniform in (0,1) with 24 random bits, exactly representable in float32
+__device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t key, uint32_t i) {
+  const uint64_t z = mix64(mix64(seed + 0x9e3779b97f4a7c15ull * (key + 1)) + i);
+  return (static_cast<float>(static_cast<uint32_t>(z >> 40)) + 0.5f) * (1.0f / 16777216.0f);
+}
+
+struct Best {
+  float value;
+  int id;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {
+  if (b.id >= 0 && (a.id < 0 || b.value > a.value || (b.value == a.value && b.id < a.id))) return b;
+  return a;
+}
+
+template <bool GUMBEL>
+__global__ void pick_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab,
+                                 float inv_temperature, uint64_t seed,
+                                 const long long* __restrict__ keys) {
+  __shared__ float s_value[32];
+  __shared__ int s_id[32];
+  __shared__ int s_bad;
+  const int row = blockIdx.x;
+  const float* x = logits + static_cast<size_t>(row) * vocab;
+  const uint64_t key = GUMBEL ? static_cast<uint64_t>(keys[row]) : 0ull;
+  if (threadIdx.x == 0) s_bad = 0;
+  __syncthreads();
+  Best best{-INFINITY, -1};
+  bool bad = false;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    float v = x[i];
+    bad |= !isfinite(v);
+    if (GUMBEL) {
+      const float u = hash_uniform(seed, key, static_cast<uint32_t>(i));
+      v = fmaf(v, inv_temperature, -logf(-logf(u)));
+    }
+    best = better(best, Best{v, i});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.id, o)};
+    best = better(best, other);
+  }
+  if (bad) atomicOr(&s_bad, 1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) {
+    s_value[warp] = best.value;
+    s_id[warp] = best.id;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Best total{-INFINITY, -1};
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) total = better(total, Best{s_value[w], s_id[w]});
+    out[row] = s_bad ? -1 : total.id;
+  }
+}
+
+LRM_API int lrm_argmax_rows(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0) return LRM_BAD_ARGUMENT;
+  const int threads = vocab >= 4096 ? 1024 : 128;
+  pick_rows_kernel<false><<<rows, threads, 0, stream>>>(logits, out, vocab, 1.f, 0ull, nullptr);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+LRM_API int lrm_sample_gumbel_rows(const float* logits, int* out, int rows, int vocab,
+                                   float temperature, unsigned long long seed,
+                                   const long long* keys, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || !(temperature > 0.f) || keys == nullptr) return LRM_BAD_ARGUMENT;
+  const int threads = vocab >= 4096 ? 1024 : 128;
+  pick_rows_kernel<true><<<rows, threads, 0, stream>>>(logits, out, vocab, 1.0f / temperature, seed,
+                                                       keys);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}

@@ -1,0 +1,83 @@
+"""What one step carries: its entries as given, and the packed device-side description."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..runtime import Runtime
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its slot, its next tokens, and the places among
+    these tokens (0-based) whose logits are wanted."""
+
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class StepContext:
+    """Device-side description of a step, read by every part.
+
+    T tokens of B sequences are packed one sequence after another.
+    """
+
+    runtime: Runtime
+    phase: str  # "prefill": every sequence starts at position 0; "decode": one token each
+    num_tokens: int
+    num_seqs: int
+    max_seq_len: int  # most tokens one sequence brings this step
+    max_kv_len: int  # longest sequence after this step
+    token_ids: torch.Tensor  # int32 [T]
+    positions: torch.Tensor  # int32 [T]
+    seq_of_token: torch.Tensor  # int32 [T]
+    cu_seqlens: torch.Tensor  # int32 [B+1]
+    slots: torch.Tensor  # int32 [B]
+    kv_lens: torch.Tensor  # int32 [B], lengths after this step
+    wanted_rows: torch.Tensor  # int32 [n], packed row numbers whose logits are wanted
+    entry: Any = None  # the schedule entry being run
+    fresh_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+
+
+def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runtime: Runtime,
+              phase: str) -> StepContext:
+    """Build the packed int32 arrays on the host and copy them to the device in one transfer."""
+    counts = [len(e.tokens) for e in entries]
+    T, B = sum(counts), len(entries)
+    n_want = sum(len(e.want) for e in entries)
+    host = np.empty(3 * T + (B + 1) + 2 * B + n_want, dtype=np.int32)
+    token_ids, positions, seq_of = host[:T], host[T:2 * T], host[2 * T:3 * T]
+    o = 3 * T
+    cu, slots, kv_lens, wanted = host[o:o + B + 1], host[o + B + 1:o + 2 * B + 1], \
+        host[o + 2 * B + 1:o + 3 * B + 1], host[o + 3 * B + 1:]
+    at, w = 0, 0
+    cu[0] = 0
+    for b, (e, before) in enumerate(zip(entries, lengths_before)):
+        n = counts[b]
+        token_ids[at:at + n] = np.asarray(e.tokens, dtype=np.int64)
+        positions[at:at + n] = np.arange(before, before + n, dtype=np.int32)
+        seq_of[at:at + n] = b
+        slots[b] = e.slot
+        kv_lens[b] = before + n
+        for p in e.want:
+            wanted[w] = at + p
+            w += 1
+        at += n
+        cu[b + 1] = at
+    device = runtime.device
+    if device.type == "cuda":
+        dev = torch.from_numpy(host).pin_memory().to(device, non_blocking=True)
+    else:
+        dev = torch.from_numpy(host).to(device)
+    o = 3 * T
+    return StepContext(
+        runtime=runtime, phase=phase, num_tokens=T, num_seqs=B, max_seq_len=max(counts),
+        max_kv_len=int(kv_lens.max()),
+        token_ids=dev[:T], positions=dev[T:2 * T], seq_of_token=dev[2 * T:3 * T],
+        cu_seqlens=dev[o:o + B + 1], slots=dev[o + B + 1:o + 2 * B + 1],
+        kv_lens=dev[o + 2 * B + 1:o + 3 * B + 1], wanted_rows=dev[o + 3 * B + 1:])

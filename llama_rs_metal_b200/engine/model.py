@@ -1,0 +1,114 @@
+"""A decoder put together from a plan: embedding, scheduled blocks, final norm, head."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..errors import InvalidError
+from ..kernels import ops
+from ..parts.base import Block, ModelPlan, PartSpec
+from ..parts.linear import LinearWeight
+from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part
+from ..runtime import Runtime
+from ..weights.loader import TensorSpec
+
+
+def _full_names(spec: PartSpec, part) -> Dict[str, str]:
+    """own tensor name -> checkpoint name, for one part."""
+    return {own: spec.names.get(own, spec.prefix + own) for own in part.tensors()}
+
+
+class DecoderModel:
+    """Owns the parts of one model and runs them over a step's packed tokens.
+
+    It knows nothing of Llama: which parts there are, their sizes, their tensor
+    names and the order of layers all come from the plan.
+    """
+
+    def __init__(self, plan: ModelPlan, runtime: Runtime):
+        self.plan, self.runtime = plan, runtime
+        self.blocks: List[Block] = []
+        self._names: List[Dict[str, Dict[str, str]]] = []
+        for layer in plan.layers:
+            if layer.block not in BLOCKS:
+                raise InvalidError(f"block kind {layer.block!r} is not registered")
+            parts = {
+                "mixer": build_part(MIXERS, layer.mixer, "mixer"),
+                "feed_forward": build_part(FEED_FORWARDS, layer.feed_forward, "feed-forward"),
+                "mixer_norm": build_part(NORMS, layer.mixer_norm, "norm"),
+                "feed_forward_norm": build_part(NORMS, layer.feed_forward_norm, "norm"),
+            }
+            self.blocks.append(BLOCKS[layer.block](**parts))
+            self._names.append({role: _full_names(getattr(layer, role), part)
+                                for role, part in parts.items()})
+        self.final_norm = build_part(NORMS, plan.final_norm, "norm")
+        self._final_names = _full_names(plan.final_norm, self.final_norm)
+        self.embedding: Optional[torch.Tensor] = None
+        self.head: Optional[LinearWeight] = None
+        self._check_schedule()
+
+    # -- schedule and cache --------------------------------------------------------
+    def _check_schedule(self) -> None:
+        writers = {}
+        for position, entry in enumerate(self.plan.schedule):
+            if not 0 <= entry.layer < len(self.blocks):
+                raise InvalidError(f"schedule names layer {entry.layer}, the model has {len(self.blocks)}")
+            if entry.writes_cache:
+                if entry.cache in writers:
+                    raise InvalidError(f"cache entry {entry.cache} is written by two schedule entries")
+                writers[entry.cache] = position
+            elif entry.cache not in writers:
+                raise InvalidError(f"schedule entry {position} reads cache entry {entry.cache} before it is written")
+        if sorted(writers) != list(range(len(writers))):
+            raise InvalidError("cache entries must be numbered 0..n-1")
+
+    def cache_requests(self) -> list:
+        """What each cache entry's writing layer asks of the cache (index = cache entry)."""
+        out = {}
+        for entry in self.plan.schedule:
+            if entry.writes_cache:
+                out[entry.cache] = self.blocks[entry.layer].mixer.cache_request()
+        return [out[i] for i in range(len(out))]
+
+    # -- weights ---------------------------------------------------------------------
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        plan = self.plan
+        specs = {plan.embedding_name: TensorSpec((plan.vocab_size, plan.hidden_size))}
+        if plan.head_name is not None:
+            specs[plan.head_name] = TensorSpec((plan.vocab_size, plan.hidden_size))
+        for block, names in zip(self.blocks, self._names):
+            for role, mapping in names.items():
+                part_specs = getattr(block, role).tensors()
+                for own, full in mapping.items():
+                    specs[full] = part_specs[own]
+        for own, full in self._final_names.items():
+            specs[full] = self.final_norm.tensors()[own]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Hand every part its tensors (already on the device, in their kept precision)."""
+        rt = self.runtime
+        self.embedding = tensors[self.plan.embedding_name].contiguous()
+        head = self.embedding if self.plan.head_name is None else tensors[self.plan.head_name]
+        self.head = LinearWeight(head)
+        for block, names in zip(self.blocks, self._names):
+            for role, mapping in names.items():
+                getattr(block, role).bind({own: tensors[full] for own, full in mapping.items()}, rt)
+        self.final_norm.bind({own: tensors[full] for own, full in self._final_names.items()}, rt)
+
+    # -- forward ---------------------------------------------------------------------
+    def forward(self, ctx, cache) -> torch.Tensor:
+        """float32 logits [len(ctx.wanted_rows), vocab] for one step."""
+        hidden = ops.embed_rows(self.embedding, ctx.token_ids)
+        for entry in self.plan.schedule:
+            ctx.entry = entry
+            view = cache.view(entry.cache) if cache is not None else None
+            hidden = self.blocks[entry.layer].forward(hidden, ctx, view)
+        ctx.entry = None
+        if ctx.wanted_rows.numel() == 0:
+            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=hidden.device)
+        # the head runs only on the rows whose logits are wanted
+        # (crates/model-runtime/src/execute.rs:238-247 does it for the last row)
+        x = self.final_norm.forward(hidden, ctx, rows=ctx.wanted_rows)
+        return self.head(x, out_dtype=torch.float32)

@@ -1,0 +1,299 @@
+"""Python wrappers of the CUDA entry points.
+
+Every wrapper checks devices, dtypes, contiguity and shapes on the host and
+then launches on torch's current stream; memory comes from torch's allocator.
+Nothing here computes on the CPU or calls a library model/attention routine.
+A kernel that cannot take a size raises UnsupportedError with the reason.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from ..errors import InvalidError, KernelUnavailableError, UnsupportedError
+from . import library
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise UnsupportedError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _lib():
+    return library.load()
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelUnavailableError(f"{name} must be a CUDA tensor: there is no CPU path")
+    if not t.is_contiguous():
+        raise InvalidError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise InvalidError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise InvalidError(f"{name} must have {dims} dimensions, got {tuple(t.shape)}")
+
+
+def _done(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == -1:
+        raise InvalidError(f"{what}: bad argument")
+    if code == -2:
+        raise UnsupportedError(f"{what}: size not supported by this kernel")
+    raise RuntimeError(f"{what}: CUDA error {code}")
+
+
+# --------------------------------------------------------------------------- embedding
+def embed_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """float32 [T, h] rows of `table` ([vocab, h], float32 or bfloat16) at int32 ids [T]."""
+    _check(table, "table", dims=2)
+    _check(ids, "ids", torch.int32, 1)
+    out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
+    _done(_lib().lrm_embed_rows(_ptr(table), _code(table.dtype), _ptr(ids), _ptr(out),
+                                ids.numel(), table.shape[1], table.shape[0], _stream()), "embed_rows")
+    return out
+
+
+# --------------------------------------------------------------------------- norm
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+             rows: Optional[torch.Tensor] = None, partials: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMSNorm of float32 rows; see csrc/norm.cu for `rows` and `partials`."""
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", dims=1)
+    hidden = x.shape[1]
+    if weight.shape[0] != hidden:
+        raise InvalidError(f"norm weight has {weight.shape[0]} elements, rows have {hidden}")
+    n_rows = x.shape[0]
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_rows = rows.numel()
+    n_partials, stride = 0, 0
+    if partials is not None:
+        _check(partials, "partials", torch.float32, 3)
+        if tuple(partials.shape[1:]) != tuple(x.shape):
+            raise InvalidError("partials must be [n, T, h]")
+        n_partials, stride = partials.shape[0], x.numel()
+    out = torch.empty((n_rows, hidden), dtype=out_dtype, device=x.device)
+    _done(_lib().lrm_rms_norm(_ptr(x), _ptr(weight), _code(weight.dtype), _ptr(out), _code(out_dtype),
+                              _ptr(rows), _ptr(partials), n_partials, ctypes.c_longlong(stride),
+                              n_rows, hidden, ctypes.c_float(eps), _stream()), "rms_norm")
+    return out
+
+
+# --------------------------------------------------------------------------- matrix products
+STORE, ADD, SILU_GATE = "store", "add", "silu_gate"
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, epilogue: str = STORE,
+           out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x . weight^T with weight [out, in] as stored.
+
+    epilogue "store": returns [M, N] in `out_dtype` (default: x's dtype).
+    epilogue "add":   adds into `out`, a float32 [M, N] tensor (the residual stream), in place.
+    epilogue "silu_gate": weight rows alternate in blocks of 8 gate / 8 up rows;
+                      returns silu(gate) * up as [M, N/2] (bfloat16 inputs only).
+    float32 inputs run the true 32-bit kernel; bfloat16 inputs the tensor-core kernels.
+    """
+    _check(x, "x", dims=2)
+    _check(weight, "weight", dims=2)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise InvalidError(f"linear: x has {K} columns, weight has {weight.shape[1]}")
+    if x.dtype != weight.dtype:
+        raise InvalidError(f"linear: x is {x.dtype}, weight is {weight.dtype}")
+    lib = _lib()
+    if epilogue == ADD:
+        if out is None:
+            raise InvalidError("linear: epilogue 'add' needs the tensor to add into")
+        _check(out, "out", torch.float32, 2)
+        if tuple(out.shape) != (M, N):
+            raise InvalidError(f"linear: out must be [{M}, {N}]")
+    if x.dtype == torch.float32:
+        if epilogue == SILU_GATE:
+            raise UnsupportedError("linear: the float32 kernel has no fused gate epilogue")
+        if epilogue == STORE:
+            if out_dtype not in (None, torch.float32):
+                raise InvalidError("linear: float32 inputs give float32 outputs")
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        _done(lib.lrm_gemm_f32(_ptr(x), _ptr(weight), _ptr(out), M, N, K,
+                               1 if epilogue == ADD else 0, _stream()), "gemm_f32")
+        return out
+    if x.dtype != torch.bfloat16:
+        raise UnsupportedError(f"linear: dtype {x.dtype}")
+    if epilogue == STORE:
+        out_dtype = out_dtype or torch.bfloat16
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        mode = 0 if out_dtype == torch.bfloat16 else 1
+        if out_dtype not in (torch.bfloat16, torch.float32):
+            raise UnsupportedError(f"linear: out dtype {out_dtype}")
+    elif epilogue == ADD:
+        mode = 2
+    elif epilogue == SILU_GATE:
+        if N % 16 != 0:
+            raise UnsupportedError("linear: the fused gate epilogue needs a multiple of 16 rows")
+        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        mode = 3
+    else:
+        raise InvalidError(f"linear: unknown epilogue {epilogue!r}")
+    from . import gemm_dispatch
+    gemm_dispatch.gemm_bf16(x, weight, out, mode)
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, block: int) -> torch.Tensor:
+    """silu(gate) * up from [T, 2I] whose columns alternate in blocks of `block` gate / up."""
+    _check(gate_up, "gate_up", dims=2)
+    inter = gate_up.shape[1] // 2
+    if gate_up.shape[1] % 2 or inter % block:
+        raise InvalidError("silu_mul: width must be 2*I with I a multiple of the block")
+    out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+    _done(_lib().lrm_silu_mul(_ptr(gate_up), _ptr(out), _code(gate_up.dtype),
+                              ctypes.c_longlong(gate_up.shape[0]), inter, block, _stream()), "silu_mul")
+    return out
+
+
+def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += delta, x float32 (the residual sum is always 32-bit)."""
+    _check(x, "x", torch.float32)
+    _check(delta, "delta")
+    if x.shape != delta.shape:
+        raise InvalidError(f"add_: shapes {tuple(x.shape)} and {tuple(delta.shape)}")
+    _done(_lib().lrm_add_inplace(_ptr(x), _ptr(delta), _code(delta.dtype),
+                                 ctypes.c_longlong(x.numel()), _stream()), "add_")
+    return x
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _check(x, "x")
+    if x.dtype == dtype:
+        return x
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _done(_lib().lrm_cast(_ptr(x), _code(x.dtype), _ptr(out), _code(dtype),
+                          ctypes.c_longlong(x.numel()), _stream()), "cast")
+    return out
+
+
+# --------------------------------------------------------------------------- rope + cache store
+def rope_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
+               inv_freq: Optional[torch.Tensor], rotary: int, positions: torch.Tensor,
+               seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+               kv=None, keep_packed: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Rotate q and k of a fused [T, (Hq+2Hk)*d] projection and store k, v.
+
+    Returns (q [T,Hq,d], k [T,Hk,d] or None, v [T,Hk,d] or None); k and v are
+    returned when `keep_packed`, and written to the paged cache view `kv` when
+    one is given.
+    """
+    _check(qkv, "qkv", dims=2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (q_heads + 2 * kv_heads) * head_dim:
+        raise InvalidError("rope_store: qkv width does not match the head geometry")
+    if head_dim % 2:
+        raise UnsupportedError("rope_store: head size must be even")
+    _check(positions, "positions", torch.int32, 1)
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.numel() != rotary // 2:
+            raise InvalidError("rope_store: inv_freq must have rotary/2 entries")
+    dev = qkv.device
+    q = torch.empty((T, q_heads, head_dim), dtype=qkv.dtype, device=dev)
+    k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
+    v = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
+    k_pages = v_pages = table = None
+    stride, page_size = 0, 1
+    if kv is not None:
+        k_pages, v_pages, table, page_size = kv.k, kv.v, kv.page_table, kv.page_size
+        _check(k_pages, "k pages", qkv.dtype, 4)
+        _check(v_pages, "v pages", qkv.dtype, 4)
+        _check(table, "page table", torch.int32, 2)
+        _check(seq_of_token, "seq_of_token", torch.int32, 1)
+        _check(slots, "slots", torch.int32, 1)
+        if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim):
+            raise InvalidError("rope_store: cache pages do not match the head geometry")
+        stride = table.shape[1]
+    _done(_lib().lrm_rope_store(_ptr(qkv), _code(qkv.dtype), _ptr(q), _ptr(k), _ptr(v),
+                                _ptr(k_pages), _ptr(v_pages), _ptr(table), stride, _ptr(positions),
+                                _ptr(seq_of_token), _ptr(slots), _ptr(inv_freq), rotary, T, q_heads,
+                                kv_heads, head_dim, page_size, _stream()), "rope_store")
+    return q, k, v
+
+
+# --------------------------------------------------------------------------- attention
+def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                      seq_of_token: torch.Tensor, max_seq_len: int, scale: float,
+                      window: Optional[int] = None) -> torch.Tensor:
+    """Causal GQA over the step's own packed k, v (sequences start at position 0). -> [T, Hq*d]"""
+    _check(q, "q", dims=3)
+    _check(k, "k", q.dtype, 3)
+    _check(v, "v", q.dtype, 3)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    T, Hq, d = q.shape
+    Hk = k.shape[1]
+    if k.shape != v.shape or k.shape[0] != T or k.shape[2] != d or Hq % Hk:
+        raise InvalidError("attention_prefill: q, k, v shapes do not agree")
+    out = torch.empty((T, Hq * d), dtype=q.dtype, device=q.device)
+    from . import attention_dispatch
+    attention_dispatch.prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len, scale, window or 0)
+    return out
+
+
+def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Tensor,
+                     max_kv_len: int, scale: float, window: Optional[int] = None) -> torch.Tensor:
+    """One query per sequence over its cached keys (the newest already stored). -> [B, Hq*d]"""
+    _check(q, "q", dims=3)
+    _check(kv.k, "k pages", q.dtype, 4)
+    _check(kv.v, "v pages", q.dtype, 4)
+    _check(kv.page_table, "page table", torch.int32, 2)
+    _check(slots, "slots", torch.int32, 1)
+    _check(kv_lens, "kv_lens", torch.int32, 1)
+    B, Hq, d = q.shape
+    if tuple(kv.k.shape[1:]) != (kv.kv_heads, kv.page_size, d) or Hq % kv.kv_heads:
+        raise InvalidError("attention_decode: cache pages do not match the query geometry")
+    out = torch.empty((B, Hq * d), dtype=q.dtype, device=q.device)
+    from . import attention_dispatch
+    attention_dispatch.decode(q, kv, out, slots, kv_lens, max_kv_len, scale, window or 0)
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """int32 [n]: largest logit per row, lowest id on ties, -1 for a row with a non-finite logit."""
+    _check(logits, "logits", torch.float32, 2)
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _done(_lib().lrm_argmax_rows(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream()),
+          "argmax_rows")
+    return out
+
+
+def sample_gumbel_rows(logits: torch.Tensor, temperature: float, seed: int, keys: torch.Tensor) -> torch.Tensor:
+    """int32 [n]: a draw from softmax(logits / temperature) per row; `keys` int64 [n] names each row's stream."""
+    _check(logits, "logits", torch.float32, 2)
+    _check(keys, "keys", torch.int64, 1)
+    if keys.numel() != logits.shape[0]:
+        raise InvalidError("sample_gumbel_rows: one key per row")
+    if not temperature > 0:
+        raise InvalidError("sample_gumbel_rows: temperature must be positive")
+    out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
+    _done(_lib().lrm_sample_gumbel_rows(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
+                                        ctypes.c_float(temperature),
+                                        ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(keys),
+                                        _stream()), "sample_gumbel_rows")
+    return out

@@ -1,0 +1,42 @@
+"""A stored [out, in] matrix and the product with it, shared by the parts that project."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+
+
+class LinearWeight:
+    """y = x . W^T (no bias: crates/model-runtime/src/execute.rs:45-47).
+
+    Precision follows storage: a matrix stored in bfloat16 multiplies bfloat16
+    activations on the tensor cores; a matrix stored in 32-bit stays 32-bit and
+    multiplies through the float32 kernel even under bfloat16 activations.
+    """
+
+    def __init__(self, weight: torch.Tensor):
+        self.weight = weight.contiguous()
+
+    @property
+    def out_features(self) -> int:
+        return self.weight.shape[0]
+
+    def supports_fused_gate(self, x_dtype: torch.dtype) -> bool:
+        return self.weight.dtype == torch.bfloat16 and x_dtype == torch.bfloat16
+
+    def __call__(self, x: torch.Tensor, epilogue: str = ops.STORE, out: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        w = self.weight
+        if x.dtype == w.dtype:
+            return ops.linear(x, w, epilogue, out, out_dtype)
+        if w.dtype == torch.float32 and x.dtype == torch.bfloat16:
+            x32 = ops.cast(x, torch.float32)
+            if epilogue == ops.ADD:
+                return ops.linear(x32, w, ops.ADD, out)
+            y = ops.linear(x32, w)
+            return ops.cast(y, out_dtype or torch.bfloat16)
+        # bfloat16 matrix under float32 activations does not occur: the float32
+        # runtime widens every weight when it loads.
+        return ops.linear(x, ops.cast(w, x.dtype), epilogue, out, out_dtype)

@@ -1,0 +1,50 @@
+"""Token choice for a batch of rows: on the device where a kernel exists, else on the host."""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from ..errors import OptionsError
+from ..kernels import ops
+from .host import SplitMix64, sample_host
+from .options import Sampling
+
+
+class BatchSampler:
+    """Picks one token per row of a step's logits.
+
+    Greedy: device argmax, lowest id on ties; a row with non-finite logits is an
+    error ("invalid GPU logits", crates/llama-rs/src/generation.rs:33-40).
+    Plain temperature (no top-k/top-p/penalty): device Gumbel-max, keyed by
+    (seed, request, step) so a row's draw does not depend on its batch.
+    Anything else: the reference's host sampler on logits copied back, one
+    SplitMix64 stream per request seeded with seed + request number.
+    """
+
+    def __init__(self, options: Sampling):
+        options.validate()
+        self.options = options
+        self._rngs = {}
+
+    def pick(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int],
+             histories: Sequence[Sequence[int]]) -> List[int]:
+        o = self.options
+        if o.greedy:
+            ids = ops.argmax_rows(logits).tolist()
+            if any(i < 0 for i in ids):
+                raise OptionsError("invalid GPU logits")
+            return ids
+        if o.plain_temperature:
+            keys = torch.tensor([(r << 32) | s for r, s in zip(requests, steps)], dtype=torch.int64)
+            keys = keys.to(logits.device)
+            ids = ops.sample_gumbel_rows(logits, o.temperature, o.seed, keys).tolist()
+            if any(i < 0 for i in ids):
+                raise OptionsError("invalid GPU logits")
+            return ids
+        rows = logits.detach().to("cpu").numpy()
+        out = []
+        for row, request, history in zip(rows, requests, histories):
+            rng = self._rngs.setdefault(request, SplitMix64(o.seed + request))
+            out.append(sample_host(row, history, rng, o))
+        return out

@@ -1,0 +1,56 @@
+"""Random-weights mode: write a model folder from a configuration and a seed.
+
+The reference has random weights only in test fixtures
+(crates/llama-rs/tests/common/mod.rs:86-100); here it is a first-class mode
+because benchmarks and tests run without checkpoints. Every tensor has its own
+generator keyed by (seed, tensor name), so a tensor's values do not depend on
+which other tensors exist or in which order they are made.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+from typing import Callable, Dict, Mapping
+
+import torch
+
+from .loader import TensorSpec
+from .safetensors_io import write_safetensors
+
+
+def _generator(seed: int, name: str) -> torch.Generator:
+    digest = hashlib.sha256(f"{seed}:{name}".encode("utf-8")).digest()
+    return torch.Generator().manual_seed(int.from_bytes(digest[:8], "little") >> 1)
+
+
+def random_tensors(wanted: Mapping[str, TensorSpec], seed: int, std: float = 0.02,
+                   vector_mean: float = 1.0, vector_std: float = 0.0,
+                   dtype: torch.dtype = torch.bfloat16,
+                   is_vector: Callable[[str, TensorSpec], bool] = None) -> Dict[str, torch.Tensor]:
+    """N(0, std) for matrices; N(vector_mean, vector_std) for 1-D scale vectors (norm weights)."""
+    out = {}
+    for name, spec in wanted.items():
+        gen = _generator(seed, name)
+        vector = is_vector(name, spec) if is_vector else len(spec.shape) == 1
+        if spec.kind == "integer":
+            out[name] = torch.zeros(spec.shape, dtype=torch.int32)
+        elif vector:
+            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * vector_std + vector_mean
+            out[name] = t.to(dtype)
+        else:
+            out[name] = (torch.randn(spec.shape, generator=gen, dtype=torch.float32) * std).to(dtype)
+    return out
+
+
+def write_model_folder(model_dir: str, config_dict: dict, tensors: Mapping[str, torch.Tensor],
+                       seed: int = None) -> str:
+    """config.json + model.safetensors in `model_dir` (created if needed)."""
+    os.makedirs(model_dir, exist_ok=True)
+    with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as handle:
+        json.dump(config_dict, handle, indent=1)
+    meta = {"format": "pt"}
+    if seed is not None:
+        meta["seed"] = str(seed)
+    write_safetensors(os.path.join(model_dir, "model.safetensors"), dict(tensors), meta)
+    return model_dir
