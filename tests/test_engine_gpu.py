@@ -1,0 +1,372 @@
+"""The engine in-process: parts alone, cutting invariance, long decoding, generation, a toy mixer."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def engine():
+    from llama_rs_metal_b200 import Engine
+    return Engine()
+
+
+def open_runner(engine, model_dir, dtype, max_tokens=2048, max_slots=8):
+    from llama_rs_metal_b200.cache import Cache
+    from llama_rs_metal_b200.engine.session import build_model
+    from llama_rs_metal_b200.engine.step import StepRunner
+    from llama_rs_metal_b200.runtime import Runtime, parse_dtype
+    rt = Runtime(engine.device, parse_dtype(dtype))
+    _, plan, model, _ = build_model(model_dir, rt)
+    cache = Cache(model.cache_requests(), rt.dtype, rt.device, max_tokens, max_slots, max_tokens)
+    return StepRunner(model, cache, rt), cache, model
+
+
+def entry(slot, tokens, want=None):
+    from llama_rs_metal_b200.engine.batch import StepEntry
+    return StepEntry(slot, tokens, range(len(tokens)) if want is None else want)
+
+
+# --------------------------------------------------------------------------- cutting invariance
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_float32_logits_are_identical_however_the_tokens_are_cut(engine, model_dirs, name):
+    vocab = helpers.TINY[name]["config"]["vocab_size"]
+    seqs = [helpers.random_tokens(40 + i, n, vocab) for i, n in enumerate([70, 9, 33])]
+    runner, cache, _ = open_runner(engine, model_dirs[name], "float32")
+    whole = []
+    for s in seqs:
+        slot = cache.open_slot()
+        whole.append(runner.step([entry(slot, s)]).clone())
+        cache.close_slot(slot)
+    # one batch: prompts of 3 tokens, then token by token; shorter sequences end earlier
+    slots = [cache.open_slot() for _ in seqs]
+    got = [[] for _ in seqs]
+    out = runner.step([entry(sl, s[:3]) for sl, s in zip(slots, seqs)])
+    for b in range(3):
+        got[b].append(out[3 * b:3 * b + 3])
+    for p in range(3, 70):
+        live = [b for b in range(3) if p < len(seqs[b])]
+        out = runner.step([entry(slots[b], [seqs[b][p]]) for b in live])
+        for row, b in enumerate(live):
+            got[b].append(out[row:row + 1])
+    for b in range(3):
+        assert torch.equal(torch.cat(got[b]), whole[b]), f"sequence {b} differs between whole and batched decoding"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_padding_and_company_change_no_result(engine, model_dirs, dtype):
+    runner, cache, _ = open_runner(engine, model_dirs["B"], dtype)
+    a, b = helpers.random_tokens(1, 20, 512), helpers.random_tokens(2, 64, 512)
+    s = cache.open_slot()
+    alone = runner.step([entry(s, a)]).clone()
+    cache.close_slot(s)
+    s1, s2 = cache.open_slot(), cache.open_slot()
+    both = runner.step([entry(s2, b), entry(s1, a)])
+    if dtype == "float32":
+        assert torch.equal(both[64:], alone)
+    else:
+        helpers.assert_logits_close(both[64:].cpu(), alone.cpu(), dtype)
+
+
+# --------------------------------------------------------------------------- long decoding, first tokens
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_long_decoding_and_first_tokens(engine, model_dirs, plain_models, name, dtype):
+    vocab = helpers.TINY[name]["config"]["vocab_size"]
+    tokens = helpers.random_tokens(77, 400, vocab)           # crosses six page boundaries
+    ref = P.forward(*plain_models[name], tokens).numpy()
+    runner, cache, _ = open_runner(engine, model_dirs[name], dtype)
+    slot = cache.open_slot()
+    rows = [runner.step([entry(slot, tokens[:1])])]           # a prompt of one token
+    for p in range(1, 400):
+        rows.append(runner.step([entry(slot, [tokens[p]])]))
+    got = torch.cat(rows).cpu().numpy()
+    helpers.assert_logits_close(got[:8], ref[:8], dtype, "first tokens")
+    helpers.assert_logits_close(got, ref, dtype, "long decoding")
+    assert cache.length(slot) == 400
+
+
+def test_a_used_slot_does_not_leak_into_its_next_sequence(engine, model_dirs, plain_models):
+    runner, cache, _ = open_runner(engine, model_dirs["A"], "float32", max_tokens=256, max_slots=1)
+    first, second = helpers.random_tokens(5, 200, 256), helpers.random_tokens(6, 90, 256)
+    s = cache.open_slot()
+    runner.step([entry(s, first, [])])
+    cache.close_slot(s)
+    s = cache.open_slot()
+    got = [runner.step([entry(s, second[:50])])]
+    got += [runner.step([entry(s, [t])]) for t in second[50:]]
+    ref = P.forward(*plain_models["A"], second).numpy()
+    helpers.assert_logits_close(torch.cat(got).cpu().numpy(), ref, "float32", "second tenant of the slot")
+
+
+def test_rejected_steps_change_nothing(engine, model_dirs):
+    from llama_rs_metal_b200.errors import CacheMemoryError, ContextError, InvalidError, UnsupportedError
+    runner, cache, _ = open_runner(engine, model_dirs["A"], "float32", max_tokens=128, max_slots=2)
+    a, b = cache.open_slot(), cache.open_slot()
+    good = runner.step([entry(a, [1, 2, 3])]).clone()
+    with pytest.raises(InvalidError, match="outside vocabulary"):
+        runner.step([entry(a, [256])])
+    with pytest.raises(UnsupportedError):
+        runner.step([entry(a, [4]), entry(b, [5, 6])])         # one goes on, one starts
+    with pytest.raises(UnsupportedError):
+        runner.step([entry(a, [4, 5])])                        # two tokens onto a started sequence
+    with pytest.raises(InvalidError):
+        runner.step([entry(a, [4]), entry(a, [5])])
+    with pytest.raises(InvalidError):
+        runner.step([entry(a, [4], [1])])
+    with pytest.raises(CacheMemoryError):
+        runner.step([entry(b, [1] * 100)])                     # 64 + 128 tokens of pages in a 128-token cache
+    assert cache.length(a) == 3 and cache.length(b) == 0
+    cache.close_slot(a)
+    a = cache.open_slot()
+    assert torch.equal(runner.step([entry(a, [1, 2, 3])]), good)
+
+
+# --------------------------------------------------------------------------- parts alone
+def context_for(runtime, lengths, before=None):
+    from llama_rs_metal_b200.engine.batch import StepEntry, pack_step
+    before = before or [0] * len(lengths)
+    entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lengths)]
+    return pack_step(entries, before, runtime, "prefill" if not any(before) else "decode")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_parts_alone(engine, dtype):
+    from llama_rs_metal_b200.parts import (Attention, GatedMLP, PartSpec, PreNormBlock, RMSNorm,
+                                           ScheduleEntry)
+    from llama_rs_metal_b200.cache import Cache
+    from llama_rs_metal_b200.runtime import Runtime, parse_dtype
+    rt = Runtime(engine.device, parse_dtype(dtype))
+    tol = helpers.TOLERANCE[dtype] * 2
+    h, Hq, Hk, d, I = 72, 6, 2, 32, 104
+    g = torch.Generator().manual_seed(0)
+
+    def w(*shape, scale=0.1):
+        return (torch.randn(*shape, generator=g) * scale).to(rt.dtype)
+
+    lengths = [7, 1, 30]
+    T = sum(lengths)
+    ctx = context_for(rt, lengths)
+    hidden = torch.randn(T, h, generator=g)
+
+    norm = RMSNorm(h, 1e-3)
+    nw = 1 + w(h)
+    norm.bind({"weight": nw.to(DEV)}, rt)
+    want_x = P.rms_norm(hidden.double(), nw.double(), 1e-3)
+    x = norm.forward(hidden.to(DEV), ctx)
+    assert x.dtype == rt.dtype
+    helpers.assert_logits_close(x.float().cpu(), want_x, dtype, "norm part")
+
+    mlp = GatedMLP(h, I)
+    mw = {"gate_proj.weight": w(I, h), "up_proj.weight": w(I, h), "down_proj.weight": w(h, I)}
+    mlp.bind({k: v.to(DEV) for k, v in mw.items()}, rt)
+    resid = hidden.to(DEV).clone()
+    out = mlp.forward(x, ctx, residual=resid)
+    want = hidden.double() + P.gated_mlp(x.double().cpu(), *(mw[k].double() for k in
+                                         ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+    helpers.assert_logits_close(out.cpu(), want, dtype, "feed-forward part")
+
+    attn = Attention(h, Hq, Hk, d, position=PartSpec("rope", dict(head_dim=d, rotary_dim=16, theta=100.0)),
+                     window=5)
+    aw = {"q_proj.weight": w(Hq * d, h), "k_proj.weight": w(Hk * d, h), "v_proj.weight": w(Hk * d, h),
+          "o_proj.weight": w(h, Hq * d)}
+    attn.bind({k: v.to(DEV) for k, v in aw.items()}, rt)
+    cache = Cache([attn.cache_request()], rt.dtype, rt.device, 256, 3, 128)
+    for _ in lengths:
+        cache.open_slot()
+    cache.grow(list(enumerate(lengths)))
+    cache.sync()
+    ctx.entry = ScheduleEntry(0, 0)
+    resid = hidden.to(DEV).clone()
+    out = attn.forward(x, ctx, cache.view(0), residual=resid)
+    xd = x.double().cpu()
+    inv = np.asarray([100.0 ** (-2.0 * i / 16) for i in range(8)]).astype(np.float32)
+    want, at = [], 0
+    for n in lengths:
+        xs = xd[at:at + n]
+        q = P.rope(P.linear(xs, aw["q_proj.weight"].double()).view(n, Hq, d), range(n), inv, 16)
+        k = P.rope(P.linear(xs, aw["k_proj.weight"].double()).view(n, Hk, d), range(n), inv, 16)
+        v = P.linear(xs, aw["v_proj.weight"].double()).view(n, Hk, d)
+        want.append(P.linear(P.attention(q, k, v, window=5).reshape(n, Hq * d), aw["o_proj.weight"].double()))
+        at += n
+    helpers.assert_logits_close(out.cpu(), hidden.double() + torch.cat(want), dtype, "attention part")
+
+    block = PreNormBlock(attn, mlp, norm, norm)
+    out = block.forward(hidden.to(DEV).clone(), ctx, cache.view(0))
+    assert out.shape == (T, h) and torch.isfinite(out).all()
+
+
+# --------------------------------------------------------------------------- generation
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(engine, model_dirs, plain_models, name, dtype):
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    vocab = helpers.TINY[name]["config"]["vocab_size"]
+    prompts = [helpers.random_tokens(20 + i, n, vocab) for i, n in enumerate([5, 11, 17, 1, 64])]
+    model = engine.load(model_dirs[name], dtype=dtype)
+    session = model.session(context=128, max_batch=2)          # five requests through two slots
+    results = session.generate(prompts, GenerationOptions(max_tokens=8, sampling=Sampling(temperature=0.0)),
+                               stop_token_ids=())
+    cfg, tensors = plain_models[name]
+    margin = helpers.TOLERANCE[dtype] * 2
+    for prompt, result in zip(prompts, results):
+        assert result.finish_reason == "length" and len(result.tokens) == 8
+        seq = list(prompt)
+        for token in result.tokens:
+            logits = P.forward(cfg, tensors, seq)[-1].numpy()
+            best = int(np.argmax(logits))
+            # the engine's pick is the oracle's, or within rounding of it
+            assert token == best or logits[best] - logits[token] <= margin * np.abs(logits).max(), \
+                f"picked {token}, the plain implementation picks {best}"
+            seq.append(token)
+    assert session.cache.slots.held == 0 and session.cache.held_pages() == [0]
+
+
+def test_stop_ids_context_and_temperature_through_the_entry_point(engine, model_dirs, plain_models):
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    model = engine.load(model_dirs["B"], dtype="float32")
+    session = model.session(context=64, max_batch=4)
+    prompts = [helpers.random_tokens(30 + i, n, 512) for i, n in enumerate([1, 9, 33, 60])]
+    greedy = GenerationOptions(max_tokens=12, sampling=Sampling(temperature=0.0))
+    free = session.generate(prompts, greedy, stop_token_ids=())
+    assert free[3].finish_reason == "context" and len(free[3].tokens) == 5     # 60 + 4 fed = 64
+    stop = free[1].tokens[3]
+    cut = free[1].tokens.index(stop)
+    stopped = session.generate(prompts, greedy, stop_token_ids=[stop])
+    assert stopped[1].finish_reason == "eos" and stopped[1].tokens == free[1].tokens[:cut]
+    # temperature 0.8, seed 9: repeatable, and independent of which requests share the batch
+    hot = GenerationOptions(max_tokens=12, sampling=Sampling(temperature=0.8, top_k=0, top_p=1.0, seed=9))
+    a = session.generate(prompts[:3], hot, stop_token_ids=())
+    b = session.generate(prompts[:3], hot, stop_token_ids=())
+    assert [r.tokens for r in a] == [r.tokens for r in b]
+    assert a[0].tokens != free[0].tokens or a[1].tokens != free[1].tokens
+    alone = model.session(context=64, max_batch=1).generate(prompts[:1], hot, stop_token_ids=())
+    assert alone[0].tokens == a[0].tokens
+    # the reference's host sampler (top-k, top-p, penalty) runs too and is repeatable
+    ref = GenerationOptions(max_tokens=6, sampling=Sampling(repeat_penalty=1.1, seed=3))
+    assert [r.tokens for r in session.generate(prompts[:2], ref, stop_token_ids=())] == \
+           [r.tokens for r in session.generate(prompts[:2], ref, stop_token_ids=())]
+
+
+def test_session_own_sequence_prefill_decode_reset(engine, model_dirs, plain_models):
+    model = engine.load(model_dirs["A"], dtype="float32")
+    session = model.session(context=96)
+    tokens = helpers.random_tokens(3, 40, 256)
+    ref = P.forward(*plain_models["A"], tokens).numpy()
+    helpers.assert_logits_close(session.prefill(tokens[:30]).cpu().numpy()[None], ref[29:30], "float32")
+    for p in range(30, 40):
+        last = session.decode(tokens[p])
+    helpers.assert_logits_close(last.cpu().numpy()[None], ref[39:40], "float32")
+    assert session.tokens() == tokens
+    k, v = session.snapshot(0)
+    assert k.shape == (40, 2, 16) and torch.isfinite(k).all()
+    from llama_rs_metal_b200.errors import ContextError
+    with pytest.raises(ContextError):
+        session.prefill([1] * 60)
+    assert session.tokens() == tokens
+    session.reset()
+    assert session.tokens() == [] and session.logits() is None
+    helpers.assert_logits_close(session.prefill(tokens[:30]).cpu().numpy()[None], ref[29:30], "float32")
+
+
+# --------------------------------------------------------------------------- a toy mixer with state
+def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(engine, tmp_path):
+    """A running-mean mixer, defined here: per-sequence state = (sum of inputs, count).
+    It is registered, put into every second layer of a toy architecture next to the
+    library's attention, and stepped; no file of the library changes."""
+    import json
+    from dataclasses import dataclass
+    from llama_rs_metal_b200.config.base import read_int
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.parts import LayerSpec, Mixer, ModelPlan, PartSpec, ScheduleEntry, StateRequest
+    from llama_rs_metal_b200.registry import register_architecture, register_mixer
+    from llama_rs_metal_b200.weights import TensorSpec
+
+    @register_mixer("running_mean")
+    class RunningMean(Mixer):
+        def __init__(self, hidden_size):
+            self.h = hidden_size
+
+        def tensors(self):
+            return {"mix.weight": TensorSpec((self.h,))}
+
+        def bind(self, weights, runtime):
+            self.w = weights["mix.weight"].float()
+
+        def cache_request(self):
+            return StateRequest((self.h + 1,))
+
+        def forward(self, x, ctx, cache, residual):
+            state = cache.state
+            cu, slots = ctx.cu_seqlens.tolist(), ctx.slots.tolist()
+            xs = x.float()
+            for b, slot in enumerate(slots):
+                rows = xs[cu[b]:cu[b + 1]]
+                sums = state[slot, :self.h] + rows.cumsum(0)
+                counts = state[slot, self.h] + torch.arange(1, rows.shape[0] + 1, device=x.device)
+                residual[cu[b]:cu[b + 1]] += sums / counts[:, None] * self.w
+                state[slot, :self.h] = sums[-1]
+                state[slot, self.h] = counts[-1]
+            return residual
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        hidden: int
+        layers: int
+        vocab: int
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(read_int(d, "hidden"), read_int(d, "layers"), read_int(d, "vocab"))
+
+        def to_dict(self):
+            return dict(architectures=["ToyForCausalLM"], hidden=self.hidden, layers=self.layers, vocab=self.vocab)
+
+    def toy_plan(c):
+        layers = []
+        for i in range(c.layers):
+            p = f"blocks.{i}."
+            mixer = PartSpec("running_mean", dict(hidden_size=c.hidden), prefix=p) if i % 2 == 0 else \
+                PartSpec("attention", dict(hidden_size=c.hidden, num_heads=2, num_kv_heads=1, head_dim=16,
+                                           position=None), prefix=p + "attn.")
+            layers.append(LayerSpec("pre_norm", mixer,
+                                    PartSpec("gated_mlp", dict(hidden_size=c.hidden, intermediate_size=40), prefix=p + "ff."),
+                                    PartSpec("rms_norm", dict(size=c.hidden, eps=1e-5), prefix=p + "n1."),
+                                    PartSpec("rms_norm", dict(size=c.hidden, eps=1e-5), prefix=p + "n2.")))
+        return ModelPlan(c.hidden, c.vocab, 1 << 20, "embed.weight", tuple(layers),
+                         tuple(ScheduleEntry(i, i) for i in range(c.layers)),
+                         PartSpec("rms_norm", dict(size=c.hidden, eps=1e-5), prefix="final."), "head.weight")
+
+    register_architecture("ToyForCausalLM", ToyConfig, toy_plan)
+    folder = write_random_model(str(tmp_path), dict(architectures=["ToyForCausalLM"], hidden=24, layers=3, vocab=50),
+                                seed=1, std=0.2)
+    runner, cache, model = open_runner(engine, folder, "float32", max_tokens=512, max_slots=3)
+    assert [type(r).__name__ for r in model.cache_requests()] == ["StateRequest", "KeyValueRequest", "StateRequest"]
+    seqs = [helpers.random_tokens(i, n, 50) for i, n in enumerate([12, 5])]
+    whole = []
+    for s in seqs:
+        slot = cache.open_slot()
+        whole.append(runner.step([entry(slot, s)]).clone())
+        cache.close_slot(slot)
+    slots = [cache.open_slot(), cache.open_slot()]              # reused slots: state starts at zero again
+    got = [[], []]
+    out = runner.step([entry(slots[0], seqs[0][:4]), entry(slots[1], seqs[1][:2])])
+    got[0].append(out[:4])
+    got[1].append(out[4:])
+    for p in range(2, 12):
+        live = [b for b in (0, 1) if p + (2 if b == 0 else 0) < len(seqs[b])]
+        if not live:
+            break
+        step = [entry(slots[b], [seqs[b][p + (2 if b == 0 else 0)]]) for b in live]
+        out = runner.step(step)
+        for row, b in enumerate(live):
+            got[b].append(out[row:row + 1])
+    for b in (0, 1):
+        assert torch.allclose(torch.cat(got[b]), whole[b], rtol=1e-5, atol=1e-6)

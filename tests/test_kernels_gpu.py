@@ -1,0 +1,364 @@
+"""Each CUDA kernel alone against the plain implementation, at sizes the engine's models do not use."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+F64 = torch.float64
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llama_rs_metal_b200.kernels import ops
+    return ops
+
+
+def close(got, want, tol, what=""):
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert got.shape == want.shape, f"{what}: {tuple(got.shape)} vs {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite"
+    scale = max(want.abs().max().item(), 1e-30)
+    err = (got - want).abs().max().item() / scale
+    assert err <= tol, f"{what}: off by {err:.3e} of the largest value (allowed {tol:.1e})"
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+TOL = {torch.float32: 1e-5, torch.bfloat16: 1.2e-2}
+
+
+# --------------------------------------------------------------------------- embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_rows(ops, dtype):
+    table = rnd(301, 72, dtype=dtype)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = ops.embed_rows(table, ids)
+    assert out.dtype == torch.float32
+    assert torch.equal(out.cpu(), P.embedding(table.float().cpu(), ids.tolist()))
+
+
+# --------------------------------------------------------------------------- norm
+@pytest.mark.parametrize("hidden", [24, 100, 1000, 4104])
+@pytest.mark.parametrize("wdtype,odtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                           (torch.float32, torch.bfloat16)])
+def test_rms_norm(ops, hidden, wdtype, odtype):
+    x = rnd(7, hidden, scale=3.0)
+    w = (1 + 0.2 * rnd(hidden)).to(wdtype)
+    want = P.rms_norm(x.double().cpu(), w.double().cpu(), 1e-6)
+    close(ops.rms_norm(x, w, 1e-6, odtype), want, 1e-5 if odtype == torch.float32 else 5e-3, "norm")
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    close(ops.rms_norm(x, w, 1e-6, odtype, rows=rows), want[[6, 0, 3]],
+          1e-5 if odtype == torch.float32 else 5e-3, "norm rows")
+
+
+def test_rms_norm_folds_partial_sums_into_the_residual(ops):
+    x = rnd(5, 136)
+    parts = rnd(3, 5, 136, seed=4)
+    w = torch.ones(136, device=DEV)
+    total = x.double().cpu() + parts.double().cpu().sum(0)
+    y = ops.rms_norm(x, w, 1e-5, torch.float32, partials=parts)
+    close(x, total, 1e-6, "residual after fold")
+    close(y, P.rms_norm(total, torch.ones(136, dtype=F64), 1e-5), 1e-5, "norm of folded")
+
+
+# --------------------------------------------------------------------------- matrix products
+SHAPES = [(1, 1, 1), (1, 130, 68), (3, 63, 15), (17, 64, 129), (65, 200, 256), (130, 7, 40), (4, 307, 68)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_linear_float32(ops, M, N, K):
+    x, w = rnd(M, K), rnd(N, K, seed=1)
+    want = P.linear(x.double().cpu(), w.double().cpu())
+    close(ops.linear(x, w), want, 1e-5, "gemm f32")
+    resid = rnd(M, N, seed=2)
+    before = resid.double().cpu()
+    ops.linear(x, w, epilogue=ops.ADD, out=resid)
+    close(resid, before + want, 1e-5, "gemm f32 add")
+
+
+def test_linear_float32_row_does_not_depend_on_the_batch(ops):
+    x, w = rnd(70, 200), rnd(150, 200, seed=1)
+    full = ops.linear(x, w)
+    for r in (0, 63, 64, 69):
+        assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w)[0], full[r])
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES + [(64, 128, 2048), (5, 48, 8)])
+def test_linear_bfloat16(ops, M, N, K):
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    want = P.linear(x.double().cpu(), w.double().cpu())
+    close(ops.linear(x, w), want, 6e-3, "gemm bf16 -> bf16")
+    close(ops.linear(x, w, out_dtype=torch.float32), want, 2e-5 * math.sqrt(K), "gemm bf16 -> f32")
+    resid = rnd(M, N, seed=2)
+    before = resid.double().cpu()
+    ops.linear(x, w, epilogue=ops.ADD, out=resid)
+    close(resid, before + want, 2e-5 * math.sqrt(K), "gemm bf16 add")
+
+
+@pytest.mark.parametrize("M,I,K", [(1, 8, 16), (5, 24, 68), (70, 136, 64), (64, 512, 256)])
+def test_linear_bfloat16_silu_gate(ops, M, I, K):
+    x = rnd(M, K, dtype=torch.bfloat16)
+    gate, up = rnd(I, K, dtype=torch.bfloat16, seed=1), rnd(I, K, dtype=torch.bfloat16, seed=2)
+    fused = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    xd = x.double().cpu()
+    want = P.silu(P.linear(xd, gate.double().cpu())) * P.linear(xd, up.double().cpu())
+    close(ops.linear(x, fused, epilogue=ops.SILU_GATE), want, 8e-3, "fused gate")
+    close(ops.silu_mul(ops.linear(x, fused), 8), want, 1.5e-2, "unfused gate")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("block", [4, 100])
+def test_silu_mul_blocks(ops, dtype, block):
+    I = 100
+    g, u = rnd(6, I, dtype=dtype, scale=2.0), rnd(6, I, dtype=dtype, seed=3)
+    gu = torch.stack([g.view(6, I // block, block), u.view(6, I // block, block)], dim=2).reshape(6, 2 * I)
+    want = P.silu(g.double().cpu()) * u.double().cpu()
+    close(ops.silu_mul(gu.contiguous(), block), want, TOL[dtype] / 2, "silu_mul")
+
+
+def test_add_and_cast(ops):
+    x, d = rnd(9, 77), rnd(9, 77, dtype=torch.bfloat16, seed=5)
+    want = x.double().cpu() + d.double().cpu()
+    close(ops.add_(x, d), want, 1e-6, "add_")
+    y = rnd(1000, 3)
+    assert torch.equal(ops.cast(y, torch.bfloat16), y.to(torch.bfloat16))
+    assert torch.equal(ops.cast(y.to(torch.bfloat16), torch.float32), y.to(torch.bfloat16).float())
+
+
+# --------------------------------------------------------------------------- rope + store
+class View:
+    def __init__(self, pages, kv_heads, page_size, d, dtype, slots=3, per_seq=6, fill=float("nan")):
+        self.k = torch.full((pages, kv_heads, page_size, d), fill, dtype=dtype, device=DEV)
+        self.v = torch.full((pages, kv_heads, page_size, d), fill, dtype=dtype, device=DEV)
+        self.page_table = torch.full((slots, per_seq), -1, dtype=torch.int32, device=DEV)
+        self.page_size, self.kv_heads, self.head_dim, self.window = page_size, kv_heads, d, None
+
+
+def i32(values):
+    return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hk,d,R", [(4, 2, 16, 16), (3, 1, 48, 32), (5, 5, 80, 80)])
+def test_rope_store(ops, dtype, Hq, Hk, d, R):
+    cfg = dict(rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+               high_freq_factor=4.0, original_max_position_embeddings=64))
+    inv = P.rope_inverse_frequencies(cfg, R)
+    positions = [0, 1, 63, 64, 130, 4999]
+    T = len(positions)
+    qkv = rnd(T, (Hq + 2 * Hk) * d, dtype=dtype)
+    view = View(pages=90, kv_heads=Hk, page_size=64, d=d, dtype=dtype, slots=3, per_seq=80)
+    # tokens 0..4 belong to sequence 0 in slot 2, the last to sequence 1 in slot 0
+    table = view.page_table.cpu()
+    table[2, :3] = torch.tensor([7, 3, 11])
+    table[0, 4999 // 64] = 5
+    view.page_table.copy_(table)
+    q, k, v = ops.rope_store(qkv, Hq, Hk, d, torch.from_numpy(inv).to(DEV), R, i32(positions),
+                             i32([0, 0, 0, 0, 0, 1]), i32([2, 0]), kv=view)
+    x = qkv.double().cpu()
+    want_q = P.rope(x[:, :Hq * d].reshape(T, Hq, d), positions, inv, R)
+    want_k = P.rope(x[:, Hq * d:(Hq + Hk) * d].reshape(T, Hk, d), positions, inv, R)
+    want_v = x[:, (Hq + Hk) * d:].reshape(T, Hk, d)
+    tol = 2e-6 if dtype == torch.float32 else 5e-3
+    close(q, want_q, tol, "q")
+    close(k, want_k, tol, "k")
+    assert torch.equal(v.double().cpu(), want_v)
+    pages = {0: (7, 0), 1: (7, 1), 2: (7, 63), 3: (3, 0), 4: (11, 2), 5: (5, 4999 % 64)}
+    written = torch.zeros(90, 64, dtype=torch.bool)
+    for t, (page, row) in pages.items():
+        assert torch.equal(view.k[page, :, row], k[t]) and torch.equal(view.v[page, :, row], v[t])
+        written[page, row] = True
+    assert torch.isnan(view.k.float().cpu()[~written]).all(), "a row outside the step was written"
+    assert torch.isnan(view.v.float().cpu()[~written]).all()
+
+
+def test_rope_store_skips_pages_a_window_dropped_and_can_leave_q_unrotated(ops):
+    view = View(pages=4, kv_heads=1, page_size=64, d=16, dtype=torch.float32)
+    qkv = rnd(2, 3 * 16)
+    q, k, v = ops.rope_store(qkv, 1, 1, 16, None, 0, i32([10, 70]), i32([0, 0]), i32([1]), kv=view)
+    assert torch.isnan(view.k).all()                      # both pages are -1: nothing stored
+    assert torch.equal(q.view(2, 16), qkv[:, :16]) and torch.equal(k.view(2, 16), qkv[:, 16:32])
+
+
+# --------------------------------------------------------------------------- attention
+def packed_case(lengths, Hq, Hk, d, dtype, seed=0):
+    T = sum(lengths)
+    q, k, v = rnd(T, Hq, d, dtype=dtype, seed=seed), rnd(T, Hk, d, dtype=dtype, seed=seed + 1), \
+        rnd(T, Hk, d, dtype=dtype, seed=seed + 2)
+    cu = np.concatenate([[0], np.cumsum(lengths)])
+    seq_of = np.repeat(np.arange(len(lengths)), lengths)
+    return q, k, v, cu, seq_of
+
+
+def plain_packed(q, k, v, cu, window=None):
+    out = []
+    for a, b in zip(cu[:-1], cu[1:]):
+        out.append(P.attention(q[a:b].double().cpu(), k[a:b].double().cpu(), v[a:b].double().cpu(), window))
+    return torch.cat(out).reshape(q.shape[0], -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (6, 6, 80), (8, 2, 128)])
+@pytest.mark.parametrize("window", [None, 5, 64])
+def test_attention_prefill(ops, dtype, Hq, Hk, d, window):
+    lengths = [1, 9, 70, 33, 130]
+    q, k, v, cu, seq_of = packed_case(lengths, Hq, Hk, d, dtype)
+    got = ops.attention_prefill(q, k, v, i32(cu), i32(seq_of), max(lengths), d ** -0.5, window)
+    close(got, plain_packed(q, k, v, cu, window), TOL[dtype], f"prefill window {window}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_prefill_finds_one_far_key_among_hundreds(ops, dtype):
+    # One key far back is scaled so that its score stands out: the output must be its value.
+    lengths = [300, 257]
+    q, k, v, cu, seq_of = packed_case(lengths, 4, 2, 32, dtype, seed=9)
+    far = {0: 3, 1: 300 + 64}                 # packed index of the far key of each sequence
+    for s, idx in far.items():
+        k[idx] = 0
+        k[idx, :, 0] = 40.0
+    q[cu[1] - 1, :, :] = 0
+    q[cu[1] - 1, :, 0] = 40.0                 # last query of sequence 0
+    q[cu[2] - 1, :, :] = 0
+    q[cu[2] - 1, :, 0] = 40.0
+    got = ops.attention_prefill(q, k, v, i32(cu), i32(seq_of), 300, 32 ** -0.5).view(-1, 4, 32)
+    close(got, plain_packed(q, k, v, cu).view(-1, 4, 32), TOL[dtype], "far key")
+    for s, idx in far.items():
+        last = cu[s + 1] - 1
+        for h in range(4):
+            close(got[last, h], v[idx, h // 2].double(), 2e-2 if dtype == torch.bfloat16 else 1e-4, "value of the far key")
+
+
+def paged_case(ops, lengths, Hq, Hk, d, dtype, page_size=64, poison=1e4, seed=0):
+    """Sequences in shuffled slots and pages; every row no sequence owns is poisoned."""
+    B = len(lengths)
+    slots = [5, 0, 3, 1, 4, 2][:B]
+    per_seq = max(-(-n // page_size) for n in lengths) + 1
+    n_pages = sum(-(-n // page_size) for n in lengths) + 3
+    view = View(n_pages, Hk, page_size, d, dtype, slots=6, per_seq=per_seq, fill=poison)
+    order = list(np.random.default_rng(seed).permutation(n_pages))
+    table = view.page_table.cpu()
+    ks, vs = [], []
+    for b, n in enumerate(lengths):
+        kb, vb = rnd(n, Hk, d, dtype=dtype, seed=seed + 10 + b), rnd(n, Hk, d, dtype=dtype, seed=seed + 20 + b)
+        ks.append(kb)
+        vs.append(vb)
+        for p in range(-(-n // page_size)):
+            page = int(order.pop())
+            table[slots[b], p] = page
+            rows = min(page_size, n - p * page_size)
+            view.k[page, :, :rows] = kb[p * page_size:p * page_size + rows].transpose(0, 1)
+            view.v[page, :, :rows] = vb[p * page_size:p * page_size + rows].transpose(0, 1)
+    view.page_table.copy_(table)
+    q = rnd(B, Hq, d, dtype=dtype, seed=seed + 5)
+    return q, view, slots, ks, vs
+
+
+def plain_decode(q, ks, vs, window=None):
+    out = []
+    for b, (kb, vb) in enumerate(zip(ks, vs)):
+        n = kb.shape[0]
+        qq = torch.zeros(n, q.shape[1], q.shape[2], dtype=F64)
+        qq[-1] = q[b].double().cpu()
+        out.append(P.attention(qq, kb.double().cpu(), vb.double().cpu(), window)[-1].reshape(-1))
+    return torch.stack(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (8, 2, 128), (32, 8, 64)])
+@pytest.mark.parametrize("window", [None, 64, 100])
+def test_attention_decode_over_poisoned_pages(ops, dtype, Hq, Hk, d, window):
+    lengths = [1, 64, 65, 300, 129, 1000]
+    q, view, slots, ks, vs = paged_case(ops, lengths, Hq, Hk, d, dtype)
+    got = ops.attention_decode(q, view, i32(slots), i32(lengths), max(lengths), d ** -0.5, window)
+    close(got, plain_decode(q, ks, vs, window), TOL[dtype], f"decode window {window}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_decode_window_edge(ops, dtype):
+    # The key just outside the window would win every score; the key just inside must still count.
+    lengths, window = [200, 131], 64
+    q, view, slots, ks, vs = paged_case(ops, lengths, 4, 2, 32, dtype, seed=3)
+    table = view.page_table.cpu()
+    for b, n in enumerate(lengths):
+        q[b] = 0
+        q[b, :, 1] = 30.0
+        for pos, strength in ((n - window - 1, 60.0), (n - window, 30.0)):
+            ks[b][pos] = 0
+            ks[b][pos, :, 1] = strength
+            page = int(table[slots[b], pos // 64])
+            view.k[page, :, pos % 64] = ks[b][pos]
+    got = ops.attention_decode(q, view, i32(slots), i32(lengths), max(lengths), 32 ** -0.5, window).view(2, 4, 32)
+    close(got, plain_decode(q, ks, vs, window).view(2, 4, 32), TOL[dtype], "window edge")
+    for b, n in enumerate(lengths):
+        close(got[b, 0], vs[b][n - window, 0].double(), 2e-2, "the key at the window's edge")
+
+
+def test_float32_decode_equals_prefill_bit_for_bit(ops):
+    lengths = [70, 5, 129]
+    q, view, slots, ks, vs = paged_case(ops, lengths, 4, 2, 16, torch.float32, seed=7)
+    dec = ops.attention_decode(q, view, i32(slots), i32(lengths), max(lengths), 0.25)
+    for b, n in enumerate(lengths):
+        qq = rnd(n, 4, 16, seed=99)
+        qq[-1] = q[b]
+        pre = ops.attention_prefill(qq, ks[b].contiguous(), vs[b].contiguous(), i32([0, n]),
+                                    i32([0] * n), n, 0.25)
+        assert torch.equal(pre[-1], dec[b])
+
+
+# --------------------------------------------------------------------------- sampling
+def test_argmax_rows_ties_and_non_finite(ops):
+    logits = rnd(5, 5003)
+    logits[0, 4000] = logits[0, 17] = 50.0        # tie: lowest id wins
+    logits[1, 5002] = 60.0
+    logits[2, 100] = float("nan")
+    logits[3, 7] = float("inf")
+    got = ops.argmax_rows(logits).tolist()
+    assert got[:2] == [17, 5002] and got[2] == -1 and got[3] == -1
+    assert got[4] == P.argmax_lowest(logits[4].cpu())
+    small = torch.tensor([[1.0, 3.0, 3.0]], device=DEV)
+    assert ops.argmax_rows(small).tolist() == [1]
+
+
+def gumbel_twin(logits, temperature, seed, key):
+    """The kernel's draw, restated on the CPU with the same integer hash (csrc/sampling.cu)."""
+    mask = (1 << 64) - 1
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        return z ^ (z >> 31)
+    scores = []
+    for i, v in enumerate(logits):
+        z = mix((mix((seed + 0x9E3779B97F4A7C15 * (key + 1)) & mask) + i) & mask)
+        u = (float(z >> 40) + 0.5) / 16777216.0
+        scores.append(float(v) / temperature - math.log(-math.log(u)))
+    return scores
+
+
+def test_gumbel_sampling_matches_its_cpu_twin_and_ignores_batch_company(ops):
+    logits = rnd(6, 333, scale=2.0)
+    keys = torch.tensor([(r << 32) | 3 for r in range(6)], dtype=torch.int64, device=DEV)
+    got = ops.sample_gumbel_rows(logits, 0.8, 9, keys).tolist()
+    for r in range(6):
+        scores = gumbel_twin(logits[r].cpu().tolist(), 0.8, 9, (r << 32) | 3)
+        best = max(scores)
+        assert scores[got[r]] >= best - 1e-4       # the same draw, up to float32 rounding of a near tie
+    alone = ops.sample_gumbel_rows(logits[4:5].contiguous(), 0.8, 9, keys[4:5].contiguous()).tolist()
+    assert alone[0] == got[4]
+
+
+def test_gumbel_sampling_follows_the_distribution(ops):
+    probs = torch.tensor([0.5, 0.25, 0.125, 0.125])
+    n = 20000
+    logits = (probs.log() * 0.7).repeat(n, 1).contiguous().to(DEV)       # temperature 0.7 undoes the 0.7
+    keys = torch.arange(n, dtype=torch.int64, device=DEV)
+    counts = torch.bincount(ops.sample_gumbel_rows(logits, 0.7, 1, keys).long().cpu(), minlength=4) / n
+    assert torch.allclose(counts, probs, atol=0.015)
