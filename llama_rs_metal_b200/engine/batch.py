@@ -44,9 +44,9 @@ class StepContext:
     fresh_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
 
 
-def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runtime: Runtime,
-              phase: str) -> StepContext:
-    """Build the packed int32 arrays on the host and copy them to the device in one transfer."""
+def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int]):
+    """The step's int32 arrays in one host buffer, laid out as
+    [token ids T | positions T | sequence of token T | cu_seqlens B+1 | slots B | kv lengths B | wanted rows n]."""
     counts = [len(e.tokens) for e in entries]
     T, B = sum(counts), len(entries)
     n_want = sum(len(e.want) for e in entries)
@@ -69,15 +69,28 @@ def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runti
             w += 1
         at += n
         cu[b + 1] = at
+    return host, T, B, n_want, max(counts), int(kv_lens.max())
+
+
+def context_over(dev: torch.Tensor, runtime: Runtime, phase: str, T: int, B: int, n_want: int,
+                 max_seq_len: int, max_kv_len: int) -> StepContext:
+    """A StepContext whose arrays are slices of `dev`, a device copy of pack_host's buffer."""
+    o = 3 * T
+    return StepContext(
+        runtime=runtime, phase=phase, num_tokens=T, num_seqs=B, max_seq_len=max_seq_len,
+        max_kv_len=max_kv_len,
+        token_ids=dev[:T], positions=dev[T:2 * T], seq_of_token=dev[2 * T:3 * T],
+        cu_seqlens=dev[o:o + B + 1], slots=dev[o + B + 1:o + 2 * B + 1],
+        kv_lens=dev[o + 2 * B + 1:o + 3 * B + 1], wanted_rows=dev[o + 3 * B + 1:o + 3 * B + 1 + n_want])
+
+
+def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runtime: Runtime,
+              phase: str) -> StepContext:
+    """Build the packed int32 arrays on the host and copy them to the device in one transfer."""
+    host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, lengths_before)
     device = runtime.device
     if device.type == "cuda":
         dev = torch.from_numpy(host).pin_memory().to(device, non_blocking=True)
     else:
         dev = torch.from_numpy(host).to(device)
-    o = 3 * T
-    return StepContext(
-        runtime=runtime, phase=phase, num_tokens=T, num_seqs=B, max_seq_len=max(counts),
-        max_kv_len=int(kv_lens.max()),
-        token_ids=dev[:T], positions=dev[T:2 * T], seq_of_token=dev[2 * T:3 * T],
-        cu_seqlens=dev[o:o + B + 1], slots=dev[o + B + 1:o + 2 * B + 1],
-        kv_lens=dev[o + 2 * B + 1:o + 3 * B + 1], wanted_rows=dev[o + 3 * B + 1:])
+    return context_over(dev, runtime, phase, T, B, n_want, max_seq_len, max_kv_len)

@@ -71,6 +71,14 @@ class DecoderModel:
                 out[entry.cache] = self.blocks[entry.layer].mixer.cache_request()
         return [out[i] for i in range(len(out))]
 
+    @property
+    def graph_safe(self) -> bool:
+        """True when every part only enqueues device work, so a decode step can be a CUDA graph."""
+        parts = [self.final_norm]
+        for block in self.blocks:
+            parts += [block, block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm]
+        return all(p.graph_safe for p in parts)
+
     # -- weights ---------------------------------------------------------------------
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         plan = self.plan

@@ -7,17 +7,23 @@ before anything is launched or changed, so a rejected step leaves the cache as
 it was (the reference validates before submitting for the same reason,
 crates/model-runtime/src/session.rs:114-130). Sequences' lengths advance only
 after the step's kernels are enqueued.
+
+A decode step's launches are captured once per (batch size, length bucket) in
+a CUDA graph and replayed: its int32 inputs live in a static device buffer
+that each step overwrites with one host-to-device copy.
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import Cache
 from ..errors import InvalidError, PoisonedError, UnsupportedError
+from ..kernels import ops
 from ..runtime import Runtime
-from .batch import StepContext, StepEntry, pack_step
+from .batch import StepContext, StepEntry, context_over, pack_host, pack_step
 from .model import DecoderModel
 
 
@@ -49,16 +55,60 @@ def validate_entries(entries: Sequence[StepEntry], vocab_size: int) -> None:
                 raise InvalidError(f"wanted place {p} is outside the {len(e.tokens)} tokens of the entry")
 
 
+def length_bucket(n: int) -> int:
+    """Launch geometry of decode attention depends on the longest sequence only through this."""
+    bucket = 256
+    while bucket < n:
+        bucket *= 2
+    return bucket
+
+
+class _DecodeGraph:
+    """One captured decode step: static inputs, the graph, its logits [B, vocab]."""
+
+    RING = 4
+
+    def __init__(self, runner: "StepRunner", batch: int, bucket: int):
+        rt = runner.runtime
+        self.batch = batch
+        self.size = 7 * batch + 1  # pack_host's layout with T = B and every row wanted
+        self.static = torch.zeros(self.size, dtype=torch.int32, device=rt.device)
+        self.ctx = context_over(self.static, rt, "decode", batch, batch, batch, 1, bucket)
+        self.pinned = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events = [torch.cuda.Event() for _ in range(self.RING)]
+        self.turn = 0
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.launches = 0
+
+    def upload(self, host: np.ndarray) -> None:
+        i = self.turn % self.RING
+        self.turn += 1
+        self.events[i].synchronize()  # the copy that last used this staging buffer is done
+        self.pinned[i].numpy()[:] = host
+        self.static.copy_(self.pinned[i], non_blocking=True)
+        self.events[i].record()
+
+
 class StepRunner:
     """Binds a model and a cache and runs steps on the current CUDA stream."""
 
-    def __init__(self, model: DecoderModel, cache: Cache, runtime: Runtime):
+    def __init__(self, model: DecoderModel, cache: Cache, runtime: Runtime, use_graphs: bool = True):
         self.model, self.cache, self.runtime = model, cache, runtime
         self.poisoned = False
         self.steps_run = 0
+        self.use_graphs = use_graphs and runtime.device.type == "cuda" and model.graph_safe
+        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        self._pool = None
+        self.last_launches = 0  # kernels of this library launched by the last step
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """float32 logits [wanted places, vocab] on the device, in entry order then `want` order."""
+    # -- the public step ----------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
+        """float32 logits [wanted places, vocab] on the device, in entry order then `want` order.
+
+        With `borrow` the result may be a buffer the next step overwrites (the
+        generation loop samples from it at once); otherwise it is the caller's.
+        """
         if self.poisoned:
             raise PoisonedError("a device error poisoned this session; reset it")
         entries = list(entries)
@@ -68,14 +118,54 @@ class StepRunner:
         phase = classify_step(entries, before)
         growth = [(e.slot, n + len(e.tokens)) for e, n in zip(entries, before)]
         cache.check_growth(growth)  # raises before anything changes
-        ctx = pack_step(entries, before, self.runtime, phase)
         cache.grow(growth)
         cache.sync()
         try:
-            logits = self.model.forward(ctx, cache)
+            if phase == "decode" and self.use_graphs:
+                logits = self._decode_with_graph(entries, before, borrow)
+            else:
+                ctx = pack_step(entries, before, self.runtime, phase)
+                start = ops.launch_count()
+                logits = self.model.forward(ctx, cache)
+                self.last_launches = ops.launch_count() - start
         except Exception:
             self.poisoned = True
             raise
         cache.commit(growth)
         self.steps_run += 1
         return logits
+
+    # -- decode through a captured graph ---------------------------------------------
+    def _decode_with_graph(self, entries: List[StepEntry], before: List[int], borrow: bool) -> torch.Tensor:
+        batch = len(entries)
+        all_rows = [StepEntry(e.slot, e.tokens, (0,)) for e in entries]
+        host, _, _, _, _, max_kv_len = pack_host(all_rows, before)
+        key = (batch, length_bucket(max_kv_len))
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._graphs[key] = _DecodeGraph(self, *key)
+        graph.upload(host)
+        if graph.graph is None:
+            self._capture(graph)
+        graph.graph.replay()
+        self.last_launches = graph.launches
+        logits = graph.logits
+        wanted = [b for b, e in enumerate(entries) for _ in e.want]
+        if wanted != list(range(batch)):
+            index = torch.tensor(wanted, dtype=torch.long, device=logits.device)
+            return logits.index_select(0, index)
+        return logits if borrow else logits.clone()
+
+    def _capture(self, graph: _DecodeGraph) -> None:
+        # One eager run first: it loads every kernel the step needs and writes
+        # exactly what the replay will write again, so it changes no result.
+        self.model.forward(graph.ctx, self.cache)
+        torch.cuda.current_stream().synchronize()
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        captured = torch.cuda.CUDAGraph()
+        start = ops.launch_count()
+        with torch.cuda.graph(captured, pool=self._pool):
+            graph.logits = self.model.forward(graph.ctx, self.cache)
+        graph.launches = ops.launch_count() - start
+        graph.graph = captured

@@ -49,8 +49,18 @@ def _check(t: torch.Tensor, name: str, dtype=None, dims: Optional[int] = None) -
         raise InvalidError(f"{name} must have {dims} dimensions, got {tuple(t.shape)}")
 
 
-def _done(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched (or captured) by this process."""
+    return _launches
+
+
+def _done(code: int, what: str, launches: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += launches
         return
     if code == -1:
         raise InvalidError(f"{what}: bad argument")

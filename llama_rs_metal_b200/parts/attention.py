@@ -38,6 +38,10 @@ class Attention(Mixer):
         self.q_only: Optional[LinearWeight] = None
         self.out: Optional[LinearWeight] = None
 
+    @property
+    def graph_safe(self) -> bool:
+        return self.position is None or self.position.graph_safe
+
     def tensors(self) -> Dict[str, TensorSpec]:
         q, kv, h = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim, self.hidden_size
         out = {"q_proj.weight": TensorSpec((q, h)), "k_proj.weight": TensorSpec((kv, h)),

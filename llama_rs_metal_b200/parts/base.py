@@ -97,6 +97,9 @@ class Part:
     """Base of every part: declares tensors, receives them bound to the device."""
 
     kind = "part"
+    # True when forward() only enqueues device work (no host read of device data, no
+    # host-side branching on it): then a decode step may be captured in a CUDA graph.
+    graph_safe = False
 
     def tensors(self) -> Dict[str, TensorSpec]:
         """Own tensor names (relative to the part's prefix) and their shapes."""

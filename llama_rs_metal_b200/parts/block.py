@@ -10,6 +10,8 @@ class PreNormBlock(Block):
     """hidden += mixer(norm(hidden)); hidden += feed_forward(norm(hidden))
     (crates/model-runtime/src/execute.rs:24,196-199,236)."""
 
+    graph_safe = True
+
     def forward(self, hidden, ctx, cache):
         x = self.mixer_norm.forward(hidden, ctx)
         hidden = self.mixer.forward(x, ctx, cache, residual=hidden)

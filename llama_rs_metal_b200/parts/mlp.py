@@ -21,6 +21,8 @@ class GatedMLP(FeedForward):
     (crates/model-runtime/src/execute.rs:251-267). Only SiLU is built, as in the
     reference (crates/model-format/src/mlx/config.rs:58-64)."""
 
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         if activation != "silu":
             raise UnsupportedError("activation other than SiLU")

@@ -16,6 +16,8 @@ class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * w, statistics in float32
     (crates/metal-backend/src/shaders/elementwise.metal:31-46; no +1 offset for Llama)."""
 
+    graph_safe = True
+
     def __init__(self, size: int, eps: float):
         self.size = size
         self.eps = float(eps)

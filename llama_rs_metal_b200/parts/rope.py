@@ -24,6 +24,8 @@ class RotaryEmbedding(PositionEncoding):
     1/((1-smooth)/factor + smooth). `linear`: scale = 1/factor (config.rs:166-172).
     """
 
+    graph_safe = True
+
     def __init__(self, head_dim: int, rotary_dim: int, theta: float, scaling: str = "default",
                  factor: float = 1.0, low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
                  original_max_position_embeddings: int = 0):
