@@ -1,0 +1,451 @@
+// Tiled bfloat16 attention on the warp-level tensor path (mma.sync m16n8k16,
+// ldmatrix, cp.async), float32 softmax and accumulation.
+//
+//  * prefill: causal grouped-query flash attention over a step's own packed
+//    q, k, v (ragged batch, every sequence starts at position 0). One CTA = 64
+//    queries of one head; K/V arrive in 64-key tiles, double buffered.
+//  * decode: one query per sequence over the paged cache, split over the keys.
+//    One CTA = (sequence, kv head, split); its 4 warps each take 16 keys of
+//    every 64-key page, so K/V are read once for all query heads of the group.
+//    Each warp leaves an unnormalised partial (acc, max, mass); a second kernel
+//    merges the partials: out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M).
+//    (reference: crates/metal-backend/src/shaders/attention.metal:61-121 splits
+//    the context the same way, one SIMD group per chunk.)
+//
+// Scores are kept in the log2 domain: s2 = (q.k) * scale * log2(e), p = 2^(s2 - m2).
+// Rows of a tile beyond a sequence's length are zero-filled on the way into
+// shared memory, so stale cache contents (even NaN bit patterns) never reach a
+// product. Head sizes 32, 64 and 128; other sizes use the row-wise kernel.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kTile = 64;     // keys per tile (= the cache's page size)
+constexpr int kThreads = 128;  // 4 warps
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3,
+                                        const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                              uint32_t& r3, const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(a));
+}
+// 16-byte asynchronous copy; `bytes` = 0 writes zeros and reads nothing.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Copy `rows` x D bfloat16 (row pitch `pitch` elements in global memory) into a
+// padded shared tile; rows >= valid_rows are zero-filled.
+template <int D>
+__device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat16* src, size_t pitch,
+                                          int valid_rows) {
+  constexpr int STRIDE = D + 8, CHUNKS = D / 8;
+  for (int idx = threadIdx.x; idx < kTile * CHUNKS; idx += kThreads) {
+    const int r = idx / CHUNKS, c = idx % CHUNKS;
+    const bool ok = r < valid_rows;
+    cp_async16(dst + r * STRIDE + c * 8, ok ? src + r * pitch + c * 8 : src, ok ? 16 : 0);
+  }
+}
+
+// Query fragments of 16 rows x D from global memory: row r lives at base + r * pitch.
+template <int D>
+__device__ __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const __nv_bfloat16* base,
+                                       size_t pitch, int valid_rows) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = g + 8 * half;
+#pragma unroll
+      for (int hi = 0; hi < 2; ++hi) {
+        uint32_t v = 0u;
+        if (r < valid_rows)
+          v = *reinterpret_cast<const uint32_t*>(base + r * pitch + 16 * ks + 8 * hi + 2 * t);
+        qa[ks][half + 2 * hi] = v;
+      }
+    }
+  }
+}
+
+// s[nt] (16 x 8) += Q (16 x D) . K^T for the 8-key tiles nt of `keys` (rows of a padded tile).
+template <int D, int NT>
+__device__ __forceinline__ void scores(float (&s)[NT][4], const uint32_t (&qa)[D / 16][4],
+                                       const __nv_bfloat16* keys) {
+  constexpr int STRIDE = D + 8;
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(b0, b1, b2, b3, keys + (8 * nt + (lane & 7)) * STRIDE + 16 * ks + 8 * (lane >> 3));
+      mma16816(s[nt], qa[ks], b0, b1);
+      mma16816(s[nt], qa[ks + 1], b2, b3);
+    }
+  }
+}
+
+// o (16 x D) += P (16 x 16*KK keys) . V, P given as score tiles already turned into probabilities.
+template <int D, int NT>
+__device__ __forceinline__ void weighted_values(float (&o)[D / 8][4], const float (&p)[NT][4],
+                                                const __nv_bfloat16* values) {
+  constexpr int STRIDE = D + 8;
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    uint32_t pa[4];
+    pa[0] = pack_bf16(p[2 * kk][0], p[2 * kk][1]);
+    pa[1] = pack_bf16(p[2 * kk][2], p[2 * kk][3]);
+    pa[2] = pack_bf16(p[2 * kk + 1][0], p[2 * kk + 1][1]);
+    pa[3] = pack_bf16(p[2 * kk + 1][2], p[2 * kk + 1][3]);
+#pragma unroll
+    for (int dn = 0; dn < D / 8; dn += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_trans(b0, b1, b2, b3,
+                    values + (16 * kk + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + 8 * dn +
+                        8 * (lane >> 4));
+      mma16816(o[dn], pa, b0, b1);
+      mma16816(o[dn + 1], pa, b2, b3);
+    }
+  }
+}
+
+// One streaming-softmax update of rows g and g+8 with NT score tiles (already masked to -inf
+// where a key is not visible). m, l: running max (log2 domain) and this thread's share of the mass.
+template <int D, int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
+                                               float (&l)[2]) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * half], s[nt][2 * half + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[half], mx);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no visible key yet
+    const float alpha = exp2f(m[half] - m_use);
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      s[nt][2 * half] = exp2f(s[nt][2 * half] - m_use);
+      s[nt][2 * half + 1] = exp2f(s[nt][2 * half + 1] - m_use);
+      sum += s[nt][2 * half] + s[nt][2 * half + 1];
+    }
+    l[half] = l[half] * alpha + sum;
+    m[half] = m_new;
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn) {
+      o[dn][2 * half] *= alpha;
+      o[dn][2 * half + 1] *= alpha;
+    }
+  }
+}
+
+// --------------------------------------------------------------------------- prefill
+template <int D>
+__global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+    const __nv_bfloat16* __restrict__ v, __nv_bfloat16* __restrict__ out,
+    const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window) {
+  constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
+  __nv_bfloat16* Vs = Ks + 2 * TILE;
+
+  const int qt = gridDim.x - 1 - blockIdx.x;  // long rows of work first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
+  const int q0 = qt * kTile;
+  if (q0 >= len) return;
+  const int kh = h / (q_heads / kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = q0 + 16 * warp;  // this warp's first query (position in the sequence)
+
+  uint32_t qa[D / 16][4];
+  load_q<D>(qa, q + (static_cast<size_t>(start + row0) * q_heads + h) * D,
+            static_cast<size_t>(q_heads) * D, len - row0);
+  float o[D / 8][4];
+#pragma unroll
+  for (int dn = 0; dn < D / 8; ++dn)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  const int kt_first = window > 0 ? max(0, q0 - window + 1) / kTile : 0;
+  const int kt_last = qt;
+  const size_t kv_pitch = static_cast<size_t>(kv_heads) * D;
+  auto issue = [&](int kt, int stage) {
+    const size_t base = (static_cast<size_t>(start + kt * kTile) * kv_heads + kh) * D;
+    load_tile<D>(Ks + stage * TILE, k + base, kv_pitch, len - kt * kTile);
+    load_tile<D>(Vs + stage * TILE, v + base, kv_pitch, len - kt * kTile);
+    cp_async_commit();
+  };
+  issue(kt_first, 0);
+  for (int kt = kt_first; kt <= kt_last; ++kt) {
+    const int stage = (kt - kt_first) & 1;
+    if (kt < kt_last) {
+      issue(kt + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+    scores<D, 8>(s, qa, Ks + stage * TILE);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
+        const int query = row0 + g + 8 * (e >> 1);
+        const bool visible = key <= query && (window <= 0 || key > query - window);
+        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+      }
+    }
+    softmax_update<D, 8>(s, o, m, l);
+    weighted_values<D, 8>(o, s, Vs + stage * TILE);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float total = l[half];
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    const int row = row0 + g + 8 * half;
+    if (row >= len) continue;
+    const float inv = 1.0f / total;
+    __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn)
+      *reinterpret_cast<uint32_t*>(dst + 8 * dn + 2 * t) =
+          pack_bf16(o[dn][2 * half] * inv, o[dn][2 * half + 1] * inv);
+  }
+}
+
+// --------------------------------------------------------------------------- decode
+// partial layout: [sequence][q head][part][D + 2] float32, part = split * 4 + warp,
+// element D = running max (log2 domain), element D + 1 = mass.
+template <int D>
+__global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+    const __nv_bfloat16* __restrict__ v_pages, float* __restrict__ partials,
+    const int* __restrict__ page_table, int table_stride, const int* __restrict__ slots,
+    const int* __restrict__ kv_lens, int q_heads, int kv_heads, int row_groups, float scale_log2,
+    int window, int n_splits) {
+  constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* Vs = Ks + 2 * TILE;
+
+  const int rg = blockIdx.x % row_groups;
+  const int kh = (blockIdx.x / row_groups) % kv_heads;
+  const int b = blockIdx.x / (row_groups * kv_heads);
+  const int split = blockIdx.y;
+  const int group = q_heads / kv_heads;
+  const int head0 = kh * group + 16 * rg;          // first query head of this CTA
+  const int rows = min(16, group - 16 * rg);       // query heads it owns
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+
+  const int len = kv_lens[b];
+  const int first_key = window > 0 ? max(0, len - window) : 0;
+  const int page_first = first_key / kTile, page_end = (len + kTile - 1) / kTile;
+  const int n_pages = page_end - page_first;
+  const int per_split = (n_pages + n_splits - 1) / n_splits;
+  const int p_begin = page_first + split * per_split;
+  const int p_end = min(page_end, p_begin + per_split);
+  const int* table = page_table + static_cast<size_t>(slots[b]) * table_stride;
+
+  uint32_t qa[D / 16][4];
+  load_q<D>(qa, q + (static_cast<size_t>(b) * q_heads + head0) * D, D, rows);
+  float o[D / 8][4];
+#pragma unroll
+  for (int dn = 0; dn < D / 8; ++dn)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  auto issue = [&](int page_index, int stage) {
+    const size_t page = static_cast<size_t>(table[page_index]);
+    const size_t base = (page * kv_heads + kh) * kTile * D;
+    load_tile<D>(Ks + stage * TILE, k_pages + base, D, len - page_index * kTile);
+    load_tile<D>(Vs + stage * TILE, v_pages + base, D, len - page_index * kTile);
+    cp_async_commit();
+  };
+  if (p_begin < p_end) issue(p_begin, 0);
+  for (int p = p_begin; p < p_end; ++p) {
+    const int stage = (p - p_begin) & 1;
+    if (p + 1 < p_end) {
+      issue(p + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+    scores<D, 2>(s, qa, Ks + stage * TILE + 16 * warp * STRIDE);
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = p * kTile + 16 * warp + 8 * nt + 2 * t + (e & 1);
+        const bool visible = key < len && key >= first_key;
+        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+      }
+    }
+    softmax_update<D, 2>(s, o, m, l);
+    weighted_values<D, 2>(o, s, Vs + stage * TILE + 16 * warp * STRIDE);
+    __syncthreads();
+  }
+
+  const int n_parts = n_splits * 4, part = split * 4 + warp;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float total = l[half];
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    const int r = g + 8 * half;
+    if (r >= rows) continue;
+    float* dst = partials + ((static_cast<size_t>(b) * q_heads + head0 + r) * n_parts + part) * (D + 2);
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn)
+      *reinterpret_cast<float2*>(dst + 8 * dn + 2 * t) = make_float2(o[dn][2 * half], o[dn][2 * half + 1]);
+    if (t == 0) {
+      dst[D] = m[half];
+      dst[D + 1] = total;
+    }
+  }
+}
+
+// out[b, head, :] = sum_i acc_i 2^(m_i - M) / sum_i l_i 2^(m_i - M); one block per (b, head).
+template <int D>
+__global__ void attention_merge_kernel(const float* __restrict__ partials,
+                                       __nv_bfloat16* __restrict__ out, int n_parts) {
+  const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (D + 2);
+  float M = -INFINITY;
+  for (int i = 0; i < n_parts; ++i) M = fmaxf(M, src[i * (D + 2) + D]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f, mass = 0.f;
+    for (int i = 0; i < n_parts; ++i) {
+      const float mi = src[i * (D + 2) + D];
+      if (mi == -INFINITY) continue;  // a part that saw no key
+      const float w = exp2f(mi - M);
+      acc = fmaf(src[i * (D + 2) + d], w, acc);
+      mass = fmaf(src[i * (D + 2) + D + 1], w, mass);
+    }
+    out[static_cast<size_t>(blockIdx.x) * D + d] = __float2bfloat16_rn(acc / mass);
+  }
+}
+
+template <int D> int prefill_launch(const void* q, const void* k, const void* v, void* out,
+                                    const int* cu_seqlens, int seqs, int max_seq_len, int q_heads,
+                                    int kv_heads, float scale, int window, cudaStream_t stream) {
+  const int smem = 4 * kTile * (D + 8) * 2;
+  auto kernel = attention_prefill_tiled_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const dim3 grid((max_seq_len + kTile - 1) / kTile, q_heads, seqs);
+  kernel<<<grid, kThreads, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
+      static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads,
+      kv_heads, scale * 1.4426950408889634f, window);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+template <int D> int decode_launch(const void* q, const void* k_pages, const void* v_pages,
+                                   float* partials, void* out, const int* page_table,
+                                   int table_stride, const int* slots, const int* kv_lens, int seqs,
+                                   int q_heads, int kv_heads, float scale, int window, int n_splits,
+                                   cudaStream_t stream) {
+  const int smem = 4 * kTile * (D + 8) * 2;
+  auto kernel = attention_decode_tiled_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const int group = q_heads / kv_heads, row_groups = (group + 15) / 16;
+  const dim3 grid(seqs * kv_heads * row_groups, n_splits);
+  kernel<<<grid, kThreads, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
+      static_cast<const __nv_bfloat16*>(v_pages), partials, page_table, table_stride, slots, kv_lens,
+      q_heads, kv_heads, row_groups, scale * 1.4426950408889634f, window, n_splits);
+  LRM_LAUNCH_CHECK();
+  attention_merge_kernel<D><<<seqs * q_heads, D <= 64 ? 64 : 128, 0, stream>>>(
+      partials, static_cast<__nv_bfloat16*>(out), n_splits * 4);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+// Head sizes the tiled kernels take; the caller falls back to the row-wise kernel otherwise.
+LRM_API int lrm_attention_tiled_supports(int head_dim, int page_size) {
+  return (head_dim == 32 || head_dim == 64 || head_dim == 128) && page_size == kTile ? 1 : 0;
+}
+
+LRM_API int lrm_attention_prefill_tiled(const void* q, const void* k, const void* v, void* out,
+                                        const int* cu_seqlens, int seqs, int max_seq_len,
+                                        int q_heads, int kv_heads, int d, float scale, int window,
+                                        cudaStream_t stream) {
+  if (seqs <= 0 || max_seq_len <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return LRM_BAD_ARGUMENT;
+  if (q_heads > 65535 || seqs > 65535) return LRM_UNSUPPORTED;
+  switch (d) {
+    case 32: return prefill_launch<32>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    case 64: return prefill_launch<64>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    case 128: return prefill_launch<128>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    default: return LRM_UNSUPPORTED;
+  }
+}
+
+// `partials` is scratch: seqs * q_heads * n_splits * 4 * (d + 2) floats.
+LRM_API int lrm_attention_decode_tiled(const void* q, const void* k_pages, const void* v_pages,
+                                       float* partials, void* out, const int* page_table,
+                                       int table_stride, const int* slots, const int* kv_lens,
+                                       int seqs, int q_heads, int kv_heads, int d, int page_size,
+                                       float scale, int window, int n_splits, cudaStream_t stream) {
+  if (seqs <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || n_splits <= 0 ||
+      partials == nullptr)
+    return LRM_BAD_ARGUMENT;
+  if (page_size != kTile || n_splits > 65535) return LRM_UNSUPPORTED;
+  switch (d) {
+    case 32: return decode_launch<32>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, stream);
+    case 64: return decode_launch<64>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, stream);
+    case 128: return decode_launch<128>(q, k_pages, v_pages, partials, out, page_table, table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, window, n_splits, stream);
+    default: return LRM_UNSUPPORTED;
+  }
+}

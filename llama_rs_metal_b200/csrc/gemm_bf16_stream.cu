@@ -1,0 +1,185 @@
+// Weight-streaming bfloat16 product for few rows (decode): Y[M,N] = X[M,K] . W[N,K]^T, M <= 64.
+//
+// Every weight byte is read from HBM exactly once, straight into registers
+// with 16-byte loads, and fed to mma.sync m16n8k16 with the weights as the
+// 16-row operand and the M activation rows as 8-wide column tiles. A thread's
+// 16-byte load holds 8 consecutive k of one weight row; the two halves serve
+// two consecutive MMAs. Within an MMA the hardware's k index is just a label,
+// so the activation fragment is loaded with the same address pattern and the
+// products pair up correctly without any shuffle or shared-memory staging.
+//
+// A CTA owns 16 weight rows; its warps split K in interleaved 128-wide chunks
+// (so many loads are in flight per SM) and their partial sums are added in
+// warp order through shared memory (no atomics: the result is deterministic).
+//
+// Epilogues: 0 store bf16, 1 store f32, 2 add into f32 in place, 3 SiLU gate
+// (rows alternate in blocks of 8 gate / 8 up rows, so a 16-row tile holds 8
+// gated pairs; out is [M, N/2] bf16).
+// (Reference role: the gemv_* family, crates/metal-backend/src/shaders/matrix.metal:10-37.)
+#include "common.cuh"
+
+namespace {
+
+constexpr int kChunk = 128;  // k values a warp handles per iteration
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {  // read once: do not keep in L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_keep(const void* p) {  // activations: reused by every CTA
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+
+template <int NT>
+__global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat16* __restrict__ X,
+                                        const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
+                                        int M, int N, int K, int mode) {
+  extern __shared__ float red[];  // [warps][NT][32 lanes][4]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int row_a = n0 + g, row_b = n0 + g + 8;
+  const bool ok_a = row_a < N, ok_b = row_b < N;
+  const __nv_bfloat16* wa = W + static_cast<size_t>(ok_a ? row_a : 0) * K;
+  const __nv_bfloat16* wb = W + static_cast<size_t>(ok_b ? row_b : 0) * K;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+
+  auto load_w = [&](int k0, uint4 (&a)[4], uint4 (&b)[4]) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int k = k0 + 32 * s + 8 * t;
+      const bool in = k < K;  // K is a multiple of 8: a 16-byte piece is inside or outside
+      a[s] = in && ok_a ? ldg_stream(wa + k) : zero;
+      b[s] = in && ok_b ? ldg_stream(wb + k) : zero;
+    }
+  };
+
+  uint4 cur_a[4], cur_b[4], nxt_a[4], nxt_b[4];
+  int k0 = warp * kChunk;
+  if (k0 < K) load_w(k0, cur_a, cur_b);
+  for (; k0 < K; k0 += warps * kChunk) {
+    const int k_next = k0 + warps * kChunk;
+    if (k_next < K) load_w(k_next, nxt_a, nxt_b);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int k = k0 + 32 * s + 8 * t;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const int m = 8 * j + g;
+        const uint4 x = (m < M && k < K) ? ldg_keep(X + static_cast<size_t>(m) * K + k) : zero;
+        mma16816(acc[j], cur_a[s].x, cur_b[s].x, cur_a[s].y, cur_b[s].y, x.x, x.y);
+        mma16816(acc[j], cur_a[s].z, cur_b[s].z, cur_a[s].w, cur_b[s].w, x.z, x.w);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      cur_a[s] = nxt_a[s];
+      cur_b[s] = nxt_b[s];
+    }
+  }
+
+  // add the warps' partial sums in warp order
+#pragma unroll
+  for (int j = 0; j < NT; ++j)
+    *reinterpret_cast<float4*>(red + ((static_cast<size_t>(warp) * NT + j) * 32 + lane) * 4) =
+        make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+  __syncthreads();
+  for (int item = threadIdx.x; item < NT * 32; item += blockDim.x) {
+    const int j = item >> 5, ln = item & 31, gg = ln >> 2, tt = ln & 3;
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int w = 0; w < warps; ++w) {
+      const float4 v = *reinterpret_cast<const float4*>(red + ((static_cast<size_t>(w) * NT + j) * 32 + ln) * 4);
+      sum.x += v.x;
+      sum.y += v.y;
+      sum.z += v.z;
+      sum.w += v.w;
+    }
+    // sum.x/.y: weight row n0+gg, batch rows 8j+2tt, +1;  sum.z/.w: weight row n0+gg+8
+    const int m0 = 8 * j + 2 * tt;
+    const float vals[2][2] = {{sum.x, sum.z}, {sum.y, sum.w}};  // [batch row offset][weight row half]
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int m = m0 + e;
+      if (m >= M) continue;
+      if (mode == 3) {
+        const int col = (n0 >> 1) + gg;  // gate row n0+gg pairs with up row n0+gg+8
+        if (n0 + gg + 8 < N)
+          static_cast<__nv_bfloat16*>(out)[static_cast<size_t>(m) * (N >> 1) + col] =
+              __float2bfloat16_rn(silu_f32(vals[e][0]) * vals[e][1]);
+        continue;
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int n = n0 + gg + 8 * half;
+        if (n >= N) continue;
+        const size_t o = static_cast<size_t>(m) * N + n;
+        const float v = vals[e][half];
+        if (mode == 0) static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
+        else if (mode == 1) static_cast<float*>(out)[o] = v;
+        else static_cast<float*>(out)[o] += v;
+      }
+    }
+  }
+}
+
+template <int NT>
+int launch_stream(const void* X, const void* W, void* out, int M, int N, int K, int mode, int warps,
+                  cudaStream_t stream) {
+  const int smem = warps * NT * 32 * 4 * static_cast<int>(sizeof(float));
+  auto kernel = gemm_bf16_stream_kernel<NT>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  kernel<<<(N + 15) / 16, warps * 32, smem, stream>>>(static_cast<const __nv_bfloat16*>(X),
+                                                       static_cast<const __nv_bfloat16*>(W), out, M, N,
+                                                       K, mode);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+// Shapes this kernel takes: at most 64 rows, K a multiple of 8, 16-byte aligned operands.
+LRM_API int lrm_gemm_bf16_stream_supports(int M, int N, int K) {
+  return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 ? 1 : 0;
+}
+
+LRM_API int lrm_gemm_bf16_stream(const void* X, const void* W, void* out, int M, int N, int K,
+                                 int mode, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!lrm_gemm_bf16_stream_supports(M, N, K)) return LRM_UNSUPPORTED;
+  if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0)) return LRM_BAD_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
+  // Enough warps that about 12 stream weights on every SM, each with one chunk in flight,
+  // but never more warps than K has chunks.
+  const int tiles = (N + 15) / 16;
+  const int chunks = (K + kChunk - 1) / kChunk;
+  int warps = 4;
+  while (warps < 16 && tiles * warps < 148 * 12 && warps * 2 <= chunks) warps *= 2;
+  while (warps > 1 && warps > chunks) warps /= 2;
+  if (M <= 8) return launch_stream<1>(X, W, out, M, N, K, mode, warps, stream);
+  if (M <= 16) return launch_stream<2>(X, W, out, M, N, K, mode, warps, stream);
+  if (M <= 32) return launch_stream<4>(X, W, out, M, N, K, mode, warps, stream);
+  return launch_stream<8>(X, W, out, M, N, K, mode, warps < 8 ? warps : 8, stream);
+}

@@ -1,8 +1,9 @@
 """Which attention kernel runs for a geometry.
 
 The row-wise kernel (csrc/attention_rowwise.cu) takes every head size up to
-512, both dtypes, and is the only attention of the float32 path; tiled
-bfloat16 kernels take over for the sizes they accept.
+512 and both dtypes, and is the only attention of the float32 path. bfloat16
+with head size 32, 64 or 128 and 64-token pages runs the tiled kernels
+(csrc/attention_tiled.cu).
 """
 from __future__ import annotations
 
@@ -13,19 +14,50 @@ import torch
 from . import library
 from .ops import _code, _done, _ptr, _stream  # noqa: PLC2701
 
+SM_COUNT = 148
+force_rowwise = False  # tests switch the tiled kernels off to compare both paths
+
+
+def _tiled(q, page_size: int) -> bool:
+    return (not force_rowwise and q.dtype == torch.bfloat16
+            and bool(library.load().lrm_attention_tiled_supports(q.shape[2], page_size)))
+
 
 def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: float, window: int) -> None:
     T, Hq, d = q.shape
     lib = library.load()
+    if _tiled(q, 64):
+        _done(lib.lrm_attention_prefill_tiled(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens),
+                                              cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
+                                              ctypes.c_float(scale), window, _stream()),
+              "attention_prefill_tiled")
+        return
     _done(lib.lrm_attention_packed_rowwise(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _code(q.dtype),
                                            _ptr(cu_seqlens), _ptr(seq_of_token), T, Hq, k.shape[1], d,
                                            ctypes.c_float(scale), window, _stream()),
           "attention_packed_rowwise")
 
 
+def decode_splits(seqs: int, kv_heads: int, group: int, max_kv_len: int, window: int) -> int:
+    """Splits of the key range so that about two CTAs per SM stream the cache."""
+    ctas = seqs * kv_heads * -(-group // 16)
+    keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
+    pages = max(1, -(-keys // 64))
+    return max(1, min(pages, -(-2 * SM_COUNT // ctas)))
+
+
 def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: int) -> None:
     B, Hq, d = q.shape
     lib = library.load()
+    if _tiled(q, kv.page_size):
+        splits = decode_splits(B, kv.kv_heads, Hq // kv.kv_heads, max_kv_len, window)
+        partials = torch.empty((B, Hq, splits * 4, d + 2), dtype=torch.float32, device=q.device)
+        _done(lib.lrm_attention_decode_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(partials), _ptr(out),
+                                             _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
+                                             _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,
+                                             ctypes.c_float(scale), window, splits, _stream()),
+              "attention_decode_tiled", launches=2)
+        return
     _done(lib.lrm_attention_paged_rowwise(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _code(q.dtype),
                                           _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                           _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,

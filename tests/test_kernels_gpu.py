@@ -91,8 +91,18 @@ def test_linear_float32_row_does_not_depend_on_the_batch(ops):
         assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w)[0], full[r])
 
 
-@pytest.mark.parametrize("M,N,K", SHAPES + [(64, 128, 2048), (5, 48, 8)])
-def test_linear_bfloat16(ops, M, N, K):
+@pytest.fixture(params=["fast kernels", "fallback kernels"])
+def kernel_choice(request, monkeypatch):
+    """Run a test once with the kernels the dispatchers pick and once with the fallbacks forced."""
+    from llama_rs_metal_b200.kernels import attention_dispatch, gemm_dispatch
+    if request.param == "fallback kernels":
+        monkeypatch.setattr(gemm_dispatch, "force_tiled", True)
+        monkeypatch.setattr(attention_dispatch, "force_rowwise", True)
+    return request.param
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES + [(64, 128, 2048), (5, 48, 8), (8, 3072, 2048), (33, 40, 1160)])
+def test_linear_bfloat16(ops, kernel_choice, M, N, K):
     x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
     want = P.linear(x.double().cpu(), w.double().cpu())
     close(ops.linear(x, w), want, 6e-3, "gemm bf16 -> bf16")
@@ -103,8 +113,8 @@ def test_linear_bfloat16(ops, M, N, K):
     close(resid, before + want, 2e-5 * math.sqrt(K), "gemm bf16 add")
 
 
-@pytest.mark.parametrize("M,I,K", [(1, 8, 16), (5, 24, 68), (70, 136, 64), (64, 512, 256)])
-def test_linear_bfloat16_silu_gate(ops, M, I, K):
+@pytest.mark.parametrize("M,I,K", [(1, 8, 16), (5, 24, 68), (70, 136, 64), (64, 512, 256), (9, 40, 1048)])
+def test_linear_bfloat16_silu_gate(ops, kernel_choice, M, I, K):
     x = rnd(M, K, dtype=torch.bfloat16)
     gate, up = rnd(I, K, dtype=torch.bfloat16, seed=1), rnd(I, K, dtype=torch.bfloat16, seed=2)
     fused = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
@@ -207,9 +217,9 @@ def plain_packed(q, k, v, cu, window=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (6, 6, 80), (8, 2, 128)])
+@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (6, 6, 80), (8, 2, 128), (3, 1, 32), (10, 5, 64)])
 @pytest.mark.parametrize("window", [None, 5, 64])
-def test_attention_prefill(ops, dtype, Hq, Hk, d, window):
+def test_attention_prefill(ops, kernel_choice, dtype, Hq, Hk, d, window):
     lengths = [1, 9, 70, 33, 130]
     q, k, v, cu, seq_of = packed_case(lengths, Hq, Hk, d, dtype)
     got = ops.attention_prefill(q, k, v, i32(cu), i32(seq_of), max(lengths), d ** -0.5, window)
@@ -217,7 +227,7 @@ def test_attention_prefill(ops, dtype, Hq, Hk, d, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_prefill_finds_one_far_key_among_hundreds(ops, dtype):
+def test_attention_prefill_finds_one_far_key_among_hundreds(ops, kernel_choice, dtype):
     # One key far back is scaled so that its score stands out: the output must be its value.
     lengths = [300, 257]
     q, k, v, cu, seq_of = packed_case(lengths, 4, 2, 32, dtype, seed=9)
@@ -273,9 +283,9 @@ def plain_decode(q, ks, vs, window=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (8, 2, 128), (32, 8, 64)])
+@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (8, 2, 128), (32, 8, 64), (3, 1, 32), (40, 2, 64)])
 @pytest.mark.parametrize("window", [None, 64, 100])
-def test_attention_decode_over_poisoned_pages(ops, dtype, Hq, Hk, d, window):
+def test_attention_decode_over_poisoned_pages(ops, kernel_choice, dtype, Hq, Hk, d, window):
     lengths = [1, 64, 65, 300, 129, 1000]
     q, view, slots, ks, vs = paged_case(ops, lengths, Hq, Hk, d, dtype)
     got = ops.attention_decode(q, view, i32(slots), i32(lengths), max(lengths), d ** -0.5, window)
@@ -283,7 +293,7 @@ def test_attention_decode_over_poisoned_pages(ops, dtype, Hq, Hk, d, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_decode_window_edge(ops, dtype):
+def test_attention_decode_window_edge(ops, kernel_choice, dtype):
     # The key just outside the window would win every score; the key just inside must still count.
     lengths, window = [200, 131], 64
     q, view, slots, ks, vs = paged_case(ops, lengths, 4, 2, 32, dtype, seed=3)
@@ -363,3 +373,19 @@ def test_gumbel_sampling_follows_the_distribution(ops):
     keys = torch.arange(n, dtype=torch.int64, device=DEV)
     counts = torch.bincount(ops.sample_gumbel_rows(logits, 0.7, 1, keys).long().cpu(), minlength=4) / n
     assert torch.allclose(counts, probs, atol=0.015)
+
+
+def test_decode_attention_never_lets_stale_nan_rows_through(ops):
+    # Rows of a page beyond a sequence's length may hold anything, NaN bit patterns included.
+    lengths = [70, 3, 129]
+    q, view, slots, ks, vs = paged_case(ops, lengths, 8, 2, 64, torch.bfloat16, poison=float("nan"), seed=11)
+    got = ops.attention_decode(q, view, i32(slots), i32(lengths), max(lengths), 0.125)
+    close(got, plain_decode(q, ks, vs), TOL[torch.bfloat16], "decode over NaN-poisoned pages")
+
+
+@pytest.mark.parametrize("lengths", [[4096], [1, 2, 3, 4, 5, 6], [700] * 6])
+def test_decode_attention_split_counts(ops, lengths):
+    q, view, slots, ks, vs = paged_case(ops, lengths, 8, 2, 64, torch.bfloat16, seed=13)
+    for bucket in (max(lengths), 8192):     # the launch may be sized for longer sequences than are live
+        got = ops.attention_decode(q, view, i32(slots), i32(lengths), bucket, 0.125)
+        close(got, plain_decode(q, ks, vs), TOL[torch.bfloat16], f"bucket {bucket}")
