@@ -1,0 +1,341 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//   D[M,N] = X[M,K] . W[N,K]^T, float32 accumulation in tensor memory.
+//
+// One CTA computes a 128 x BN tile. Operand tiles (128 x 64 of X, BN x 64 of W,
+// 128-byte swizzle) are brought into a ring of shared-memory stages by TMA
+// (cp.async.bulk.tensor) issued by one thread; one other thread issues
+// tcgen05.mma (M 128, N = BN, K 16) from shared-memory descriptors into a TMEM
+// accumulator of BN columns; tcgen05.commit signals both "stage free" to the
+// loader and "accumulator ready" to the epilogue. All four warps then read
+// their 32 TMEM lanes (tcgen05.ld, one row per thread) and apply the epilogue:
+//   0 store bfloat16, 1 store float32, 2 add into float32 in place (residual
+//   stream), 3 SiLU gate over alternating blocks of 8 gate / 8 up columns.
+// Rows and columns beyond M, N, K are zero-filled by TMA and skipped on store,
+// so any M, N and any K that is a multiple of 8 is accepted.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the thread
+// records where it gave up in `status` and the CTA winds down (waiting, again
+// bounded, for its own copies in flight, then freeing its tensor memory).
+// No cluster multicast is used anywhere.
+// (Reference role: the tiled simdgroup GEMM,
+// crates/metal-backend/src/shaders/matrix.metal:236-282.)
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait. Returns false (and records `where`) if the barrier never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (status != nullptr) atomicCAS(status, 0, where);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)),
+               "r"(columns));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// K-major operand tile in shared memory, 128-byte swizzle: rows are 128 bytes apart, groups
+// of 8 rows 1024 bytes apart. Fields: start address >> 4 | leading offset (1) << 16 |
+// stride offset (1024 >> 4) << 32 | version 1 << 46 | SWIZZLE_128B (2) << 61.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+         (2ull << 61);
+}
+__device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
+      "%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// status codes (where a wait gave up)
+enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain = 4 };
+
+template <int BN, int STAGES>
+__global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
+    const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+    void* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ status) {
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // operand ring first (1024-byte aligned for the swizzle), then barriers
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* accum_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_full + 1);
+  int* bail = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(accum_full, 1);
+    *bail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---- loader: one thread feeds the ring with TMA
+    int issued = 0;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % STAGES;
+      const uint32_t round = kb / STAGES;
+      if (round > 0 && !mbar_wait(empty + s, (round - 1) & 1, status, kStuckEmpty)) {
+        *bail = 1;
+        break;
+      }
+      mbar_expect_tx(full + s, STAGE_BYTES);
+      tma_load_2d(tiles + s * STAGE_BYTES, &map_x, full + s, kb * BK, m0);
+      tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, full + s, kb * BK, n0);
+      issued = kb + 1;
+    }
+    if (*bail) {
+      // wait (bounded) for the copies already in flight before the CTA may exit
+      for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
+        mbar_wait(full + kb % STAGES, (kb / STAGES) & 1, status, kStuckDrain);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- issuer: one thread drives the tensor core
+    // instruction descriptor: D float32 (1 << 4), A and B bfloat16 (1 << 7, 1 << 10), both
+    // K-major, N >> 3 at bit 17, M >> 4 at bit 24
+    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                               (static_cast<uint32_t>(BM >> 4) << 24);
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % STAGES;
+      ok = mbar_wait(full + s, (kb / STAGES) & 1, status, kStuckFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a = smem_u32(tiles + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        umma_bf16(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                  (kb > 0 || k > 0) ? 1u : 0u);
+      umma_commit(empty + s);  // arrives when these MMAs have finished reading the stage
+    }
+    if (!ok) *bail = 1;
+    umma_commit(accum_full);  // arrives when every MMA issued so far has completed
+  }
+
+  // ---- epilogue: all four warps, one accumulator row per thread
+  __syncwarp();
+  const bool ready = mbar_wait(accum_full, 0, status, kStuckAccumulator);
+  tc_fence_after();
+  __syncthreads();
+  const bool good = ready && *bail == 0;
+  const int m = m0 + warp * 32 + lane;
+  if (good) {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      tmem_load32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c * 32, r);
+      const int n = n0 + c * 32;
+      if (m >= M || n >= N) continue;
+      const bool whole = n + 32 <= N;
+      if (mode == 3) {
+        // [8 gate | 8 up | 8 gate | 8 up] -> 16 gated values
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m) * (N >> 1) + (n >> 1);
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const int a = (i >> 3) * 16 + (i & 7);
+          const float v0 = silu_f32(__uint_as_float(r[a])) * __uint_as_float(r[a + 8]);
+          const float v1 = silu_f32(__uint_as_float(r[a + 1])) * __uint_as_float(r[a + 9]);
+          packed[i >> 1] = pack_bf16(v0, v1);
+        }
+        if (whole) {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        } else {
+          const __nv_bfloat16* vals = reinterpret_cast<const __nv_bfloat16*>(packed);
+          for (int i = 0; i < 16 && n + (i >> 3) * 16 + 8 + (i & 7) < N; ++i) dst[i] = vals[i];
+        }
+      } else if (mode == 0) {
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m) * N + n;
+        if (whole && (N & 7) == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(dst + i) = make_uint4(
+                pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+                pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+        } else {
+          for (int i = 0; i < 32 && n + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+        }
+      } else {
+        float* dst = static_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+        if (whole && (N & 3) == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                                   __uint_as_float(r[i + 3]));
+            if (mode == 2) {
+              const float4 old = *reinterpret_cast<const float4*>(dst + i);
+              v.x += old.x;
+              v.y += old.y;
+              v.z += old.z;
+              v.w += old.w;
+            }
+            *reinterpret_cast<float4*>(dst + i) = v;
+          }
+        } else {
+          for (int i = 0; i < 32 && n + i < N; ++i)
+            dst[i] = mode == 2 ? dst[i] + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, BN);
+}
+
+// ------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    looked = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// Row-major [rows, K] bfloat16 matrix, boxes of `box_rows` x 64 elements, 128-byte swizzle,
+// out-of-range elements read as zero.
+bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES>
+int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode, int* status,
+                cudaStream_t stream) {
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
+  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  auto kernel = gemm_bf16_umma_kernel<BN, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  kernel<<<grid, 128, smem, stream>>>(map_x, map_w, out, M, N, K, mode, status);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+// Shapes the tensor-core kernel takes: K a multiple of 8 (TMA needs 16-byte row pitches).
+LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
+  return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && encode_tiled() != nullptr ? 1 : 0;
+}
+
+// `status`: one int in device memory, 0 before the launch; a kernel that gave up on a wait
+// writes a nonzero code there (the result is then invalid and the caller must raise).
+LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode,
+                               int wide, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
+  if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
+  if ((M + BM - 1) / BM > 65535) return LRM_UNSUPPORTED;
+  if (wide) return launch_umma<256, 4>(X, W, out, M, N, K, mode, status, stream);
+  return launch_umma<128, 6>(X, W, out, M, N, K, mode, status, stream);
+}

@@ -1,4 +1,5 @@
-// Token choice on the device, one block per row of float32 logits.
+// Token choice on the device over rows of float32 logits, in two small stages so that a
+// long row is scanned by many blocks.
 //
 // Greedy: the largest logit, lowest id on ties; a row with any non-finite
 // logit yields -1 (reference: crates/metal-backend/src/shaders/sampling.metal:39-80,
@@ -28,25 +29,31 @@ struct Best {
   int id;
 };
 __device__ __forceinline__ Best better(Best a, Best b) {
+  // ids < 0 mean "nothing"; a non-finite value never wins because its row is rejected anyway
   if (b.id >= 0 && (a.id < 0 || b.value > a.value || (b.value == a.value && b.id < a.id))) return b;
   return a;
 }
 
+// Stage 1: block (row, piece) scans its piece of the row and leaves its best (value, id) and
+// whether it saw a non-finite logit. Stage 2: one block per row reduces the pieces.
+// Ties always go to the lower id, so the result does not depend on how a row is cut.
 template <bool GUMBEL>
-__global__ void pick_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab,
-                                 float inv_temperature, uint64_t seed,
-                                 const long long* __restrict__ keys) {
+__global__ void pick_pieces_kernel(const float* __restrict__ logits, float* __restrict__ piece_value,
+                                   int* __restrict__ piece_id, int vocab, int piece,
+                                   float inv_temperature, uint64_t seed,
+                                   const long long* __restrict__ keys) {
   __shared__ float s_value[32];
   __shared__ int s_id[32];
   __shared__ int s_bad;
-  const int row = blockIdx.x;
+  const int row = blockIdx.y;
   const float* x = logits + static_cast<size_t>(row) * vocab;
   const uint64_t key = GUMBEL ? static_cast<uint64_t>(keys[row]) : 0ull;
   if (threadIdx.x == 0) s_bad = 0;
   __syncthreads();
   Best best{-INFINITY, -1};
   bool bad = false;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  const int begin = blockIdx.x * piece, end = min(vocab, begin + piece);
+  for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
     float v = x[i];
     bad |= !isfinite(v);
     if (GUMBEL) {
@@ -70,27 +77,69 @@ __global__ void pick_rows_kernel(const float* __restrict__ logits, int* __restri
   if (threadIdx.x == 0) {
     Best total{-INFINITY, -1};
     for (int w = 0; w < (blockDim.x + 31) / 32; ++w) total = better(total, Best{s_value[w], s_id[w]});
-    out[row] = s_bad ? -1 : total.id;
+    const size_t o = static_cast<size_t>(row) * gridDim.x + blockIdx.x;
+    piece_value[o] = total.value;
+    piece_id[o] = s_bad ? -2 : total.id;  // -2: this piece saw a non-finite logit
   }
 }
 
-LRM_API int lrm_argmax_rows(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
-  if (rows <= 0) return 0;
-  if (vocab <= 0) return LRM_BAD_ARGUMENT;
-  const int threads = vocab >= 4096 ? 1024 : 128;
-  pick_rows_kernel<false><<<rows, threads, 0, stream>>>(logits, out, vocab, 1.f, 0ull, nullptr);
+__global__ void pick_reduce_kernel(const float* __restrict__ piece_value,
+                                   const int* __restrict__ piece_id, int* __restrict__ out,
+                                   int pieces) {
+  const int row = blockIdx.x;
+  Best best{-INFINITY, -1};
+  bool bad = false;
+  for (int i = threadIdx.x; i < pieces; i += 32) {
+    const int id = piece_id[static_cast<size_t>(row) * pieces + i];
+    bad |= id == -2;
+    best = better(best, Best{piece_value[static_cast<size_t>(row) * pieces + i], id});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.id, o)};
+    best = better(best, other);
+  }
+  bad = __any_sync(0xffffffffu, bad);
+  if (threadIdx.x == 0) out[row] = bad ? -1 : best.id;
+}
+
+constexpr int kPiece = 4096;  // logits one stage-1 block scans
+
+// scratch: rows * pieces floats and as many ints, pieces = ceil(vocab / 4096)
+LRM_API int lrm_pick_pieces(int vocab) { return (vocab + kPiece - 1) / kPiece; }
+
+static int pick_rows(const float* logits, int* out, float* piece_value, int* piece_id, int rows,
+                     int vocab, bool gumbel, float inv_temperature, uint64_t seed,
+                     const long long* keys, cudaStream_t stream) {
+  const int pieces = lrm_pick_pieces(vocab);
+  if (rows > 65535) return LRM_UNSUPPORTED;
+  const dim3 grid(pieces, rows);
+  if (gumbel)
+    pick_pieces_kernel<true><<<grid, 256, 0, stream>>>(logits, piece_value, piece_id, vocab, kPiece,
+                                                       inv_temperature, seed, keys);
+  else
+    pick_pieces_kernel<false><<<grid, 256, 0, stream>>>(logits, piece_value, piece_id, vocab, kPiece,
+                                                        1.f, 0ull, nullptr);
+  LRM_LAUNCH_CHECK();
+  pick_reduce_kernel<<<rows, 32, 0, stream>>>(piece_value, piece_id, out, pieces);
   LRM_LAUNCH_CHECK();
   return 0;
 }
 
-LRM_API int lrm_sample_gumbel_rows(const float* logits, int* out, int rows, int vocab,
-                                   float temperature, unsigned long long seed,
+LRM_API int lrm_argmax_rows(const float* logits, int* out, float* piece_value, int* piece_id,
+                            int rows, int vocab, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || piece_value == nullptr || piece_id == nullptr) return LRM_BAD_ARGUMENT;
+  return pick_rows(logits, out, piece_value, piece_id, rows, vocab, false, 1.f, 0ull, nullptr, stream);
+}
+
+LRM_API int lrm_sample_gumbel_rows(const float* logits, int* out, float* piece_value, int* piece_id,
+                                   int rows, int vocab, float temperature, unsigned long long seed,
                                    const long long* keys, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (vocab <= 0 || !(temperature > 0.f) || keys == nullptr) return LRM_BAD_ARGUMENT;
-  const int threads = vocab >= 4096 ? 1024 : 128;
-  pick_rows_kernel<true><<<rows, threads, 0, stream>>>(logits, out, vocab, 1.0f / temperature, seed,
-                                                       keys);
-  LRM_LAUNCH_CHECK();
-  return 0;
+  if (vocab <= 0 || !(temperature > 0.f) || keys == nullptr || piece_value == nullptr ||
+      piece_id == nullptr)
+    return LRM_BAD_ARGUMENT;
+  return pick_rows(logits, out, piece_value, piece_id, rows, vocab, true, 1.0f / temperature, seed,
+                   keys, stream);
 }

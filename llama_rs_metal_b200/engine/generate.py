@@ -142,6 +142,9 @@ def _run_batch(stepper, sampler, live: List[_Live], options, stop, context, canc
             [seq.result.request for seq in active],
             [len(seq.result.tokens) for seq in active],
             [seq.result.prompt + seq.result.tokens for seq in active])
+        check = getattr(stepper, "check_device_status", None)
+        if check is not None:
+            check()  # the pick above already synchronized with the device
         if len(picked) != len(active):
             raise InvalidError("sampler returned a different number of tokens than rows")
         still = []

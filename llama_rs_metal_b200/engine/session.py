@@ -139,6 +139,9 @@ class Session:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.runner.step(entries)
 
+    def check_device_status(self) -> None:
+        self.runner.check_device_status()
+
     # -- many sequences -------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
                  stop_token_ids: Optional[Iterable[int]] = None,

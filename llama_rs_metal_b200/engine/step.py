@@ -135,6 +135,16 @@ class StepRunner:
         self.steps_run += 1
         return logits
 
+    def check_device_status(self) -> None:
+        """Raise if a kernel recorded that it gave up on a bounded wait (reads 4 bytes back,
+        so callers do it where they synchronize anyway)."""
+        from ..kernels import gemm_dispatch
+        try:
+            gemm_dispatch.check_status()
+        except Exception:
+            self.poisoned = True
+            raise
+
     # -- decode through a captured graph ---------------------------------------------
     def _decode_with_graph(self, entries: List[StepEntry], before: List[int], borrow: bool) -> torch.Tensor:
         batch = len(entries)

@@ -284,12 +284,20 @@ def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Te
 
 
 # --------------------------------------------------------------------------- sampling
+def _pick_scratch(logits: torch.Tensor):
+    pieces = _lib().lrm_pick_pieces(logits.shape[1])
+    values = torch.empty((logits.shape[0], pieces), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((logits.shape[0], pieces), dtype=torch.int32, device=logits.device)
+    return values, ids
+
+
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     """int32 [n]: largest logit per row, lowest id on ties, -1 for a row with a non-finite logit."""
     _check(logits, "logits", torch.float32, 2)
     out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _done(_lib().lrm_argmax_rows(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream()),
-          "argmax_rows")
+    values, ids = _pick_scratch(logits)
+    _done(_lib().lrm_argmax_rows(_ptr(logits), _ptr(out), _ptr(values), _ptr(ids), logits.shape[0],
+                                 logits.shape[1], _stream()), "argmax_rows", launches=2)
     return out
 
 
@@ -302,8 +310,9 @@ def sample_gumbel_rows(logits: torch.Tensor, temperature: float, seed: int, keys
     if not temperature > 0:
         raise InvalidError("sample_gumbel_rows: temperature must be positive")
     out = torch.empty((logits.shape[0],), dtype=torch.int32, device=logits.device)
-    _done(_lib().lrm_sample_gumbel_rows(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
-                                        ctypes.c_float(temperature),
+    values, ids = _pick_scratch(logits)
+    _done(_lib().lrm_sample_gumbel_rows(_ptr(logits), _ptr(out), _ptr(values), _ptr(ids), logits.shape[0],
+                                        logits.shape[1], ctypes.c_float(temperature),
                                         ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(keys),
-                                        _stream()), "sample_gumbel_rows")
+                                        _stream()), "sample_gumbel_rows", launches=2)
     return out

@@ -389,3 +389,45 @@ def test_decode_attention_split_counts(ops, lengths):
     for bucket in (max(lengths), 8192):     # the launch may be sized for longer sequences than are live
         got = ops.attention_decode(q, view, i32(slots), i32(lengths), bucket, 0.125)
         close(got, plain_decode(q, ks, vs), TOL[torch.bfloat16], f"bucket {bucket}")
+
+
+# --------------------------------------------------------------------------- TMA + tcgen05 product
+UMMA_SHAPES = [(65, 128, 64), (128, 128, 128), (129, 72, 8), (200, 300, 72), (333, 520, 1000),
+               (2048, 512, 256), (70, 16, 2048), (256, 1100, 136)]
+
+
+@pytest.mark.parametrize("width", [128, 256])
+@pytest.mark.parametrize("M,N,K", UMMA_SHAPES)
+def test_linear_bfloat16_tensor_core_tiles(ops, monkeypatch, width, M, N, K):
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    monkeypatch.setattr(gemm_dispatch, "umma_width", width)
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    want = P.linear(x.double().cpu(), w.double().cpu())
+    close(ops.linear(x, w), want, 6e-3, "umma -> bf16")
+    close(ops.linear(x, w, out_dtype=torch.float32), want, 2e-5 * math.sqrt(K), "umma -> f32")
+    resid = rnd(M, N, seed=2)
+    before = resid.double().cpu()
+    ops.linear(x, w, epilogue=ops.ADD, out=resid)
+    close(resid, before + want, 2e-5 * math.sqrt(K), "umma add")
+    gemm_dispatch.check_status()
+
+
+@pytest.mark.parametrize("width", [128, 256])
+@pytest.mark.parametrize("M,I,K", [(70, 136, 64), (300, 520, 200), (128, 8, 16)])
+def test_linear_bfloat16_tensor_core_silu_gate(ops, monkeypatch, width, M, I, K):
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    monkeypatch.setattr(gemm_dispatch, "umma_width", width)
+    x = rnd(M, K, dtype=torch.bfloat16)
+    gate, up = rnd(I, K, dtype=torch.bfloat16, seed=1), rnd(I, K, dtype=torch.bfloat16, seed=2)
+    fused = torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
+    xd = x.double().cpu()
+    want = P.silu(P.linear(xd, gate.double().cpu())) * P.linear(xd, up.double().cpu())
+    close(ops.linear(x, fused, epilogue=ops.SILU_GATE), want, 8e-3, "umma fused gate")
+    gemm_dispatch.check_status()
+
+
+def test_tensor_core_result_does_not_depend_on_the_rows_around_it(ops):
+    x, w = rnd(300, 520, dtype=torch.bfloat16), rnd(200, 520, dtype=torch.bfloat16, seed=1)
+    full = ops.linear(x, w, out_dtype=torch.float32)
+    part = ops.linear(x[100:230].contiguous(), w, out_dtype=torch.float32)
+    assert torch.equal(part, full[100:230])
