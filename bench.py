@@ -225,7 +225,7 @@ def main() -> int:
         torch.cuda.synchronize()
         done = time.perf_counter()
         first = stamps[batch - 1]           # every request's first token (the prefill's) is out
-        return batch * steps / (done - first), (7 * batch + 1) * 4, batch * 4
+        return batch * steps / (done - first), (8 * batch + 1) * 4, batch * 4
 
     def time_prefill(tokens, reps=5):
         session = model.session(context=CONTEXT, max_batch=1)

@@ -43,6 +43,7 @@ class KeyValueView:
     kv_heads: int
     head_dim: int
     window: Optional[int]
+    group: int = 0  # index of the storage group (a step's destination rows are per group)
 
 
 @dataclass
@@ -238,13 +239,28 @@ class Cache:
         for group in self.kv_groups:
             group.sync()
 
+    def destination_rows(self, slots: Sequence[int], before: Sequence[int], counts: Sequence[int]):
+        """For every key/value group, where each token of a step is stored: an int32 array over
+        the step's packed tokens, page * page_size + row in page, -1 where the group does not
+        keep that position. Call after grow()."""
+        out = []
+        for group in self.kv_groups:
+            ps = group.page_size
+            parts = []
+            for slot, start, n in zip(slots, before, counts):
+                pos = np.arange(start, start + n, dtype=np.int64)
+                pages = group.table_host[slot][pos // ps].astype(np.int64)
+                parts.append(np.where(pages >= 0, pages * ps + pos % ps, -1))
+            out.append(np.concatenate(parts).astype(np.int32) if parts else np.zeros(0, np.int32))
+        return out
+
     # -- views ---------------------------------------------------------------------
     def view(self, entry: int):
         kind, index = self._where.get(entry, (None, None))
         if kind == "kv":
             g = self.kv_groups[index]
             return KeyValueView(g.k[entry], g.v[entry], g.table_device, g.page_size,
-                                g.request.kv_heads, g.request.head_dim, g.request.window)
+                                g.request.kv_heads, g.request.head_dim, g.request.window, index)
         if kind == "state":
             return StateView(self.state_groups[index].state[entry])
         return None

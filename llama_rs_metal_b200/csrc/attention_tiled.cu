@@ -8,7 +8,9 @@
 //    One CTA = (sequence, kv head, split); its 4 warps each take 16 keys of
 //    every 64-key page, so K/V are read once for all query heads of the group.
 //    Each warp leaves an unnormalised partial (acc, max, mass); a second kernel
-//    merges the partials: out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M).
+//    merges the partials in part order: out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M).
+//    (Merging in the last CTA to arrive, found with a global counter, was tried and
+//    was slower than the separate launch: its serial tail costs more than a launch.)
 //    (reference: crates/metal-backend/src/shaders/attention.metal:61-121 splits
 //    the context the same way, one SIMD group per chunk.)
 //
@@ -179,6 +181,8 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
   __nv_bfloat16* Vs = Ks + 2 * TILE;
 
+  pdl_trigger();
+  pdl_wait();
   const int qt = gridDim.x - 1 - blockIdx.x;  // long rows of work first
   const int h = blockIdx.y, b = blockIdx.z;
   const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
@@ -267,6 +271,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Vs = Ks + 2 * TILE;
+  pdl_trigger();
+  pdl_wait();  // q and the newest key/value row come from the kernel before this one
 
   const int rg = blockIdx.x % row_groups;
   const int kh = (blockIdx.x / row_groups) % kv_heads;
@@ -349,23 +355,43 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
       dst[D + 1] = total;
     }
   }
+
 }
 
 // out[b, head, :] = sum_i acc_i 2^(m_i - M) / sum_i l_i 2^(m_i - M); one block per (b, head).
+// Branch-free and in chunks of 8 parts, so that a chunk's loads are all in flight together.
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ partials,
                                        __nv_bfloat16* __restrict__ out, int n_parts) {
+  pdl_trigger();
+  pdl_wait();
   const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (D + 2);
-  float M = -INFINITY;
-  for (int i = 0; i < n_parts; ++i) M = fmaxf(M, src[i * (D + 2) + D]);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float M = -INFINITY;
+    for (int i0 = 0; i0 < n_parts; i0 += 8) {
+      float mi[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) mi[u] = i0 + u < n_parts ? src[(i0 + u) * (D + 2) + D] : -INFINITY;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) M = fmaxf(M, mi[u]);
+    }
     float acc = 0.f, mass = 0.f;
-    for (int i = 0; i < n_parts; ++i) {
-      const float mi = src[i * (D + 2) + D];
-      if (mi == -INFINITY) continue;  // a part that saw no key
-      const float w = exp2f(mi - M);
-      acc = fmaf(src[i * (D + 2) + d], w, acc);
-      mass = fmaf(src[i * (D + 2) + D + 1], w, mass);
+    for (int i0 = 0; i0 < n_parts; i0 += 8) {
+      float mi[8], ai[8], li[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = i0 + u < n_parts;
+        const float* part_src = src + (in ? i0 + u : 0) * (D + 2);
+        mi[u] = in ? part_src[D] : -INFINITY;
+        ai[u] = part_src[d];
+        li[u] = part_src[D + 1];
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {  // a part that saw no key has max -inf and weight 0
+        const float w = mi[u] == -INFINITY ? 0.f : exp2f(mi[u] - M);
+        acc = fmaf(ai[u], w, acc);
+        mass = fmaf(li[u], w, mass);
+      }
     }
     out[static_cast<size_t>(blockIdx.x) * D + d] = __float2bfloat16_rn(acc / mass);
   }
@@ -379,11 +405,10 @@ template <int D> int prefill_launch(const void* q, const void* k, const void* v,
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
   const dim3 grid((max_seq_len + kTile - 1) / kTile, q_heads, seqs);
-  kernel<<<grid, kThreads, smem, stream>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k),
-      static_cast<const __nv_bfloat16*>(v), static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads,
-      kv_heads, scale * 1.4426950408889634f, window);
-  LRM_LAUNCH_CHECK();
+  LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
+             static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+             static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads, kv_heads,
+             scale * 1.4426950408889634f, window);
   return 0;
 }
 
@@ -398,14 +423,12 @@ template <int D> int decode_launch(const void* q, const void* k_pages, const voi
   if (e != cudaSuccess) return static_cast<int>(e);
   const int group = q_heads / kv_heads, row_groups = (group + 15) / 16;
   const dim3 grid(seqs * kv_heads * row_groups, n_splits);
-  kernel<<<grid, kThreads, smem, stream>>>(
-      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
-      static_cast<const __nv_bfloat16*>(v_pages), partials, page_table, table_stride, slots, kv_lens,
-      q_heads, kv_heads, row_groups, scale * 1.4426950408889634f, window, n_splits);
-  LRM_LAUNCH_CHECK();
-  attention_merge_kernel<D><<<seqs * q_heads, D <= 64 ? 64 : 128, 0, stream>>>(
-      partials, static_cast<__nv_bfloat16*>(out), n_splits * 4);
-  LRM_LAUNCH_CHECK();
+  LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
+             static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages),
+             partials, page_table, table_stride, slots, kv_lens, q_heads, kv_heads, row_groups,
+             scale * 1.4426950408889634f, window, n_splits);
+  LRM_LAUNCH(attention_merge_kernel<D>, seqs * q_heads, D <= 64 ? 64 : 128, 0, stream, partials,
+             static_cast<__nv_bfloat16*>(out), n_splits * 4);
   return 0;
 }
 
@@ -431,7 +454,8 @@ LRM_API int lrm_attention_prefill_tiled(const void* q, const void* k, const void
   }
 }
 
-// `partials` is scratch: seqs * q_heads * n_splits * 4 * (d + 2) floats.
+// Scratch: `partials`, seqs * q_heads * n_splits * 4 * (d + 2) floats (contents do not matter).
+// Launches that share scratch must not overlap on the GPU.
 LRM_API int lrm_attention_decode_tiled(const void* q, const void* k_pages, const void* v_pages,
                                        float* partials, void* out, const int* page_table,
                                        int table_stride, const int* slots, const int* kv_lens,

@@ -20,6 +20,40 @@ enum : int { LRM_BAD_ARGUMENT = -1, LRM_UNSUPPORTED = -2, LRM_DEVICE_STATUS = -3
     if (e__ != cudaSuccess) return static_cast<int>(e__); \
   } while (0)
 
+// --- programmatic dependent launch ------------------------------------------------------
+// Kernels of a step run back to back on one stream. With the launch attribute below a kernel
+// may be scheduled while its predecessor still runs; it then does whatever does not depend on
+// the predecessor (index arithmetic, prefetching weights) and calls pdl_wait() before it
+// reads or writes anything the predecessor touches. pdl_wait() returns once the predecessor
+// grid has completed and its writes are visible. pdl_trigger() lets the successor be
+// scheduled as soon as every CTA of this grid has called it (or exited).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_lrm_pdl;  // 1: launch with programmatic stream serialization (set by lrm_set_pdl)
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t lrm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = g_lrm_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
+#define LRM_LAUNCH(kernel, grid, block, smem, stream, ...)                                  \
+  do {                                                                                      \
+    cudaError_t e__ = lrm_launch(kernel, grid, block, smem, stream, __VA_ARGS__);           \
+    if (e__ != cudaSuccess) return static_cast<int>(e__);                                   \
+  } while (0)
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -3,9 +3,16 @@
 // ids before launch (reference: crates/metal-backend/src/shaders/matrix.metal:94-103).
 #include "common.cuh"
 
+int g_lrm_pdl = 0;
+
+// Switch programmatic dependent launch on or off for every kernel of the library.
+LRM_API void lrm_set_pdl(int enabled) { g_lrm_pdl = enabled ? 1 : 0; }
+
 template <typename W>
 __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int hidden, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -20,11 +27,11 @@ LRM_API int lrm_embed_rows(const void* table, int table_dtype, const int* ids, f
   if (hidden <= 0 || vocab <= 0) return LRM_BAD_ARGUMENT;
   const int threads = hidden >= 256 ? 256 : 64;
   if (table_dtype == LRM_F32)
-    embed_rows_kernel<float><<<tokens, threads, 0, stream>>>(
-        static_cast<const float*>(table), ids, out, hidden, vocab);
+    LRM_LAUNCH(embed_rows_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(table), ids, out,
+               hidden, vocab);
   else if (table_dtype == LRM_BF16)
-    embed_rows_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab);
+    LRM_LAUNCH(embed_rows_kernel<__nv_bfloat16>, tokens, threads, 0, stream,
+               static_cast<const __nv_bfloat16*>(table), ids, out, hidden, vocab);
   else
     return LRM_BAD_ARGUMENT;
   LRM_LAUNCH_CHECK();

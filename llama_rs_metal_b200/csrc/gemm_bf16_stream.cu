@@ -8,7 +8,7 @@
 // so the activation fragment is loaded with the same address pattern and the
 // products pair up correctly without any shuffle or shared-memory staging.
 //
-// A CTA owns 16 weight rows; its warps split K in interleaved 128-wide chunks
+// A CTA owns 16 weight rows; its warps split K in interleaved 64- or 128-wide chunks
 // (so many loads are in flight per SM) and their partial sums are added in
 // warp order through shared memory (no atomics: the result is deterministic).
 //
@@ -20,7 +20,9 @@
 
 namespace {
 
-constexpr int kChunk = 128;  // k values a warp handles per iteration
+// k values a warp handles per iteration: 64 for up to 16 activation rows (fewer registers, so
+// more warps per SM), 128 beyond
+template <int NT> struct Chunk { static constexpr int kK = NT <= 2 ? 64 : 128; };
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -44,12 +46,14 @@ __device__ __forceinline__ uint4 ldg_keep(const void* p) {  // activations: reus
 
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
 
-template <int NT>
-__global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat16* __restrict__ X,
-                                        const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
-                                        int M, int N, int K, int mode) {
-  extern __shared__ float red[];  // [warps][NT][32 lanes][4]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+// MINB: CTAs per SM the register budget must allow (a single wave for the usual sizes).
+template <int NT, int WARPS, int MINB>
+__global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
+    const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
+    int M, int N, int K, int mode) {
+  extern __shared__ float red[];  // [WARPS][NT][32 lanes][4]
+  constexpr int kChunk = Chunk<NT>::kK, kSub = kChunk / 32;  // kSub: 16-byte pieces per thread and row
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
   const int row_a = n0 + g, row_b = n0 + g + 8;
@@ -64,9 +68,9 @@ __global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
-  auto load_w = [&](int k0, uint4 (&a)[4], uint4 (&b)[4]) {
+  auto load_w = [&](int k0, uint4 (&a)[kSub], uint4 (&b)[kSub]) {
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < kSub; ++s) {
       const int k = k0 + 32 * s + 8 * t;
       const bool in = k < K;  // K is a multiple of 8: a 16-byte piece is inside or outside
       a[s] = in && ok_a ? ldg_stream(wa + k) : zero;
@@ -74,14 +78,31 @@ __global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat
     }
   };
 
-  uint4 cur_a[4], cur_b[4], nxt_a[4], nxt_b[4];
+  // Weights do not depend on the kernel before this one: start streaming them, then wait
+  // for the predecessor (which produced X and may still be writing `out`). Each warp keeps the
+  // next chunk in flight while it multiplies the current one.
+  pdl_trigger();
+  uint4 cur_a[kSub], cur_b[kSub], nxt_a[kSub], nxt_b[kSub];
   int k0 = warp * kChunk;
   if (k0 < K) load_w(k0, cur_a, cur_b);
-  for (; k0 < K; k0 += warps * kChunk) {
-    const int k_next = k0 + warps * kChunk;
+  pdl_wait();
+  // mode 2 adds into `out`: fetch the old values now so their latency hides behind the stream
+  float old[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  if (mode == 2 && threadIdx.x < NT * 32) {
+    const int j = threadIdx.x >> 5, gg = (threadIdx.x & 31) >> 2, tt = threadIdx.x & 3;
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int m = 8 * j + 2 * tt + e, n = n0 + gg + 8 * half;
+        if (m < M && n < N) old[e][half] = static_cast<const float*>(out)[static_cast<size_t>(m) * N + n];
+      }
+  }
+  while (k0 < K) {
+    const int k_next = k0 + WARPS * kChunk;
     if (k_next < K) load_w(k_next, nxt_a, nxt_b);
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < kSub; ++s) {
       const int k = k0 + 32 * s + 8 * t;
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
@@ -91,8 +112,9 @@ __global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat
         mma16816(acc[j], cur_a[s].z, cur_b[s].z, cur_a[s].w, cur_b[s].w, x.z, x.w);
       }
     }
+    k0 = k_next;
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
+    for (int s = 0; s < kSub; ++s) {
       cur_a[s] = nxt_a[s];
       cur_b[s] = nxt_b[s];
     }
@@ -104,10 +126,11 @@ __global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat
     *reinterpret_cast<float4*>(red + ((static_cast<size_t>(warp) * NT + j) * 32 + lane) * 4) =
         make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
   __syncthreads();
-  for (int item = threadIdx.x; item < NT * 32; item += blockDim.x) {
+  for (int item = threadIdx.x; item < NT * 32; item += WARPS * 32) {
     const int j = item >> 5, ln = item & 31, gg = ln >> 2, tt = ln & 3;
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int w = 0; w < warps; ++w) {
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
       const float4 v = *reinterpret_cast<const float4*>(red + ((static_cast<size_t>(w) * NT + j) * 32 + ln) * 4);
       sum.x += v.x;
       sum.y += v.y;
@@ -136,26 +159,37 @@ __global__ __launch_bounds__(512) void gemm_bf16_stream_kernel(const __nv_bfloat
         const float v = vals[e][half];
         if (mode == 0) static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
         else if (mode == 1) static_cast<float*>(out)[o] = v;
-        else static_cast<float*>(out)[o] += v;
+        else static_cast<float*>(out)[o] = (item < WARPS * 32 ? old[e][half] : static_cast<float*>(out)[o]) + v;
       }
     }
   }
 }
 
-template <int NT>
-int launch_stream(const void* X, const void* W, void* out, int M, int N, int K, int mode, int warps,
-                  cudaStream_t stream) {
-  const int smem = warps * NT * 32 * 4 * static_cast<int>(sizeof(float));
-  auto kernel = gemm_bf16_stream_kernel<NT>;
+template <int NT, int WARPS, int MINB>
+int launch_variant(const void* X, const void* W, void* out, int M, int N, int K, int mode,
+                   cudaStream_t stream) {
+  constexpr int smem = WARPS * NT * 32 * 4 * static_cast<int>(sizeof(float));
+  auto kernel = gemm_bf16_stream_kernel<NT, WARPS, MINB>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  kernel<<<(N + 15) / 16, warps * 32, smem, stream>>>(static_cast<const __nv_bfloat16*>(X),
-                                                       static_cast<const __nv_bfloat16*>(W), out, M, N,
-                                                       K, mode);
-  LRM_LAUNCH_CHECK();
+  LRM_LAUNCH(kernel, (N + 15) / 16, WARPS * 32, smem, stream, static_cast<const __nv_bfloat16*>(X),
+             static_cast<const __nv_bfloat16*>(W), out, M, N, K, mode);
   return 0;
+}
+
+// Register budgets: 64 per thread for up to 16 activation rows (32 warps resident per SM),
+// 128 beyond (the accumulators of 4 or 8 column tiles need them).
+template <int NT>
+int launch_stream(const void* X, const void* W, void* out, int M, int N, int K, int mode, int warps,
+                  cudaStream_t stream) {
+  constexpr int kWarpsPerSm = NT <= 2 ? 32 : 16;
+  if (warps >= 16) return launch_variant<NT, 16, kWarpsPerSm / 16>(X, W, out, M, N, K, mode, stream);
+  if (warps >= 8) return launch_variant<NT, 8, kWarpsPerSm / 8>(X, W, out, M, N, K, mode, stream);
+  if (warps >= 4) return launch_variant<NT, 4, kWarpsPerSm / 4>(X, W, out, M, N, K, mode, stream);
+  if (warps >= 2) return launch_variant<NT, 2, kWarpsPerSm / 2>(X, W, out, M, N, K, mode, stream);
+  return launch_variant<NT, 1, kWarpsPerSm>(X, W, out, M, N, K, mode, stream);
 }
 
 }  // namespace
@@ -174,7 +208,7 @@ LRM_API int lrm_gemm_bf16_stream(const void* X, const void* W, void* out, int M,
   // Enough warps that about 12 stream weights on every SM, each with one chunk in flight,
   // but never more warps than K has chunks.
   const int tiles = (N + 15) / 16;
-  const int chunks = (K + kChunk - 1) / kChunk;
+  const int chunks = (K + 127) / 128;
   int warps = 4;
   while (warps < 16 && tiles * warps < 148 * 12 && warps * 2 <= chunks) warps *= 2;
   while (warps > 1 && warps > chunks) warps /= 2;

@@ -3,44 +3,69 @@
 // (reference: crates/metal-backend/src/shaders/elementwise.metal:31-46).
 // The sum of squares is float32 in a fixed order; the output is float32 or
 // bfloat16. Optional fusions, all in the same pass over the row:
-//  * `rows`: normalize only the listed rows (the head runs on wanted rows);
+//  * `rows`: normalize only the listed rows (the head runs on wanted rows); a gathered
+//    row is never written back;
 //  * `partials`: `n_partials` float32 [T,h] slices that are first added, in
 //    slice order, into the residual row, which is written back (this folds a
 //    split-K projection's partial sums and the residual add into the norm).
 #include "common.cuh"
 
-template <typename W, typename O>
+// PER: elements each thread keeps in registers (hidden <= PER * blockDim.x); the row is read
+// once, the norm weight is fetched together with it so only one memory latency is exposed.
+template <typename W, typename O, int PER>
 __global__ void rms_norm_kernel(float* __restrict__ x, const W* __restrict__ w, O* __restrict__ out,
                                 const int* __restrict__ rows, const float* __restrict__ partials,
                                 int n_partials, size_t partial_stride, int hidden, float eps) {
   __shared__ float scratch[32];
+  pdl_trigger();
+  float wv[PER];
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {  // weights do not depend on the kernel before this one
+    const int i = threadIdx.x + e * blockDim.x;
+    wv[e] = i < hidden ? to_f32(w[i]) : 0.f;
+  }
+  pdl_wait();
   const int r = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[r] : r) * hidden;
   float* xr = x + src;
   O* yr = out + static_cast<size_t>(r) * hidden;
+  float xv[PER];
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = xr[i];
-    if (n_partials > 0) {
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = threadIdx.x + e * blockDim.x;
+    float v = i < hidden ? xr[i] : 0.f;
+    if (n_partials > 0 && i < hidden) {
       for (int p = 0; p < n_partials; ++p) v += partials[p * partial_stride + src + i];
-      xr[i] = v;
+      if (rows == nullptr) xr[i] = v;  // the folded sum becomes the residual stream
     }
+    xv[e] = v;
     ss = fmaf(v, v, ss);
   }
   const float total = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
-    yr[i] = from_f32<O>((xr[i] * inv) * to_f32(w[i]));
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = threadIdx.x + e * blockDim.x;
+    if (i < hidden) yr[i] = from_f32<O>((xv[e] * inv) * wv[e]);
+  }
 }
 
 template <typename W, typename O>
-static void launch_norm(float* x, const void* w, void* out, const int* rows, const float* partials,
+static int launch_norm(float* x, const void* w, void* out, const int* rows, const float* partials,
                         int n_partials, size_t partial_stride, int n_rows, int hidden, float eps,
                         cudaStream_t stream) {
-  const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32);
-  rms_norm_kernel<W, O><<<n_rows, threads, 0, stream>>>(
-      x, static_cast<const W*>(w), static_cast<O*>(out), rows, partials, n_partials, partial_stride,
-      hidden, eps);
+  // up to 8 elements per thread for rows up to 8192 long, 32 beyond
+  int threads = hidden >= 8192 ? 1024 : (hidden > 2048 ? 1024 : (hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32)));
+#define LRM_NORM_PER(PER)                                                                         \
+  return static_cast<int>(lrm_launch(rms_norm_kernel<W, O, PER>, n_rows, threads, 0, stream, x,  \
+                                     static_cast<const W*>(w), static_cast<O*>(out), rows,       \
+                                     partials, n_partials, partial_stride, hidden, eps))
+  const int per = (hidden + threads - 1) / threads;
+  if (per <= 8) LRM_NORM_PER(8);
+  if (per <= 32) LRM_NORM_PER(32);
+  return LRM_UNSUPPORTED;  // rows longer than 32768 elements
+#undef LRM_NORM_PER
 }
 
 LRM_API int lrm_rms_norm(float* x, const void* w, int w_dtype, void* out, int out_dtype,
@@ -49,15 +74,12 @@ LRM_API int lrm_rms_norm(float* x, const void* w, int w_dtype, void* out, int ou
                          cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (hidden <= 0 || !(eps > 0.f)) return LRM_BAD_ARGUMENT;
-  if (rows != nullptr && n_partials > 0) return LRM_BAD_ARGUMENT;  // a gathered row is not written back
   const size_t ps = static_cast<size_t>(partial_stride);
 #define LRM_NORM(WT, OT) launch_norm<WT, OT>(x, w, out, rows, partials, n_partials, ps, n_rows, hidden, eps, stream)
-  if (w_dtype == LRM_F32 && out_dtype == LRM_F32) LRM_NORM(float, float);
-  else if (w_dtype == LRM_F32 && out_dtype == LRM_BF16) LRM_NORM(float, __nv_bfloat16);
-  else if (w_dtype == LRM_BF16 && out_dtype == LRM_F32) LRM_NORM(__nv_bfloat16, float);
-  else if (w_dtype == LRM_BF16 && out_dtype == LRM_BF16) LRM_NORM(__nv_bfloat16, __nv_bfloat16);
-  else return LRM_BAD_ARGUMENT;
+  if (w_dtype == LRM_F32 && out_dtype == LRM_F32) return LRM_NORM(float, float);
+  if (w_dtype == LRM_F32 && out_dtype == LRM_BF16) return LRM_NORM(float, __nv_bfloat16);
+  if (w_dtype == LRM_BF16 && out_dtype == LRM_F32) return LRM_NORM(__nv_bfloat16, float);
+  if (w_dtype == LRM_BF16 && out_dtype == LRM_BF16) return LRM_NORM(__nv_bfloat16, __nv_bfloat16);
+  return LRM_BAD_ARGUMENT;
 #undef LRM_NORM
-  LRM_LAUNCH_CHECK();
-  return 0;
 }

@@ -11,32 +11,30 @@
 // With inv_freq == nullptr nothing is rotated (another position scheme ran
 // before, or none is used).
 //
-// Cache layout: pages [page][kv_head][page_size][d]; a sequence's position p
-// lives in page table[slot][p / page_size] at row p % page_size. A table entry
-// < 0 means that page is not kept (outside a windowed group's window): skipped.
+// Cache layout: pages [page][kv_head][page_size][d]. Where a token's key and
+// value go is resolved on the host from the page table: dest_rows[t] =
+// page * page_size + row in page, or < 0 when that position is not kept
+// (outside a windowed group's window), which skips the store.
 #include "common.cuh"
 
 template <typename A>
 __global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_out,
                                   A* __restrict__ k_out, A* __restrict__ v_out,
                                   A* __restrict__ k_pages, A* __restrict__ v_pages,
-                                  const int* __restrict__ page_table, int table_stride,
+                                  const int* __restrict__ dest_rows,
                                   const int* __restrict__ positions,
-                                  const int* __restrict__ seq_of_token,
-                                  const int* __restrict__ slots,
                                   const float* __restrict__ inv_freq, int rotary, int q_heads,
                                   int kv_heads, int d, int page_size) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rotary / 2, dh = d / 2;
   const size_t row = static_cast<size_t>(q_heads + 2 * kv_heads) * d;
   const A* src = qkv + static_cast<size_t>(t) * row;
-  long long page = -1;
-  if (k_pages != nullptr) {
-    const int slot = slots[seq_of_token[t]];
-    page = page_table[static_cast<size_t>(slot) * table_stride + pos / page_size];
-  }
-  const int in_page = pos % page_size;
+  const int dest = k_pages != nullptr ? dest_rows[t] : -1;
+  const long long page = dest >= 0 ? dest / page_size : -1;
+  const int in_page = dest >= 0 ? dest % page_size : 0;
   const float fpos = static_cast<float>(pos);
   // rotated heads: q heads then k heads; one work item = one (head, i < d/2)
   const int rot_items = (q_heads + kv_heads) * dh;
@@ -96,29 +94,25 @@ __global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_o
 }
 
 LRM_API int lrm_rope_store(const void* qkv, int dtype, void* q_out, void* k_out, void* v_out,
-                           void* k_pages, void* v_pages, const int* page_table, int table_stride,
-                           const int* positions, const int* seq_of_token, const int* slots,
-                           const float* inv_freq, int rotary, int tokens, int q_heads,
+                           void* k_pages, void* v_pages, const int* dest_rows,
+                           const int* positions, const float* inv_freq, int rotary, int tokens, int q_heads,
                            int kv_heads, int d, int page_size, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d <= 0 || d % 2 != 0 || rotary < 0 || rotary > d || rotary % 2 != 0 || q_heads <= 0 ||
       kv_heads < 0 || page_size <= 0)
     return LRM_BAD_ARGUMENT;
   if ((k_pages == nullptr) != (v_pages == nullptr)) return LRM_BAD_ARGUMENT;
-  if (k_pages != nullptr && (page_table == nullptr || slots == nullptr || seq_of_token == nullptr))
-    return LRM_BAD_ARGUMENT;
+  if (k_pages != nullptr && dest_rows == nullptr) return LRM_BAD_ARGUMENT;
   const int work = (q_heads + kv_heads) * d / 2;
   const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
 #define LRM_ROPE(A)                                                                              \
-  rope_store_kernel<A><<<tokens, threads, 0, stream>>>(                                          \
-      static_cast<const A*>(qkv), static_cast<A*>(q_out), static_cast<A*>(k_out),               \
-      static_cast<A*>(v_out), static_cast<A*>(k_pages), static_cast<A*>(v_pages), page_table,    \
-      table_stride, positions, seq_of_token, slots, inv_freq, rotary, q_heads, kv_heads, d,      \
-      page_size)
+  LRM_LAUNCH(rope_store_kernel<A>, tokens, threads, 0, stream, static_cast<const A*>(qkv),        \
+             static_cast<A*>(q_out), static_cast<A*>(k_out), static_cast<A*>(v_out),             \
+             static_cast<A*>(k_pages), static_cast<A*>(v_pages), dest_rows, positions, inv_freq,   \
+             rotary, q_heads, kv_heads, d, page_size)
   if (dtype == LRM_F32) LRM_ROPE(float);
   else if (dtype == LRM_BF16) LRM_ROPE(__nv_bfloat16);
   else return LRM_BAD_ARGUMENT;
 #undef LRM_ROPE
-  LRM_LAUNCH_CHECK();
   return 0;
 }

@@ -40,21 +40,26 @@ class StepContext:
     slots: torch.Tensor  # int32 [B]
     kv_lens: torch.Tensor  # int32 [B], lengths after this step
     wanted_rows: torch.Tensor  # int32 [n], packed row numbers whose logits are wanted
+    dest_rows: List[torch.Tensor] = field(default_factory=list)  # per key/value group: int32 [T]
     entry: Any = None  # the schedule entry being run
     fresh_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
 
 
-def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int]):
+def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_rows=()):
     """The step's int32 arrays in one host buffer, laid out as
-    [token ids T | positions T | sequence of token T | cu_seqlens B+1 | slots B | kv lengths B | wanted rows n]."""
+    [token ids T | positions T | sequence of token T | cu_seqlens B+1 | slots B | kv lengths B |
+     wanted rows n | destination rows T per key/value group]."""
     counts = [len(e.tokens) for e in entries]
     T, B = sum(counts), len(entries)
     n_want = sum(len(e.want) for e in entries)
-    host = np.empty(3 * T + (B + 1) + 2 * B + n_want, dtype=np.int32)
+    base = 3 * T + (B + 1) + 2 * B + n_want
+    host = np.empty(base + T * len(dest_rows), dtype=np.int32)
+    for g, rows in enumerate(dest_rows):
+        host[base + g * T:base + (g + 1) * T] = rows
     token_ids, positions, seq_of = host[:T], host[T:2 * T], host[2 * T:3 * T]
     o = 3 * T
     cu, slots, kv_lens, wanted = host[o:o + B + 1], host[o + B + 1:o + 2 * B + 1], \
-        host[o + 2 * B + 1:o + 3 * B + 1], host[o + 3 * B + 1:]
+        host[o + 2 * B + 1:o + 3 * B + 1], host[o + 3 * B + 1:base]
     at, w = 0, 0
     cu[0] = 0
     for b, (e, before) in enumerate(zip(entries, lengths_before)):
@@ -73,10 +78,12 @@ def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int]):
 
 
 def context_over(dev: torch.Tensor, runtime: Runtime, phase: str, T: int, B: int, n_want: int,
-                 max_seq_len: int, max_kv_len: int) -> StepContext:
+                 max_seq_len: int, max_kv_len: int, groups: int = 0) -> StepContext:
     """A StepContext whose arrays are slices of `dev`, a device copy of pack_host's buffer."""
     o = 3 * T
+    base = o + 3 * B + 1 + n_want
     return StepContext(
+        dest_rows=[dev[base + g * T:base + (g + 1) * T] for g in range(groups)],
         runtime=runtime, phase=phase, num_tokens=T, num_seqs=B, max_seq_len=max_seq_len,
         max_kv_len=max_kv_len,
         token_ids=dev[:T], positions=dev[T:2 * T], seq_of_token=dev[2 * T:3 * T],
@@ -85,12 +92,12 @@ def context_over(dev: torch.Tensor, runtime: Runtime, phase: str, T: int, B: int
 
 
 def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runtime: Runtime,
-              phase: str) -> StepContext:
+              phase: str, dest_rows=()) -> StepContext:
     """Build the packed int32 arrays on the host and copy them to the device in one transfer."""
-    host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, lengths_before)
+    host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, lengths_before, dest_rows)
     device = runtime.device
     if device.type == "cuda":
         dev = torch.from_numpy(host).pin_memory().to(device, non_blocking=True)
     else:
         dev = torch.from_numpy(host).to(device)
-    return context_over(dev, runtime, phase, T, B, n_want, max_seq_len, max_kv_len)
+    return context_over(dev, runtime, phase, T, B, n_want, max_seq_len, max_kv_len, len(dest_rows))

@@ -71,9 +71,10 @@ class _DecodeGraph:
     def __init__(self, runner: "StepRunner", batch: int, bucket: int):
         rt = runner.runtime
         self.batch = batch
-        self.size = 7 * batch + 1  # pack_host's layout with T = B and every row wanted
+        groups = len(runner.cache.kv_groups)
+        self.size = (7 + groups) * batch + 1  # pack_host's layout with T = B and every row wanted
         self.static = torch.zeros(self.size, dtype=torch.int32, device=rt.device)
-        self.ctx = context_over(self.static, rt, "decode", batch, batch, batch, 1, bucket)
+        self.ctx = context_over(self.static, rt, "decode", batch, batch, batch, 1, bucket, groups)
         self.pinned = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.events = [torch.cuda.Event() for _ in range(self.RING)]
         self.turn = 0
@@ -120,11 +121,12 @@ class StepRunner:
         cache.check_growth(growth)  # raises before anything changes
         cache.grow(growth)
         cache.sync()
+        dest_rows = cache.destination_rows([e.slot for e in entries], before, [len(e.tokens) for e in entries])
         try:
             if phase == "decode" and self.use_graphs:
-                logits = self._decode_with_graph(entries, before, borrow)
+                logits = self._decode_with_graph(entries, before, borrow, dest_rows)
             else:
-                ctx = pack_step(entries, before, self.runtime, phase)
+                ctx = pack_step(entries, before, self.runtime, phase, dest_rows)
                 start = ops.launch_count()
                 logits = self.model.forward(ctx, cache)
                 self.last_launches = ops.launch_count() - start
@@ -146,10 +148,11 @@ class StepRunner:
             raise
 
     # -- decode through a captured graph ---------------------------------------------
-    def _decode_with_graph(self, entries: List[StepEntry], before: List[int], borrow: bool) -> torch.Tensor:
+    def _decode_with_graph(self, entries: List[StepEntry], before: List[int], borrow: bool,
+                           dest_rows) -> torch.Tensor:
         batch = len(entries)
         all_rows = [StepEntry(e.slot, e.tokens, (0,)) for e in entries]
-        host, _, _, _, _, max_kv_len = pack_host(all_rows, before)
+        host, _, _, _, _, max_kv_len = pack_host(all_rows, before, dest_rows)
         key = (batch, length_bucket(max_kv_len))
         graph = self._graphs.get(key)
         if graph is None:

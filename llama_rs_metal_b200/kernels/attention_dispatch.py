@@ -38,12 +38,15 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
           "attention_packed_rowwise")
 
 
+CTAS_PER_SM = 2  # decode attention CTAs wanted per SM (each keeps one 64-key K/V tile in flight)
+
+
 def decode_splits(seqs: int, kv_heads: int, group: int, max_kv_len: int, window: int) -> int:
-    """Splits of the key range so that about two CTAs per SM stream the cache."""
+    """Splits of the key range so that about CTAS_PER_SM CTAs per SM stream the cache."""
     ctas = seqs * kv_heads * -(-group // 16)
     keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
     pages = max(1, -(-keys // 64))
-    return max(1, min(pages, -(-2 * SM_COUNT // ctas)))
+    return max(1, min(pages, -(-CTAS_PER_SM * SM_COUNT // ctas)))
 
 
 def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: int) -> None:

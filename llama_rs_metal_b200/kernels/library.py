@@ -146,4 +146,8 @@ def load() -> ctypes.CDLL:
                 _library = ctypes.CDLL(path)
             except OSError as exc:
                 raise KernelUnavailableError(f"cannot load {path}: {exc}") from None
+            # LRM_PDL=1 launches kernels with programmatic dependent launch (a kernel may be
+            # scheduled while its predecessor drains). Off by default: measured on B200 it made
+            # the whole decode step slower, although single kernel chains gained a little.
+            _library.lrm_set_pdl(1 if os.environ.get("LRM_PDL", "0") == "1" else 0)
         return _library

@@ -203,13 +203,13 @@ def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 # --------------------------------------------------------------------------- rope + cache store
 def rope_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
                inv_freq: Optional[torch.Tensor], rotary: int, positions: torch.Tensor,
-               seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
-               kv=None, keep_packed: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+               kv=None, dest_rows: Optional[torch.Tensor] = None,
+               keep_packed: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
     """Rotate q and k of a fused [T, (Hq+2Hk)*d] projection and store k, v.
 
     Returns (q [T,Hq,d], k [T,Hk,d] or None, v [T,Hk,d] or None); k and v are
-    returned when `keep_packed`, and written to the paged cache view `kv` when
-    one is given.
+    returned when `keep_packed`, and written to the paged cache view `kv` at
+    `dest_rows` (int32 [T]: page * page_size + row, < 0 = not stored) when given.
     """
     _check(qkv, "qkv", dims=2)
     T = qkv.shape[0]
@@ -226,21 +226,20 @@ def rope_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
     q = torch.empty((T, q_heads, head_dim), dtype=qkv.dtype, device=dev)
     k = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
     v = torch.empty((T, kv_heads, head_dim), dtype=qkv.dtype, device=dev) if keep_packed else None
-    k_pages = v_pages = table = None
-    stride, page_size = 0, 1
+    k_pages = v_pages = None
+    page_size = 1
     if kv is not None:
-        k_pages, v_pages, table, page_size = kv.k, kv.v, kv.page_table, kv.page_size
+        k_pages, v_pages, page_size = kv.k, kv.v, kv.page_size
         _check(k_pages, "k pages", qkv.dtype, 4)
         _check(v_pages, "v pages", qkv.dtype, 4)
-        _check(table, "page table", torch.int32, 2)
-        _check(seq_of_token, "seq_of_token", torch.int32, 1)
-        _check(slots, "slots", torch.int32, 1)
+        _check(dest_rows, "dest_rows", torch.int32, 1)
+        if dest_rows.numel() != T:
+            raise InvalidError("rope_store: one destination row per token")
         if tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim):
             raise InvalidError("rope_store: cache pages do not match the head geometry")
-        stride = table.shape[1]
     _done(_lib().lrm_rope_store(_ptr(qkv), _code(qkv.dtype), _ptr(q), _ptr(k), _ptr(v),
-                                _ptr(k_pages), _ptr(v_pages), _ptr(table), stride, _ptr(positions),
-                                _ptr(seq_of_token), _ptr(slots), _ptr(inv_freq), rotary, T, q_heads,
+                                _ptr(k_pages), _ptr(v_pages), _ptr(dest_rows if kv is not None else None),
+                                _ptr(positions), _ptr(inv_freq), rotary, T, q_heads,
                                 kv_heads, head_dim, page_size, _stream()), "rope_store")
     return q, k, v
 

@@ -75,7 +75,8 @@ class Attention(Mixer):
             if self.position is not None and table is None:
                 qkv = self._apply_other_position(qkv, ctx)
             q, k, v = ops.rope_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim, inv_freq,
-                                     rotary, ctx.positions, ctx.seq_of_token, ctx.slots, kv=cache,
+                                     rotary, ctx.positions, kv=cache,
+                                     dest_rows=ctx.dest_rows[cache.group] if cache is not None else None,
                                      keep_packed=prefill)
             if prefill:
                 ctx.fresh_kv[entry.cache] = (k, v)

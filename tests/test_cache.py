@@ -149,3 +149,22 @@ def test_random_walk_keeps_the_books():
     for slot in list(live):
         cache.close_slot(slot)
     assert cache.held_pages() == [0, 0] and cache.slots.held == 0
+
+
+def test_destination_rows_follow_the_page_table_and_skip_dropped_positions():
+    cache = make(requests=(FULL, WINDOW), max_tokens=1024, max_sequence=512)
+    a, b = cache.open_slot(), cache.open_slot()
+    cache.grow([(a, 70), (b, 300)])
+    full, window = cache.destination_rows([a, b], [0, 0], [70, 300])
+    assert len(full) == len(window) == 370
+    tf = cache.kv_groups[0].table_host
+    assert full[0] == tf[a][0] * 64 and full[69] == tf[a][1] * 64 + 5
+    assert full[70 + 299] == tf[b][4] * 64 + 299 % 64
+    assert (full >= 0).all()
+    tw = cache.kv_groups[1].table_host
+    assert (window[70:70 + 192] == -1).all()              # positions 0..191 of b lie in dropped pages
+    assert window[70 + 192] == tw[b][3] * 64 and window[-1] == tw[b][4] * 64 + 299 % 64
+    cache.commit([(a, 70), (b, 300)])
+    cache.grow([(a, 71), (b, 301)])
+    full, _ = cache.destination_rows([a, b], [70, 300], [1, 1])
+    assert full.tolist() == [tf[a][1] * 64 + 6, tf[b][4] * 64 + 300 % 64]

@@ -130,11 +130,11 @@ def test_rejected_steps_change_nothing(engine, model_dirs):
 
 
 # --------------------------------------------------------------------------- parts alone
-def context_for(runtime, lengths, before=None):
+def context_for(runtime, lengths, before=None, dest_rows=()):
     from llama_rs_metal_b200.engine.batch import StepEntry, pack_step
     before = before or [0] * len(lengths)
     entries = [StepEntry(i, [0] * n, []) for i, n in enumerate(lengths)]
-    return pack_step(entries, before, runtime, "prefill" if not any(before) else "decode")
+    return pack_step(entries, before, runtime, "prefill" if not any(before) else "decode", dest_rows)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -183,6 +183,7 @@ def test_parts_alone(engine, dtype):
         cache.open_slot()
     cache.grow(list(enumerate(lengths)))
     cache.sync()
+    ctx = context_for(rt, lengths, dest_rows=cache.destination_rows([0, 1, 2], [0, 0, 0], lengths))
     ctx.entry = ScheduleEntry(0, 0)
     resid = hidden.to(DEV).clone()
     out = attn.forward(x, ctx, cache.view(0), residual=resid)

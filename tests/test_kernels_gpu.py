@@ -166,13 +166,11 @@ def test_rope_store(ops, dtype, Hq, Hk, d, R):
     T = len(positions)
     qkv = rnd(T, (Hq + 2 * Hk) * d, dtype=dtype)
     view = View(pages=90, kv_heads=Hk, page_size=64, d=d, dtype=dtype, slots=3, per_seq=80)
-    # tokens 0..4 belong to sequence 0 in slot 2, the last to sequence 1 in slot 0
-    table = view.page_table.cpu()
-    table[2, :3] = torch.tensor([7, 3, 11])
-    table[0, 4999 // 64] = 5
-    view.page_table.copy_(table)
+    # where each token's key and value go: page * 64 + row in page
+    pages = {0: (7, 0), 1: (7, 1), 2: (7, 63), 3: (3, 0), 4: (11, 2), 5: (5, 4999 % 64)}
+    dest = i32([pages[t][0] * 64 + pages[t][1] for t in range(T)])
     q, k, v = ops.rope_store(qkv, Hq, Hk, d, torch.from_numpy(inv).to(DEV), R, i32(positions),
-                             i32([0, 0, 0, 0, 0, 1]), i32([2, 0]), kv=view)
+                             kv=view, dest_rows=dest)
     x = qkv.double().cpu()
     want_q = P.rope(x[:, :Hq * d].reshape(T, Hq, d), positions, inv, R)
     want_k = P.rope(x[:, Hq * d:(Hq + Hk) * d].reshape(T, Hk, d), positions, inv, R)
@@ -181,7 +179,6 @@ def test_rope_store(ops, dtype, Hq, Hk, d, R):
     close(q, want_q, tol, "q")
     close(k, want_k, tol, "k")
     assert torch.equal(v.double().cpu(), want_v)
-    pages = {0: (7, 0), 1: (7, 1), 2: (7, 63), 3: (3, 0), 4: (11, 2), 5: (5, 4999 % 64)}
     written = torch.zeros(90, 64, dtype=torch.bool)
     for t, (page, row) in pages.items():
         assert torch.equal(view.k[page, :, row], k[t]) and torch.equal(view.v[page, :, row], v[t])
@@ -194,8 +191,8 @@ def test_rope_store(ops, dtype, Hq, Hk, d, R):
 def test_rope_store_skips_pages_a_window_dropped_and_can_leave_q_unrotated(ops):
     view = View(pages=4, kv_heads=1, page_size=64, d=16, dtype=torch.float32)
     qkv = rnd(2, 3 * 16)
-    q, k, v = ops.rope_store(qkv, 1, 1, 16, None, 0, i32([10, 70]), i32([0, 0]), i32([1]), kv=view)
-    assert torch.isnan(view.k).all()                      # both pages are -1: nothing stored
+    q, k, v = ops.rope_store(qkv, 1, 1, 16, None, 0, i32([10, 70]), kv=view, dest_rows=i32([-1, -1]))
+    assert torch.isnan(view.k).all()                      # neither position is kept: nothing stored
     assert torch.equal(q.view(2, 16), qkv[:, :16]) and torch.equal(k.view(2, 16), qkv[:, 16:32])
 
 
