@@ -7,8 +7,9 @@
 //  * decode: one query per sequence over the paged cache, split over the keys.
 //    One CTA = (sequence, kv head, split); its 4 warps each take 16 keys of
 //    every 64-key page, so K/V are read once for all query heads of the group.
-//    Each warp leaves an unnormalised partial (acc, max, mass); a second kernel
-//    merges the partials in part order: out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M).
+//    The warps' unnormalised partials (acc, max, mass) are combined in shared memory,
+//    the CTA leaves one partial per split, and a second kernel merges the splits in
+//    order: out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M).
 //    (Merging in the last CTA to arrive, found with a global counter, was tried and
 //    was slower than the separate launch: its serial tail costs more than a launch.)
 //    (reference: crates/metal-backend/src/shaders/attention.metal:61-121 splits
@@ -258,7 +259,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
 }
 
 // --------------------------------------------------------------------------- decode
-// partial layout: [sequence][q head][part][D + 2] float32, part = split * 4 + warp,
+// partial layout: [sequence][q head][split][D + 2] float32,
 // element D = running max (log2 domain), element D + 1 = mass.
 template <int D>
 __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
@@ -338,15 +339,16 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     __syncthreads();
   }
 
-  const int n_parts = n_splits * 4, part = split * 4 + warp;
+  // Combine the four warps (each saw 16 keys of every page) through shared memory, which the
+  // K/V tiles no longer need: per warp [16 rows][D + 2] floats.
+  __syncthreads();
+  float* stage = reinterpret_cast<float*>(smem_raw) + warp * 16 * (D + 2);
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     float total = l[half];
     total += __shfl_xor_sync(0xffffffffu, total, 1);
     total += __shfl_xor_sync(0xffffffffu, total, 2);
-    const int r = g + 8 * half;
-    if (r >= rows) continue;
-    float* dst = partials + ((static_cast<size_t>(b) * q_heads + head0 + r) * n_parts + part) * (D + 2);
+    float* dst = stage + (g + 8 * half) * (D + 2);
 #pragma unroll
     for (int dn = 0; dn < D / 8; ++dn)
       *reinterpret_cast<float2*>(dst + 8 * dn + 2 * t) = make_float2(o[dn][2 * half], o[dn][2 * half + 1]);
@@ -355,7 +357,27 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
       dst[D + 1] = total;
     }
   }
-
+  __syncthreads();
+  const float* all = reinterpret_cast<const float*>(smem_raw);
+  for (int item = threadIdx.x; item < rows * (D + 2); item += kThreads) {
+    const int r = item / (D + 2), c = item % (D + 2);
+    float mw[4], M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      mw[w] = all[(w * 16 + r) * (D + 2) + D];
+      M = fmaxf(M, mw[w]);
+    }
+    float value;
+    if (c == D) {
+      value = M;
+    } else {  // accumulator columns and the mass column scale alike
+      value = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w)
+        value += mw[w] == -INFINITY ? 0.f : all[(w * 16 + r) * (D + 2) + c] * exp2f(mw[w] - M);
+    }
+    partials[((static_cast<size_t>(b) * q_heads + head0 + r) * n_splits + split) * (D + 2) + c] = value;
+  }
 }
 
 // out[b, head, :] = sum_i acc_i 2^(m_i - M) / sum_i l_i 2^(m_i - M); one block per (b, head).
@@ -428,7 +450,7 @@ template <int D> int decode_launch(const void* q, const void* k_pages, const voi
              partials, page_table, table_stride, slots, kv_lens, q_heads, kv_heads, row_groups,
              scale * 1.4426950408889634f, window, n_splits);
   LRM_LAUNCH(attention_merge_kernel<D>, seqs * q_heads, D <= 64 ? 64 : 128, 0, stream, partials,
-             static_cast<__nv_bfloat16*>(out), n_splits * 4);
+             static_cast<__nv_bfloat16*>(out), n_splits);
   return 0;
 }
 
@@ -454,7 +476,7 @@ LRM_API int lrm_attention_prefill_tiled(const void* q, const void* k, const void
   }
 }
 
-// Scratch: `partials`, seqs * q_heads * n_splits * 4 * (d + 2) floats (contents do not matter).
+// Scratch: `partials`, seqs * q_heads * n_splits * (d + 2) floats (contents do not matter).
 // Launches that share scratch must not overlap on the GPU.
 LRM_API int lrm_attention_decode_tiled(const void* q, const void* k_pages, const void* v_pages,
                                        float* partials, void* out, const int* page_table,

@@ -28,6 +28,7 @@ __global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_o
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
+  const int first_item = blockIdx.y * blockDim.x, item_stride = gridDim.y * blockDim.x;
   const int pos = positions[t];
   const int half = rotary / 2, dh = d / 2;
   const size_t row = static_cast<size_t>(q_heads + 2 * kv_heads) * d;
@@ -38,7 +39,7 @@ __global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_o
   const float fpos = static_cast<float>(pos);
   // rotated heads: q heads then k heads; one work item = one (head, i < d/2)
   const int rot_items = (q_heads + kv_heads) * dh;
-  for (int item = threadIdx.x; item < rot_items; item += blockDim.x) {
+  for (int item = first_item + threadIdx.x; item < rot_items; item += item_stride) {
     const int head = item / dh, i = item % dh;
     int a, b;  // the two elements this item produces
     float ya, yb;
@@ -84,7 +85,7 @@ __global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_o
   }
   // v heads: copy
   const A* vsrc = src + static_cast<size_t>(q_heads + kv_heads) * d;
-  for (int item = threadIdx.x; item < kv_heads * d; item += blockDim.x) {
+  for (int item = first_item + threadIdx.x; item < kv_heads * d; item += item_stride) {
     const int kh = item / d, j = item % d;
     const A val = vsrc[item];
     if (v_out != nullptr) v_out[(static_cast<size_t>(t) * kv_heads + kh) * d + j] = val;
@@ -103,10 +104,12 @@ LRM_API int lrm_rope_store(const void* qkv, int dtype, void* q_out, void* k_out,
     return LRM_BAD_ARGUMENT;
   if ((k_pages == nullptr) != (v_pages == nullptr)) return LRM_BAD_ARGUMENT;
   if (k_pages != nullptr && dest_rows == nullptr) return LRM_BAD_ARGUMENT;
-  const int work = (q_heads + kv_heads) * d / 2;
-  const int threads = work >= 1024 ? 256 : (work >= 256 ? 128 : 64);
+  // one thread per (head, pair): every load of a token is in flight at once
+  const int work = max((q_heads + kv_heads) * d / 2, kv_heads * d);
+  const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+  const dim3 grid(tokens, min(64, (work + threads - 1) / threads));
 #define LRM_ROPE(A)                                                                              \
-  LRM_LAUNCH(rope_store_kernel<A>, tokens, threads, 0, stream, static_cast<const A*>(qkv),        \
+  LRM_LAUNCH(rope_store_kernel<A>, grid, threads, 0, stream, static_cast<const A*>(qkv),          \
              static_cast<A*>(q_out), static_cast<A*>(k_out), static_cast<A*>(v_out),             \
              static_cast<A*>(k_pages), static_cast<A*>(v_pages), dest_rows, positions, inv_freq,   \
              rotary, q_heads, kv_heads, d, page_size)

@@ -38,7 +38,7 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
           "attention_packed_rowwise")
 
 
-CTAS_PER_SM = 2  # decode attention CTAs wanted per SM (each keeps one 64-key K/V tile in flight)
+CTAS_PER_SM = 4  # decode attention CTAs wanted per SM (each keeps one 64-key K/V tile in flight)
 
 
 def decode_splits(seqs: int, kv_heads: int, group: int, max_kv_len: int, window: int) -> int:
@@ -54,7 +54,7 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
     lib = library.load()
     if _tiled(q, kv.page_size):
         splits = decode_splits(B, kv.kv_heads, Hq // kv.kv_heads, max_kv_len, window)
-        partials = torch.empty((B, Hq, splits * 4, d + 2), dtype=torch.float32, device=q.device)
+        partials = torch.empty((B, Hq, splits, d + 2), dtype=torch.float32, device=q.device)
         _done(lib.lrm_attention_decode_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(partials), _ptr(out),
                                              _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                              _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,
