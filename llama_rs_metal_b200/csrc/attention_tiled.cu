@@ -495,3 +495,73 @@ LRM_API int lrm_attention_decode_tiled(const void* q, const void* k_pages, const
     default: return LRM_UNSUPPORTED;
   }
 }
+
+// --------------------------------------------------------------------------- no-allocation variant
+// See attention_static_scratch.h: the same decode attention with its partials in a static
+// device array, for callers that cannot allocate. No counterpart in the reference.
+#include "attention_static_scratch.h"
+
+#include <mutex>
+
+namespace {
+constexpr int kStaticScratchFloats = 1 << 20;  // 4 MiB per device that loads the library
+constexpr int kMaxDevices = 64;
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_static_partials[kStaticScratchFloats];
+float* g_static_partials_address[kMaxDevices] = {};
+std::mutex g_static_partials_mutex;
+
+// Device address of the array on the current device; looked up once per device.
+int static_partials(float** address) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (device < 0 || device >= kMaxDevices) return LRM_UNSUPPORTED;
+  std::lock_guard<std::mutex> guard(g_static_partials_mutex);
+  if (g_static_partials_address[device] == nullptr) {
+    void* found = nullptr;
+    e = cudaGetSymbolAddress(&found, g_static_partials);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (found == nullptr) return LRM_UNSUPPORTED;
+    g_static_partials_address[device] = static_cast<float*>(found);
+  }
+  *address = g_static_partials_address[device];
+  return 0;
+}
+}  // namespace
+
+LRM_API int lrm_attention_static_scratch_floats(void) { return kStaticScratchFloats; }
+
+LRM_API int lrm_attention_decode_tiled_static_scratch(const void* q, const void* k_pages,
+                                                      const void* v_pages, void* out,
+                                                      const int* page_table, int table_stride,
+                                                      const int* slots, const int* kv_lens, int seqs,
+                                                      int q_heads, int kv_heads, int head_dim,
+                                                      int page_size, float scale, int window,
+                                                      int n_splits, cudaStream_t stream) {
+  if (seqs <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || n_splits <= 0) return LRM_BAD_ARGUMENT;
+  const long long needed =
+      static_cast<long long>(seqs) * q_heads * n_splits * (static_cast<long long>(head_dim) + 2);
+  if (needed > kStaticScratchFloats) return LRM_SCRATCH_EXCEEDED;
+  float* partials = nullptr;
+  const int status = static_partials(&partials);
+  if (status != 0) return status;
+  // Every (sequence, head, split) partial is written by the first kernel before the second
+  // reads it, so nothing in the array needs clearing between calls.
+  return lrm_attention_decode_tiled(q, k_pages, v_pages, partials, out, page_table, table_stride,
+                                    slots, kv_lens, seqs, q_heads, kv_heads, head_dim, page_size,
+                                    scale, window, n_splits, stream);
+}
+
+LRM_API const char* lrm_attention_static_scratch_error(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case LRM_SCRATCH_EXCEEDED:
+      return "seqs * q_heads * n_splits * (head_dim + 2) floats of partials do not fit the 4 MiB static "
+             "scratch: use fewer splits or a smaller batch";
+    case LRM_BAD_ARGUMENT: return "bad argument";
+    case LRM_UNSUPPORTED: return "head size, page size or device not supported by the tiled decode kernel";
+    default: return "CUDA error (the code is a cudaError_t)";
+  }
+}
