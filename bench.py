@@ -132,6 +132,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=FULL_LAYERS,
                         help="fewer layers than the configuration's 16 (named in config when used)")
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill extras")
+    parser.add_argument("--only", choices=["prefill"], default=None,
+                        help="run just this part (a small case for profiling); prints a shorter line")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -243,6 +245,13 @@ def main() -> int:
                 times.append(begin.elapsed_time(end))
         return statistics.median(times)
 
+    if args.only == "prefill":
+        ms = time_prefill(PREFILL_TOKENS, reps=max(1, args.steps))
+        flops = prefill_flops(config, args.layers, PREFILL_TOKENS)
+        print(json.dumps({"metric": "prefill tok/s, one 2048-token prompt", "value": round(PREFILL_TOKENS / (ms * 1e-3), 1),
+                          "unit": "tok/s", "ms": round(ms, 3), "layers": args.layers,
+                          "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "peaks": peak_source}))
+        return 0
     main_run = time_decode(args.batch, args.steps, args.warmup, sample_clocks=True)
     e2e_value, h2d, d2h = time_e2e(args.batch, args.steps)
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9

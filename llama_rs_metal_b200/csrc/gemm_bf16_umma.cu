@@ -12,6 +12,9 @@
 //   stream), 3 SiLU gate over alternating blocks of 8 gate / 8 up columns.
 // Rows and columns beyond M, N, K are zero-filled by TMA and skipped on store,
 // so any M, N and any K that is a multiple of 8 is accepted.
+// With `splits` > 1 (epilogue 2 only) blockIdx.z takes a slice of K and the slices meet in
+// the float32 output through vector atomic adds: this is how a product with few rows and few
+// columns (decode at batch 17-64: O and down projections) still fills the machine.
 //
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the thread
 // records where it gave up in `status` and the CTA winds down (waiting, again
@@ -119,7 +122,7 @@ enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain
 template <int BN, int STAGES>
 __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-    void* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ status) {
+    void* __restrict__ out, int M, int N, int K, int mode, int kb_per_split, int* __restrict__ status) {
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // operand ring first (1024-byte aligned for the swizzle), then barriers
@@ -133,7 +136,9 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int num_kb = (K + BK - 1) / BK;
+  const int kb_begin = blockIdx.z * kb_per_split;
+  const int num_kb = min((K + BK - 1) / BK - kb_begin, kb_per_split);  // k blocks of this slice
+  const bool atomic = gridDim.z > 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -165,8 +170,8 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
         break;
       }
       mbar_expect_tx(full + s, STAGE_BYTES);
-      tma_load_2d(tiles + s * STAGE_BYTES, &map_x, full + s, kb * BK, m0);
-      tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, full + s, kb * BK, n0);
+      tma_load_2d(tiles + s * STAGE_BYTES, &map_x, full + s, (kb_begin + kb) * BK, m0);
+      tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, full + s, (kb_begin + kb) * BK, n0);
       issued = kb + 1;
     }
     if (*bail) {
@@ -202,7 +207,7 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
   const bool ready = mbar_wait(accum_full, 0, status, kStuckAccumulator);
   tc_fence_after();
   __syncthreads();
-  const bool good = ready && *bail == 0;
+  const bool good = ready && *bail == 0 && num_kb > 0;  // an empty slice adds nothing
   const int m = m0 + warp * 32 + lane;
   if (good) {
 #pragma unroll 1
@@ -250,6 +255,10 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
           for (int i = 0; i < 32; i += 4) {
             float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
                                    __uint_as_float(r[i + 3]));
+            if (atomic) {
+              atomicAdd(reinterpret_cast<float4*>(dst + i), v);
+              continue;
+            }
             if (mode == 2) {
               const float4 old = *reinterpret_cast<const float4*>(dst + i);
               v.x += old.x;
@@ -260,8 +269,10 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
             *reinterpret_cast<float4*>(dst + i) = v;
           }
         } else {
-          for (int i = 0; i < 32 && n + i < N; ++i)
-            dst[i] = mode == 2 ? dst[i] + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+          for (int i = 0; i < 32 && n + i < N; ++i) {
+            if (atomic) atomicAdd(dst + i, __uint_as_float(r[i]));
+            else dst[i] = mode == 2 ? dst[i] + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+          }
         }
       }
     }
@@ -306,16 +317,18 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows)
 }
 
 template <int BN, int STAGES>
-int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode, int* status,
-                cudaStream_t stream) {
+int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode, int splits,
+                int* status, cudaStream_t stream) {
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
   constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   auto kernel = gemm_bf16_umma_kernel<BN, STAGES>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kernel<<<grid, 128, smem, stream>>>(map_x, map_w, out, M, N, K, mode, status);
+  const int k_blocks = (K + BK - 1) / BK;
+  const int kb_per_split = (k_blocks + splits - 1) / splits;
+  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, (k_blocks + kb_per_split - 1) / kb_per_split);
+  kernel<<<grid, 128, smem, stream>>>(map_x, map_w, out, M, N, K, mode, kb_per_split, status);
   LRM_LAUNCH_CHECK();
   return 0;
 }
@@ -329,13 +342,15 @@ LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
 
 // `status`: one int in device memory, 0 before the launch; a kernel that gave up on a wait
 // writes a nonzero code there (the result is then invalid and the caller must raise).
+// `splits` > 1 cuts K into that many slices that meet by atomic adds (epilogue 2 only).
 LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode,
-                               int wide, int* status, cudaStream_t stream) {
+                               int wide, int splits, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
   if ((M + BM - 1) / BM > 65535) return LRM_UNSUPPORTED;
-  if (wide) return launch_umma<256, 4>(X, W, out, M, N, K, mode, status, stream);
-  return launch_umma<128, 6>(X, W, out, M, N, K, mode, status, stream);
+  if (splits < 1 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
+  if (wide) return launch_umma<256, 4>(X, W, out, M, N, K, mode, splits, status, stream);
+  return launch_umma<128, 6>(X, W, out, M, N, K, mode, splits, status, stream);
 }

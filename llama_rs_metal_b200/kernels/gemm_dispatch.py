@@ -1,8 +1,12 @@
 """Which bfloat16 matrix-product kernel runs for a shape.
 
-* up to 64 rows (decode): the weight-streaming kernel (csrc/gemm_bf16_stream.cu);
-* more rows (prompts): the TMA + tcgen05 kernel (csrc/gemm_bf16_umma.cu), with
-  128 x 128 or 128 x 256 tiles, whichever leaves fewer idle SMs in the last wave;
+* up to 16 rows (small decode batches): the weight-streaming kernel
+  (csrc/gemm_bf16_stream.cu); it also takes 17-64 rows when the tensor-core kernel would
+  leave most SMs idle and cannot split K (few output columns, epilogue other than "add");
+* more rows (prompts, larger decode batches): the TMA + tcgen05 kernel
+  (csrc/gemm_bf16_umma.cu), with 128 x 128 or 128 x 256 tiles, whichever leaves fewer idle
+  SMs in the last wave; with at most 64 rows and few columns it cuts K into slices that
+  meet by atomic adds in the float32 residual stream;
 * every shape the others refuse (K not a multiple of 8, unaligned views): the
   warp-level tiled kernel (csrc/gemm_bf16_mma.cu), which takes any M, N, K.
 """
@@ -54,6 +58,21 @@ def _wide(M: int, N: int) -> bool:
     return wide <= narrow
 
 
+STREAM_ROWS = 16  # up to this many rows the streaming kernel is the faster one
+force_stream = False  # tests: keep 17-64 rows on the streaming kernel
+
+
+def _few_rows_plan(M: int, N: int, K: int, mode: int):
+    """For 17-64 rows: (use the tensor-core kernel?, K slices)."""
+    tiles = -(-N // 128)
+    if tiles >= SM_COUNT // 2:
+        return True, 1
+    if mode == 2:
+        k_blocks = -(-K // 64)
+        return True, max(1, min(k_blocks, 64, -(-SM_COUNT // tiles)))
+    return False, 1
+
+
 def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int) -> None:
     """out (mode 0 bf16 store, 1 f32 store, 2 f32 add in place, 3 silu gate) = x . weight^T."""
     global _status_dirty
@@ -61,14 +80,22 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
     N = weight.shape[0]
     lib = library.load()
     aligned = x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
-    if not force_tiled and aligned and lib.lrm_gemm_bf16_stream_supports(M, N, K):
+    fast = not force_tiled and aligned
+    stream_ok = fast and lib.lrm_gemm_bf16_stream_supports(M, N, K)
+    umma_ok = fast and lib.lrm_gemm_bf16_umma_supports(M, N, K)
+    wide, splits = _wide(M, N), 1
+    if stream_ok and umma_ok and M > STREAM_ROWS and not force_stream:
+        use_umma, splits = _few_rows_plan(M, N, K, mode)
+        stream_ok = not use_umma
+        wide = False if umma_width is None else wide
+    if stream_ok:
         _done(lib.lrm_gemm_bf16_stream(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, _stream()),
               "gemm_bf16_stream")
         return
-    if not force_tiled and aligned and lib.lrm_gemm_bf16_umma_supports(M, N, K):
+    if umma_ok:
         _status_dirty = True
         _done(lib.lrm_gemm_bf16_umma(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode,
-                                     1 if _wide(M, N) else 0, _ptr(_status_word(x.device)), _stream()),
+                                     1 if wide else 0, splits, _ptr(_status_word(x.device)), _stream()),
               "gemm_bf16_umma")
         return
     _done(lib.lrm_gemm_bf16_mma(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, _stream()),

@@ -428,3 +428,20 @@ def test_tensor_core_result_does_not_depend_on_the_rows_around_it(ops):
     full = ops.linear(x, w, out_dtype=torch.float32)
     part = ops.linear(x[100:230].contiguous(), w, out_dtype=torch.float32)
     assert torch.equal(part, full[100:230])
+
+
+@pytest.mark.parametrize("M", [17, 40, 64])
+def test_linear_bfloat16_few_rows_on_the_tensor_cores_and_on_the_streaming_kernel(ops, monkeypatch, M):
+    """17 to 64 rows: wide products and split-K adds run on tcgen05, the rest streams; both must agree."""
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    x = rnd(M, 520, dtype=torch.bfloat16)
+    wide_w, small_w = rnd(128 * 80, 520, dtype=torch.bfloat16, seed=1), rnd(300, 520, dtype=torch.bfloat16, seed=2)
+    xd = x.double().cpu()
+    for forced in (False, True):
+        monkeypatch.setattr(gemm_dispatch, "force_stream", forced)
+        close(ops.linear(x, wide_w), P.linear(xd, wide_w.double().cpu()), 6e-3, f"wide, stream={forced}")
+        resid = rnd(M, 300, seed=3)
+        want = resid.double().cpu() + P.linear(xd, small_w.double().cpu())
+        ops.linear(x, small_w, epilogue=ops.ADD, out=resid)          # K cut into slices that add atomically
+        close(resid, want, 2e-5 * math.sqrt(520), f"split-K add, stream={forced}")
+    gemm_dispatch.check_status()
