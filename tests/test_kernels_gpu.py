@@ -157,7 +157,7 @@ def i32(values):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hk,d,R", [(4, 2, 16, 16), (3, 1, 48, 32), (5, 5, 80, 80)])
+@pytest.mark.parametrize("Hq,Hk,d,R", [(4, 2, 16, 16), (3, 1, 48, 32), (5, 5, 80, 80), (2, 1, 48, 24), (32, 8, 64, 64)])
 def test_rope_store(ops, dtype, Hq, Hk, d, R):
     cfg = dict(rope_theta=500000.0, rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
                high_freq_factor=4.0, original_max_position_embeddings=64))
