@@ -1,13 +1,15 @@
 // bfloat16 matrix product on the 5th-generation tensor cores:
 //   D[M,N] = X[M,K] . W[N,K]^T, float32 accumulation in tensor memory.
 //
-// One CTA computes a 128 x BN tile. Operand tiles (128 x 64 of X, BN x 64 of W,
-// 128-byte swizzle) are brought into a ring of shared-memory stages by TMA
-// (cp.async.bulk.tensor) issued by one thread; one other thread issues
-// tcgen05.mma (M 128, N = BN, K 16) from shared-memory descriptors into a TMEM
-// accumulator of BN columns; tcgen05.commit signals both "stage free" to the
-// loader and "accumulator ready" to the epilogue. All four warps then read
-// their 32 TMEM lanes (tcgen05.ld, one row per thread) and apply the epilogue:
+// A persistent kernel, one CTA per SM, each working through 128 x BN tiles.
+// Operand tiles (128 x 64 of X, BN x 64 of W, 128-byte swizzle) are brought
+// into a ring of shared-memory stages by TMA (cp.async.bulk.tensor) issued by
+// one thread; one other thread issues tcgen05.mma (M 128, N = BN, K 16) from
+// shared-memory descriptors into one of two TMEM accumulators of BN columns;
+// tcgen05.commit signals both "stage free" to the loader and "accumulator
+// ready" to the epilogue. Four epilogue warps read their 32 TMEM lanes
+// (tcgen05.ld, one row per thread) while the next tile's MMAs fill the other
+// accumulator, and apply the epilogue:
 //   0 store bfloat16, 1 store float32, 2 add into float32 in place (residual
 //   stream), 3 SiLU gate over alternating blocks of 8 gate / 8 up columns.
 // Rows and columns beyond M, N, K are zero-filled by TMA and skipped on store,
@@ -29,7 +31,7 @@
 namespace {
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -40,6 +42,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
@@ -117,12 +122,83 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // status codes (where a wait gave up)
-enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain = 4 };
+enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain = 4, kStuckTmemFree = 5 };
 
+// The epilogue of one 32-column piece of an accumulator row held in registers.
+__device__ __forceinline__ void store_piece(const uint32_t (&r)[32], void* __restrict__ out, int m, int n,
+                                            int M, int N, int mode, bool atomic) {
+  if (m >= M || n >= N) return;
+  const bool whole = n + 32 <= N;
+  if (mode == 3) {
+    // [8 gate | 8 up | 8 gate | 8 up] -> 16 gated values
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m) * (N >> 1) + (n >> 1);
+    uint32_t packed[8];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const int a = (i >> 3) * 16 + (i & 7);
+      const float v0 = silu_f32(__uint_as_float(r[a])) * __uint_as_float(r[a + 8]);
+      const float v1 = silu_f32(__uint_as_float(r[a + 1])) * __uint_as_float(r[a + 9]);
+      packed[i >> 1] = pack_bf16(v0, v1);
+    }
+    if (whole) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    } else {
+      const __nv_bfloat16* vals = reinterpret_cast<const __nv_bfloat16*>(packed);
+      for (int i = 0; i < 16 && n + (i >> 3) * 16 + 8 + (i & 7) < N; ++i) dst[i] = vals[i];
+    }
+  } else if (mode == 0) {
+    __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m) * N + n;
+    if (whole && (N & 7) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8)
+        *reinterpret_cast<uint4*>(dst + i) = make_uint4(
+            pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+            pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+            pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
+            pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+    } else {
+      for (int i = 0; i < 32 && n + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
+    }
+  } else {
+    float* dst = static_cast<float*>(out) + static_cast<size_t>(m) * N + n;
+    if (whole && (N & 3) == 0) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                               __uint_as_float(r[i + 3]));
+        if (atomic) {
+          atomicAdd(reinterpret_cast<float4*>(dst + i), v);
+          continue;
+        }
+        if (mode == 2) {
+          const float4 old = *reinterpret_cast<const float4*>(dst + i);
+          v.x += old.x;
+          v.y += old.y;
+          v.z += old.z;
+          v.w += old.w;
+        }
+        *reinterpret_cast<float4*>(dst + i) = v;
+      }
+    } else {
+      for (int i = 0; i < 32 && n + i < N; ++i) {
+        if (atomic) atomicAdd(dst + i, __uint_as_float(r[i]));
+        else dst[i] = mode == 2 ? dst[i] + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+      }
+    }
+  }
+}
+
+// Persistent: CTA b works on items b, b + gridDim.x, ...; an item is (K slice, column tile, row
+// tile) with the row tile fastest, so CTAs that run together share a tile of W in L2.
+// Warp 0: TMA loader. Warp 1: MMA issuer (and owner of the tensor memory). Warps 2-5: epilogue.
+// Two accumulators of BN columns alternate, so the epilogue of one item runs under the MMAs of
+// the next.
 template <int BN, int STAGES>
-__global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
+__global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-    void* __restrict__ out, int M, int N, int K, int mode, int kb_per_split, int* __restrict__ status) {
+    void* __restrict__ out, int M, int N, int K, int mode, int kb_per_split, int splits,
+    int* __restrict__ status) {
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // operand ring first (1024-byte aligned for the swizzle), then barriers
@@ -130,28 +206,32 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* accum_full = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_full + 1);
-  int* bail = reinterpret_cast<int*>(tmem_slot + 1);
+  uint64_t* acc_full = empty + STAGES;   // [2] accumulator written
+  uint64_t* acc_free = acc_full + 2;     // [2] accumulator read back by all four epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
+  volatile int* bail = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int kb_begin = blockIdx.z * kb_per_split;
-  const int num_kb = min((K + BK - 1) / BK - kb_begin, kb_per_split);  // k blocks of this slice
-  const bool atomic = gridDim.z > 1;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int items = m_tiles * n_tiles * splits;
+  const int k_blocks = (K + BK - 1) / BK;
+  const bool atomic = splits > 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full + s, 1);
       mbar_init(empty + s, 1);
     }
-    mbar_init(accum_full, 1);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full + a, 1);
+      mbar_init(acc_free + a, 4);
+    }
     *bail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, BN);
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -159,127 +239,101 @@ __global__ __launch_bounds__(128, 1) void gemm_bf16_umma_kernel(
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0 && lane == 0) {
-    // ---- loader: one thread feeds the ring with TMA
-    int issued = 0;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      const int s = kb % STAGES;
-      const uint32_t round = kb / STAGES;
-      if (round > 0 && !mbar_wait(empty + s, (round - 1) & 1, status, kStuckEmpty)) {
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- loader: one thread feeds the ring with TMA, straight through all items
+      uint32_t it = 0;  // k blocks issued so far by this CTA
+      for (int item = blockIdx.x; item < items && !*bail; item += gridDim.x) {
+        const int m0 = (item % m_tiles) * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
+        const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
+        const int num_kb = min(k_blocks - kb_begin, kb_per_split);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = it / STAGES;
+          if (round > 0 && !mbar_wait(empty + s, (round - 1) & 1, status, kStuckEmpty)) {
+            *bail = 1;
+            break;
+          }
+          mbar_expect_tx(full + s, STAGE_BYTES);
+          tma_load_2d(tiles + s * STAGE_BYTES, &map_x, full + s, (kb_begin + kb) * BK, m0);
+          tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, full + s, (kb_begin + kb) * BK, n0);
+        }
+      }
+      if (*bail) {
+        // wait (bounded) for the copies already in flight before the CTA may exit
+        const uint32_t first = it > STAGES ? it - STAGES : 0;
+        for (uint32_t i = first; i < it; ++i)
+          mbar_wait(full + i % STAGES, (i / STAGES) & 1, status, kStuckDrain);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- issuer: one thread drives the tensor core
+      // instruction descriptor: D float32 (1 << 4), A and B bfloat16 (1 << 7, 1 << 10), both
+      // K-major, N >> 3 at bit 17, M >> 4 at bit 24
+      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                 (static_cast<uint32_t>(BM >> 4) << 24);
+      uint32_t it = 0, local = 0;
+      for (int item = blockIdx.x; item < items && !*bail; item += gridDim.x, ++local) {
+        const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
+        const int num_kb = min(k_blocks - kb_begin, kb_per_split);
+        const uint32_t acc = local & 1, use = local >> 1;
+        // the epilogue must have emptied this accumulator (its previous use)
+        if (use > 0 && !mbar_wait(acc_free + acc, (use - 1) & 1, status, kStuckTmemFree)) {
+          *bail = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full + s, (it / STAGES) & 1, status, kStuckFull)) {
+            *bail = 1;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a = smem_u32(tiles + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty + s);  // arrives when these MMAs have finished reading the stage
+        }
+        umma_commit(acc_full + acc);  // arrives when every MMA issued so far has completed
+      }
+    }
+  } else {
+    // ---- epilogue: four warps, one accumulator row per thread; a warp may touch only the
+    // quarter of the tensor memory's lanes given by its index modulo 4
+    const int quarter = warp & 3;
+    uint32_t local = 0;
+    for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+      const int m0 = (item % m_tiles) * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
+      const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
+      const int num_kb = min(k_blocks - kb_begin, kb_per_split);
+      const uint32_t acc = local & 1, use = local >> 1;
+      if (*bail || !mbar_wait(acc_full + acc, use & 1, status, kStuckAccumulator)) {
         *bail = 1;
         break;
       }
-      mbar_expect_tx(full + s, STAGE_BYTES);
-      tma_load_2d(tiles + s * STAGE_BYTES, &map_x, full + s, (kb_begin + kb) * BK, m0);
-      tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, full + s, (kb_begin + kb) * BK, n0);
-      issued = kb + 1;
-    }
-    if (*bail) {
-      // wait (bounded) for the copies already in flight before the CTA may exit
-      for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-        mbar_wait(full + kb % STAGES, (kb / STAGES) & 1, status, kStuckDrain);
-    }
-  } else if (warp == 1 && lane == 0) {
-    // ---- issuer: one thread drives the tensor core
-    // instruction descriptor: D float32 (1 << 4), A and B bfloat16 (1 << 7, 1 << 10), both
-    // K-major, N >> 3 at bit 17, M >> 4 at bit 24
-    constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                               (static_cast<uint32_t>(BM >> 4) << 24);
-    bool ok = true;
-    for (int kb = 0; kb < num_kb && ok; ++kb) {
-      const int s = kb % STAGES;
-      ok = mbar_wait(full + s, (kb / STAGES) & 1, status, kStuckFull);
-      if (!ok) break;
       tc_fence_after();
-      const uint32_t a = smem_u32(tiles + s * STAGE_BYTES), b = a + A_BYTES;
-#pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k)
-        umma_bf16(tmem_base, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
-                  (kb > 0 || k > 0) ? 1u : 0u);
-      umma_commit(empty + s);  // arrives when these MMAs have finished reading the stage
-    }
-    if (!ok) *bail = 1;
-    umma_commit(accum_full);  // arrives when every MMA issued so far has completed
-  }
-
-  // ---- epilogue: all four warps, one accumulator row per thread
-  __syncwarp();
-  const bool ready = mbar_wait(accum_full, 0, status, kStuckAccumulator);
-  tc_fence_after();
-  __syncthreads();
-  const bool good = ready && *bail == 0 && num_kb > 0;  // an empty slice adds nothing
-  const int m = m0 + warp * 32 + lane;
-  if (good) {
+      const int m = m0 + quarter * 32 + lane;
+      if (num_kb > 0) {  // an empty slice adds nothing
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      uint32_t r[32];
-      tmem_load32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c * 32, r);
-      const int n = n0 + c * 32;
-      if (m >= M || n >= N) continue;
-      const bool whole = n + 32 <= N;
-      if (mode == 3) {
-        // [8 gate | 8 up | 8 gate | 8 up] -> 16 gated values
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m) * (N >> 1) + (n >> 1);
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const int a = (i >> 3) * 16 + (i & 7);
-          const float v0 = silu_f32(__uint_as_float(r[a])) * __uint_as_float(r[a + 8]);
-          const float v1 = silu_f32(__uint_as_float(r[a + 1])) * __uint_as_float(r[a + 9]);
-          packed[i >> 1] = pack_bf16(v0, v1);
-        }
-        if (whole) {
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4*>(dst + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        } else {
-          const __nv_bfloat16* vals = reinterpret_cast<const __nv_bfloat16*>(packed);
-          for (int i = 0; i < 16 && n + (i >> 3) * 16 + 8 + (i & 7) < N; ++i) dst[i] = vals[i];
-        }
-      } else if (mode == 0) {
-        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(m) * N + n;
-        if (whole && (N & 7) == 0) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8)
-            *reinterpret_cast<uint4*>(dst + i) = make_uint4(
-                pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
-                pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
-                pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])),
-                pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
-        } else {
-          for (int i = 0; i < 32 && n + i < N; ++i) dst[i] = __float2bfloat16_rn(__uint_as_float(r[i]));
-        }
-      } else {
-        float* dst = static_cast<float*>(out) + static_cast<size_t>(m) * N + n;
-        if (whole && (N & 3) == 0) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                                   __uint_as_float(r[i + 3]));
-            if (atomic) {
-              atomicAdd(reinterpret_cast<float4*>(dst + i), v);
-              continue;
-            }
-            if (mode == 2) {
-              const float4 old = *reinterpret_cast<const float4*>(dst + i);
-              v.x += old.x;
-              v.y += old.y;
-              v.z += old.z;
-              v.w += old.w;
-            }
-            *reinterpret_cast<float4*>(dst + i) = v;
-          }
-        } else {
-          for (int i = 0; i < 32 && n + i < N; ++i) {
-            if (atomic) atomicAdd(dst + i, __uint_as_float(r[i]));
-            else dst[i] = mode == 2 ? dst[i] + __uint_as_float(r[i]) : __uint_as_float(r[i]);
-          }
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_load32(tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
+          store_piece(r, out, m, n0 + c * 32, M, N, mode, atomic);
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_free + acc);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem_base, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 // ------------------------------------------------------------------------- host side
@@ -327,8 +381,17 @@ int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, in
   if (e != cudaSuccess) return static_cast<int>(e);
   const int k_blocks = (K + BK - 1) / BK;
   const int kb_per_split = (k_blocks + splits - 1) / splits;
-  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, (k_blocks + kb_per_split - 1) / kb_per_split);
-  kernel<<<grid, 128, smem, stream>>>(map_x, map_w, out, M, N, K, mode, kb_per_split, status);
+  const int real_splits = (k_blocks + kb_per_split - 1) / kb_per_split;
+  const long long items = static_cast<long long>((N + BN - 1) / BN) * ((M + BM - 1) / BM) * real_splits;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int grid = static_cast<int>(items < sm_count ? items : sm_count);
+  kernel<<<grid, 192, smem, stream>>>(map_x, map_w, out, M, N, K, mode, kb_per_split, real_splits, status);
   LRM_LAUNCH_CHECK();
   return 0;
 }
@@ -349,7 +412,6 @@ LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, i
   if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
-  if ((M + BM - 1) / BM > 65535) return LRM_UNSUPPORTED;
   if (splits < 1 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
   if (wide) return launch_umma<256, 4>(X, W, out, M, N, K, mode, splits, status, stream);
   return launch_umma<128, 6>(X, W, out, M, N, K, mode, splits, status, stream);
