@@ -12,6 +12,10 @@
 // (so many loads are in flight per SM) and their partial sums are added in
 // warp order through shared memory (no atomics: the result is deterministic).
 //
+// For the add epilogue blockIdx.y may cut K into slices handled by different CTAs that meet in
+// the float32 output by atomic adds: narrow products (few 16-row tiles) then still keep every
+// SM streaming.
+//
 // Epilogues: 0 store bf16, 1 store f32, 2 add into f32 in place, 3 SiLU gate
 // (rows alternate in blocks of 8 gate / 8 up rows, so a 16-row tile holds 8
 // gated pairs; out is [M, N/2] bf16).
@@ -50,16 +54,19 @@ __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)
 template <int NT, int WARPS, int MINB>
 __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
     const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
-    int M, int N, int K, int mode) {
+    int M, int N, int K_total, int mode, int k_per_split) {
   extern __shared__ float red[];  // [WARPS][NT][32 lanes][4]
   constexpr int kChunk = Chunk<NT>::kK, kSub = kChunk / 32;  // kSub: 16-byte pieces per thread and row
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
+  const int k_lo = blockIdx.y * k_per_split;              // this CTA's slice of K: [k_lo, K)
+  const int K = min(K_total, k_lo + k_per_split);
+  const bool sliced = gridDim.y > 1;
   const int row_a = n0 + g, row_b = n0 + g + 8;
   const bool ok_a = row_a < N, ok_b = row_b < N;
-  const __nv_bfloat16* wa = W + static_cast<size_t>(ok_a ? row_a : 0) * K;
-  const __nv_bfloat16* wb = W + static_cast<size_t>(ok_b ? row_b : 0) * K;
+  const __nv_bfloat16* wa = W + static_cast<size_t>(ok_a ? row_a : 0) * K_total;
+  const __nv_bfloat16* wb = W + static_cast<size_t>(ok_b ? row_b : 0) * K_total;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
   float acc[NT][4];
@@ -83,12 +90,12 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
   // next chunk in flight while it multiplies the current one.
   pdl_trigger();
   uint4 cur_a[kSub], cur_b[kSub], nxt_a[kSub], nxt_b[kSub];
-  int k0 = warp * kChunk;
+  int k0 = k_lo + warp * kChunk;
   if (k0 < K) load_w(k0, cur_a, cur_b);
   pdl_wait();
   // mode 2 adds into `out`: fetch the old values now so their latency hides behind the stream
   float old[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  if (mode == 2 && threadIdx.x < NT * 32) {
+  if (mode == 2 && !sliced && threadIdx.x < NT * 32) {
     const int j = threadIdx.x >> 5, gg = (threadIdx.x & 31) >> 2, tt = threadIdx.x & 3;
 #pragma unroll
     for (int e = 0; e < 2; ++e)
@@ -107,7 +114,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         const int m = 8 * j + g;
-        const uint4 x = (m < M && k < K) ? ldg_keep(X + static_cast<size_t>(m) * K + k) : zero;
+        const uint4 x = (m < M && k < K) ? ldg_keep(X + static_cast<size_t>(m) * K_total + k) : zero;
         mma16816(acc[j], cur_a[s].x, cur_b[s].x, cur_a[s].y, cur_b[s].y, x.x, x.y);
         mma16816(acc[j], cur_a[s].z, cur_b[s].z, cur_a[s].w, cur_b[s].w, x.z, x.w);
       }
@@ -159,6 +166,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
         const float v = vals[e][half];
         if (mode == 0) static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
         else if (mode == 1) static_cast<float*>(out)[o] = v;
+        else if (sliced) atomicAdd(static_cast<float*>(out) + o, v);
         else static_cast<float*>(out)[o] = (item < WARPS * 32 ? old[e][half] : static_cast<float*>(out)[o]) + v;
       }
     }
@@ -166,7 +174,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
 }
 
 template <int NT, int WARPS, int MINB>
-int launch_variant(const void* X, const void* W, void* out, int M, int N, int K, int mode,
+int launch_variant(const void* X, const void* W, void* out, int M, int N, int K, int mode, int splits,
                    cudaStream_t stream) {
   constexpr int smem = WARPS * NT * 32 * 4 * static_cast<int>(sizeof(float));
   auto kernel = gemm_bf16_stream_kernel<NT, WARPS, MINB>;
@@ -174,8 +182,11 @@ int launch_variant(const void* X, const void* W, void* out, int M, int N, int K,
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  LRM_LAUNCH(kernel, (N + 15) / 16, WARPS * 32, smem, stream, static_cast<const __nv_bfloat16*>(X),
-             static_cast<const __nv_bfloat16*>(W), out, M, N, K, mode);
+  constexpr int kChunk = Chunk<NT>::kK;
+  const int k_per_split = ((K + splits - 1) / splits + kChunk - 1) / kChunk * kChunk;
+  const dim3 grid((N + 15) / 16, (K + k_per_split - 1) / k_per_split);
+  LRM_LAUNCH(kernel, grid, WARPS * 32, smem, stream, static_cast<const __nv_bfloat16*>(X),
+             static_cast<const __nv_bfloat16*>(W), out, M, N, K, mode, k_per_split);
   return 0;
 }
 
@@ -183,13 +194,13 @@ int launch_variant(const void* X, const void* W, void* out, int M, int N, int K,
 // 128 beyond (the accumulators of 4 or 8 column tiles need them).
 template <int NT>
 int launch_stream(const void* X, const void* W, void* out, int M, int N, int K, int mode, int warps,
-                  cudaStream_t stream) {
+                  int splits, cudaStream_t stream) {
   constexpr int kWarpsPerSm = NT <= 2 ? 32 : 16;
-  if (warps >= 16) return launch_variant<NT, 16, kWarpsPerSm / 16>(X, W, out, M, N, K, mode, stream);
-  if (warps >= 8) return launch_variant<NT, 8, kWarpsPerSm / 8>(X, W, out, M, N, K, mode, stream);
-  if (warps >= 4) return launch_variant<NT, 4, kWarpsPerSm / 4>(X, W, out, M, N, K, mode, stream);
-  if (warps >= 2) return launch_variant<NT, 2, kWarpsPerSm / 2>(X, W, out, M, N, K, mode, stream);
-  return launch_variant<NT, 1, kWarpsPerSm>(X, W, out, M, N, K, mode, stream);
+  if (warps >= 16) return launch_variant<NT, 16, kWarpsPerSm / 16>(X, W, out, M, N, K, mode, splits, stream);
+  if (warps >= 8) return launch_variant<NT, 8, kWarpsPerSm / 8>(X, W, out, M, N, K, mode, splits, stream);
+  if (warps >= 4) return launch_variant<NT, 4, kWarpsPerSm / 4>(X, W, out, M, N, K, mode, splits, stream);
+  if (warps >= 2) return launch_variant<NT, 2, kWarpsPerSm / 2>(X, W, out, M, N, K, mode, splits, stream);
+  return launch_variant<NT, 1, kWarpsPerSm>(X, W, out, M, N, K, mode, splits, stream);
 }
 
 }  // namespace
@@ -205,15 +216,18 @@ LRM_API int lrm_gemm_bf16_stream(const void* X, const void* W, void* out, int M,
   if (!lrm_gemm_bf16_stream_supports(M, N, K)) return LRM_UNSUPPORTED;
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0)) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
-  // Enough warps that about 12 stream weights on every SM, each with one chunk in flight,
-  // but never more warps than K has chunks.
+  // The add epilogue may cut K across CTAs (slices of at least 1024) until about 28 warps per SM
+  // stream weights; then enough warps per CTA that each has at least one chunk.
   const int tiles = (N + 15) / 16;
-  const int chunks = (K + 127) / 128;
+  int splits = 1;
+  if (mode == 2)
+    while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 1024) splits *= 2;
+  const int chunks = ((K + splits - 1) / splits + 127) / 128;
   int warps = 4;
-  while (warps < 16 && tiles * warps < 148 * 12 && warps * 2 <= chunks) warps *= 2;
+  while (warps < 16 && tiles * splits * warps < 148 * 12 && warps * 2 <= chunks) warps *= 2;
   while (warps > 1 && warps > chunks) warps /= 2;
-  if (M <= 8) return launch_stream<1>(X, W, out, M, N, K, mode, warps, stream);
-  if (M <= 16) return launch_stream<2>(X, W, out, M, N, K, mode, warps, stream);
-  if (M <= 32) return launch_stream<4>(X, W, out, M, N, K, mode, warps, stream);
-  return launch_stream<8>(X, W, out, M, N, K, mode, warps < 8 ? warps : 8, stream);
+  if (M <= 8) return launch_stream<1>(X, W, out, M, N, K, mode, warps, splits, stream);
+  if (M <= 16) return launch_stream<2>(X, W, out, M, N, K, mode, warps, splits, stream);
+  if (M <= 32) return launch_stream<4>(X, W, out, M, N, K, mode, warps, splits, stream);
+  return launch_stream<8>(X, W, out, M, N, K, mode, warps < 8 ? warps : 8, splits, stream);
 }
