@@ -371,3 +371,81 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(engine, tmp_
             got[b].append(out[row:row + 1])
     for b in (0, 1):
         assert torch.allclose(torch.cat(got[b]), whole[b], rtol=1e-5, atol=1e-6)
+
+
+# --------------------------------------------------------------------------- layer order and windows as data
+def _llama_like_plan(config, window=None, schedule=None):
+    """The library's Llama plan with a window on every attention and another layer order."""
+    import dataclasses
+    from llama_rs_metal_b200.models.llama import llama_plan
+    from llama_rs_metal_b200.parts import PartSpec
+    plan = llama_plan(config)
+    layers = []
+    for layer in plan.layers:
+        params = dict(layer.mixer.params, window=window)
+        layers.append(dataclasses.replace(layer, mixer=PartSpec("attention", params, layer.mixer.prefix)))
+    return dataclasses.replace(plan, layers=tuple(layers), schedule=tuple(schedule or plan.schedule))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_attention_in_a_whole_model_matches_the_plain_implementation(engine, tmp_path, dtype):
+    """A window of 40 keys on every layer: the windowed cache group drops pages, prompts longer
+    than the window and decoding across page boundaries must still match the oracle."""
+    import json
+    from llama_rs_metal_b200.config import LlamaConfig
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.registry import register_architecture
+
+    register_architecture("WindowedLlamaForTest", LlamaConfig, lambda c: _llama_like_plan(c, window=40))
+    cfg = dict(helpers.TINY["B"]["config"], architectures=["WindowedLlamaForTest"], model_type="windowed_test")
+    folder = write_random_model(str(tmp_path), cfg, seed=5, std=0.05, norm_std=0.1)
+    plain_cfg, tensors = P.read_model(folder)
+    runner, cache, model = open_runner(engine, folder, dtype, max_tokens=1024, max_slots=3)
+    assert cache.kv_groups[0].request.window == 40
+    seqs = [helpers.random_tokens(60 + i, n, 512) for i, n in enumerate([200, 30])]
+    refs = [P.forward(plain_cfg, tensors, s, window=40).numpy() for s in seqs]
+    slots = [cache.open_slot() for _ in seqs]
+    prompts = [150, 10]
+    out = runner.step([entry(sl, s[:p]) for sl, s, p in zip(slots, seqs, prompts)])
+    helpers.assert_logits_close(out[:150].cpu(), refs[0][:150], dtype, "windowed prompt")
+    helpers.assert_logits_close(out[150:].cpu(), refs[1][:10], dtype, "windowed short prompt")
+    rows = [[], []]
+    for step in range(50):
+        live = [b for b in (0, 1) if prompts[b] + step < len(seqs[b])]
+        out = runner.step([entry(slots[b], [seqs[b][prompts[b] + step]]) for b in live])
+        for r, b in enumerate(live):
+            rows[b].append(out[r:r + 1].clone())
+    helpers.assert_logits_close(torch.cat(rows[0]).cpu(), refs[0][150:200], dtype, "windowed decoding")
+    helpers.assert_logits_close(torch.cat(rows[1]).cpu(), refs[1][10:30], dtype, "windowed decoding, short")
+    # only the pages that still hold visible positions are kept: 200 tokens, window 40 -> pages 2 and 3
+    kept = (cache.kv_groups[0].table_host[slots[0]] >= 0).nonzero()[0].tolist()
+    assert kept == [2, 3]
+
+
+def test_a_schedule_may_run_a_layer_twice_and_share_another_layers_cache(engine, tmp_path):
+    """Order of layers is data: layer 0, then layer 1 reading layer 0's keys and values, then
+    layer 0 again on a cache entry of its own. Whole prompts and token-by-token decoding must
+    agree bit for bit in float32, and the result must differ from the plain order."""
+    from llama_rs_metal_b200.config import LlamaConfig
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.parts import ScheduleEntry
+    from llama_rs_metal_b200.registry import register_architecture
+
+    order = [ScheduleEntry(0, 0), ScheduleEntry(1, 0, writes_cache=False), ScheduleEntry(0, 1)]
+    register_architecture("ReorderedLlamaForTest", LlamaConfig, lambda c: _llama_like_plan(c, schedule=order))
+    cfg = dict(helpers.TINY["A"]["config"], architectures=["ReorderedLlamaForTest"], model_type="reordered_test")
+    folder = write_random_model(str(tmp_path / "re"), cfg, seed=2, std=0.1)
+    plain_folder = write_random_model(str(tmp_path / "plain"), helpers.TINY["A"]["config"], seed=2, std=0.1)
+    runner, cache, model = open_runner(engine, folder, "float32", max_tokens=512, max_slots=2)
+    assert len(model.cache_requests()) == 2                       # two cache entries for three executed layers
+    tokens = helpers.random_tokens(9, 80, 256)
+    slot = cache.open_slot()
+    whole = runner.step([entry(slot, tokens)]).clone()
+    cache.close_slot(slot)
+    slot = cache.open_slot()
+    rows = [runner.step([entry(slot, tokens[:30])]).clone()]
+    rows += [runner.step([entry(slot, [t])]).clone() for t in tokens[30:]]
+    assert torch.equal(torch.cat(rows), whole)
+    straight, cache2, _ = open_runner(engine, plain_folder, "float32", max_tokens=512, max_slots=2)
+    other = straight.step([entry(cache2.open_slot(), tokens)])
+    assert not torch.allclose(other, whole, atol=1e-3)
