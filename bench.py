@@ -28,7 +28,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Llama 3.2 1B shape
+# The Llama 3.2 1B shape: the configuration the benchmark is quoted on
 LLAMA_1B = dict(
     architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=2048, intermediate_size=8192,
     num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
