@@ -182,7 +182,6 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
   __nv_bfloat16* Vs = Ks + 2 * TILE;
 
-  pdl_trigger();
   pdl_wait();
   const int qt = gridDim.x - 1 - blockIdx.x;  // long rows of work first
   const int h = blockIdx.y, b = blockIdx.z;
@@ -272,7 +271,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Vs = Ks + 2 * TILE;
-  pdl_trigger();
   pdl_wait();  // q and the newest key/value row come from the kernel before this one
 
   const int rg = blockIdx.x % row_groups;
@@ -339,6 +337,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     __syncthreads();
   }
 
+  pdl_trigger();  // the cache has been read: the next kernel may be scheduled during the merge
   // Combine the four warps (each saw 16 keys of every page) through shared memory, which the
   // K/V tiles no longer need: per warp [16 rows][D + 2] floats.
   __syncthreads();
@@ -385,7 +384,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
 template <int D>
 __global__ void attention_merge_kernel(const float* __restrict__ partials,
                                        __nv_bfloat16* __restrict__ out, int n_parts) {
-  pdl_trigger();
+  pdl_trigger();  // a small kernel: let the next one start (and prefetch its weights) right away
   pdl_wait();
   const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (D + 2);
   for (int d = threadIdx.x; d < D; d += blockDim.x) {

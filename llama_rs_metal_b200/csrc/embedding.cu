@@ -3,7 +3,7 @@
 // ids before launch (reference: crates/metal-backend/src/shaders/matrix.metal:94-103).
 #include "common.cuh"
 
-int g_lrm_pdl = 0;
+int g_lrm_pdl = 1;
 
 // Switch programmatic dependent launch on or off for every kernel of the library.
 LRM_API void lrm_set_pdl(int enabled) { g_lrm_pdl = enabled ? 1 : 0; }
@@ -11,7 +11,7 @@ LRM_API void lrm_set_pdl(int enabled) { g_lrm_pdl = enabled ? 1 : 0; }
 template <typename W>
 __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int hidden, int vocab) {
-  pdl_trigger();
+  pdl_trigger();  // a small kernel: let the next one start (and prefetch its weights) right away
   pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];

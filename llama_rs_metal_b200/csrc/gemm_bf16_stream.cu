@@ -88,7 +88,6 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
   // Weights do not depend on the kernel before this one: start streaming them, then wait
   // for the predecessor (which produced X and may still be writing `out`). Each warp keeps the
   // next chunk in flight while it multiplies the current one.
-  pdl_trigger();
   uint4 cur_a[kSub], cur_b[kSub], nxt_a[kSub], nxt_b[kSub];
   int k0 = k_lo + warp * kChunk;
   if (k0 < K) load_w(k0, cur_a, cur_b);
@@ -127,6 +126,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
     }
   }
 
+  pdl_trigger();  // the stream is done: the next kernel may be scheduled while the sums are added
   // add the warps' partial sums in warp order
 #pragma unroll
   for (int j = 0; j < NT; ++j)

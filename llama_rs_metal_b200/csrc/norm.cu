@@ -17,13 +17,13 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const W* __restrict__ w, 
                                 const int* __restrict__ rows, const float* __restrict__ partials,
                                 int n_partials, size_t partial_stride, int hidden, float eps) {
   __shared__ float scratch[32];
-  pdl_trigger();
   float wv[PER];
 #pragma unroll
   for (int e = 0; e < PER; ++e) {  // weights do not depend on the kernel before this one
     const int i = threadIdx.x + e * blockDim.x;
     wv[e] = i < hidden ? to_f32(w[i]) : 0.f;
   }
+  pdl_trigger();  // a small kernel: let the next one start (and prefetch its weights) right away
   pdl_wait();
   const int r = blockIdx.x;
   const size_t src = static_cast<size_t>(rows ? rows[r] : r) * hidden;

@@ -25,7 +25,7 @@ __global__ void rope_store_kernel(const A* __restrict__ qkv, A* __restrict__ q_o
                                   const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, int rotary, int q_heads,
                                   int kv_heads, int d, int page_size) {
-  pdl_trigger();
+  pdl_trigger();  // a small kernel: let the next one start right away
   pdl_wait();
   const int t = blockIdx.x;
   const int first_item = blockIdx.y * blockDim.x, item_stride = gridDim.y * blockDim.x;
@@ -109,7 +109,7 @@ __global__ void rope_store_vec_kernel(const A* __restrict__ qkv, A* __restrict__
                                       int kv_heads, int d, int page_size) {
   constexpr int VEC = 16 / sizeof(A);
   using V = Vec16<A>;
-  pdl_trigger();
+  pdl_trigger();  // a small kernel: let the next one start right away
   pdl_wait();
   const int t = blockIdx.x;
   const int half = rotary / 2;

@@ -146,8 +146,9 @@ def load() -> ctypes.CDLL:
                 _library = ctypes.CDLL(path)
             except OSError as exc:
                 raise KernelUnavailableError(f"cannot load {path}: {exc}") from None
-            # LRM_PDL=1 launches kernels with programmatic dependent launch (a kernel may be
-            # scheduled while its predecessor drains). Off by default: measured on B200 it made
-            # the whole decode step slower, although single kernel chains gained a little.
-            _library.lrm_set_pdl(1 if os.environ.get("LRM_PDL", "0") == "1" else 0)
+            # Kernels are launched with programmatic dependent launch: a kernel may be scheduled
+            # while its predecessor drains and prefetch what does not depend on it. Small kernels
+            # let their successor start at once, large ones after their main loop (letting every
+            # kernel do so at once made the whole step slower). LRM_PDL=0 switches it off.
+            _library.lrm_set_pdl(0 if os.environ.get("LRM_PDL", "1") == "0" else 1)
         return _library
