@@ -271,8 +271,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* Vs = Ks + 2 * TILE;
-  pdl_wait();  // q and the newest key/value row come from the kernel before this one
-
   const int rg = blockIdx.x % row_groups;
   const int kh = (blockIdx.x / row_groups) % kv_heads;
   const int b = blockIdx.x / (row_groups * kv_heads);
@@ -291,6 +289,21 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   const int p_end = min(page_end, p_begin + per_split);
   const int* table = page_table + static_cast<size_t>(slots[b]) * table_stride;
 
+  auto issue = [&](int page_index, int stage) {
+    const size_t page = static_cast<size_t>(table[page_index]);
+    const size_t base = (page * kv_heads + kh) * kTile * D;
+    load_tile<D>(Ks + stage * TILE, k_pages + base, D, len - page_index * kTile);
+    load_tile<D>(Vs + stage * TILE, v_pages + base, D, len - page_index * kTile);
+    cp_async_commit();
+  };
+  // Lengths, slots and the page table were set before the step; only q and the newest
+  // key/value row (in the sequence's last page) come from the kernel before this one. A first
+  // page that is not the last one can therefore be fetched before waiting for that kernel.
+  const bool early = p_begin < p_end && p_begin != page_end - 1;
+  if (early) issue(p_begin, 0);
+  pdl_wait();
+  if (!early && p_begin < p_end) issue(p_begin, 0);
+
   uint32_t qa[D / 16][4];
   load_q<D>(qa, q + (static_cast<size_t>(b) * q_heads + head0) * D, D, rows);
   float o[D / 8][4];
@@ -300,14 +313,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  auto issue = [&](int page_index, int stage) {
-    const size_t page = static_cast<size_t>(table[page_index]);
-    const size_t base = (page * kv_heads + kh) * kTile * D;
-    load_tile<D>(Ks + stage * TILE, k_pages + base, D, len - page_index * kTile);
-    load_tile<D>(Vs + stage * TILE, v_pages + base, D, len - page_index * kTile);
-    cp_async_commit();
-  };
-  if (p_begin < p_end) issue(p_begin, 0);
   for (int p = p_begin; p < p_end; ++p) {
     const int stage = (p - p_begin) & 1;
     if (p + 1 < p_end) {

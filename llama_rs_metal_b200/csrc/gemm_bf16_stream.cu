@@ -91,6 +91,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
   uint4 cur_a[kSub], cur_b[kSub], nxt_a[kSub], nxt_b[kSub];
   int k0 = k_lo + warp * kChunk;
   if (k0 < K) load_w(k0, cur_a, cur_b);
+  if (k0 + WARPS * kChunk < K) load_w(k0 + WARPS * kChunk, nxt_a, nxt_b);
   pdl_wait();
   // mode 2 adds into `out`: fetch the old values now so their latency hides behind the stream
   float old[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -104,9 +105,11 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
         if (m < M && n < N) old[e][half] = static_cast<const float*>(out)[static_cast<size_t>(m) * N + n];
       }
   }
+  bool first = true;
   while (k0 < K) {
     const int k_next = k0 + WARPS * kChunk;
-    if (k_next < K) load_w(k_next, nxt_a, nxt_b);
+    if (!first && k_next < K) load_w(k_next, nxt_a, nxt_b);  // the first pair was fetched before the wait
+    first = false;
 #pragma unroll
     for (int s = 0; s < kSub; ++s) {
       const int k = k0 + 32 * s + 8 * t;
