@@ -167,23 +167,16 @@ __device__ __forceinline__ void store_piece(const uint32_t (&r)[32], void* __res
       for (int i = 0; i < 32; i += 4) {
         float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
                                __uint_as_float(r[i + 3]));
-        if (atomic) {
-          atomicAdd(reinterpret_cast<float4*>(dst + i), v);
-          continue;
-        }
-        if (mode == 2) {
-          const float4 old = *reinterpret_cast<const float4*>(dst + i);
-          v.x += old.x;
-          v.y += old.y;
-          v.z += old.z;
-          v.w += old.w;
-        }
-        *reinterpret_cast<float4*>(dst + i) = v;
+        // Adding goes through a vector reduction in L2 (no value comes back, so the thread does
+        // not wait for the old contents). Without K slices each element gets exactly one add,
+        // so the result is as deterministic as a read-modify-write.
+        if (mode == 2) atomicAdd(reinterpret_cast<float4*>(dst + i), v);
+        else *reinterpret_cast<float4*>(dst + i) = v;
       }
     } else {
       for (int i = 0; i < 32 && n + i < N; ++i) {
-        if (atomic) atomicAdd(dst + i, __uint_as_float(r[i]));
-        else dst[i] = mode == 2 ? dst[i] + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+        if (mode == 2) atomicAdd(dst + i, __uint_as_float(r[i]));
+        else dst[i] = __uint_as_float(r[i]);
       }
     }
   }
