@@ -1,0 +1,433 @@
+// Causal grouped-query flash attention for prompts on the 5th-generation tensor cores.
+//
+// One CTA = 128 queries of one head of one sequence; keys and values arrive in tiles of 128
+// through TMA (cp.async.bulk.tensor, 128-byte swizzle, two stages). Per key tile:
+//   S = Q K^T      tcgen05.mma, M 128 x N 128, K = head size, into tensor memory
+//   softmax        four warps, one query row per thread: tcgen05.ld of the row, scale, causal and
+//                  window mask, running max and mass in float32 (log2 domain), P = 2^(s - m)
+//                  rounded to bfloat16 and written to shared memory in the operand layout
+//   PV = P V       tcgen05.mma, M 128 x N = head size, K 128, V read as an MN-major operand
+//                  exactly as TMA laid it down ([key][d] rows of 128 bytes)
+//   O = O a + PV   in registers (a = 2^(m_old - m_new)), tcgen05.ld of PV
+// The next tile's S is issued as soon as the probabilities of the current one are written, so
+// it runs under the current tile's PV and rescale. Head sizes 64 and 128.
+// Rows and keys outside a sequence are zero-filled by TMA or belong to a neighbouring sequence
+// of the packed batch; the causal mask hides such keys and such rows are never stored.
+// Every mbarrier wait is bounded; a wait that gives up records a code in `status`, and the CTA
+// winds down and frees its tensor memory. No cluster multicast.
+// (Reference: crates/metal-backend/src/shaders/attention.metal:28-57, the streaming softmax.)
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BQ = 128, BKV = 128, UMMA_K = 16;
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try_wait(bar, parity)) return true;
+  if (status != nullptr) atomicCAS(status, 0, where);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Shared-memory operand descriptor, 128-byte swizzle: start address >> 4 | leading byte offset
+// >> 4 at bit 16 | stride byte offset >> 4 at bit 32 | version 1 at bit 46 | SWIZZLE_128B at 61.
+// K-major tile (rows of 128 bytes along K): leading offset unused (1), stride 1024 (8 rows).
+// MN-major tile (rows of 128 bytes along N, one row per k): leading offset = distance between
+// 64-element blocks along N, stride 1024 (8 k).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes) {
+  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(leading_bytes >> 4) << 16) |
+         (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
+      "%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 2^x on the special-function unit (2 ulp; the probabilities are rounded to bfloat16 anyway)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+enum : int { kStuckQ = 11, kStuckKV = 12, kStuckScores = 13, kStuckProbabilities = 14, kStuckValues = 15,
+             kStuckStage = 16, kMisaligned = 17 };
+
+// Shared memory (1024-byte aligned): Q [128][D] | 2 stages of (K [128][D] | V [128][D]) |
+// P [2 blocks of 64 keys][128 rows][64] | barriers. A [128][D] tile with D = 128 is two
+// [128][64] blocks of 16 KB one after the other (a swizzle row is 128 bytes = 64 elements).
+template <int D>
+__global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+    const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window,
+    int* __restrict__ status) {
+  constexpr uint32_t TILE = BQ * D * 2;       // bytes of one [128][D] tile
+  constexpr uint32_t BLOCK = BQ * 64 * 2;     // bytes of one [128][64] block
+  constexpr int DB = D / 64;                  // 64-column blocks per tile
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  // The kernel has no static shared memory, so the dynamic block starts 1024-byte aligned, which
+  // the swizzled tiles need; should that ever not hold, give up rather than compute nonsense.
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, kMisaligned);
+    return;
+  }
+  unsigned char* q_tile = smem_raw;
+  unsigned char* kv_tiles = q_tile + TILE;                 // stage s: K at s * 2 * TILE, V right after
+  unsigned char* p_tile = kv_tiles + 4 * TILE;             // [2][128][64] bf16
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_tile + 2 * BLOCK);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_free = bars + 3;     // [2]
+  uint64_t* s_full = bars + 5;
+  uint64_t* p_ready = bars + 6;
+  uint64_t* pv_full = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* bail = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int qt = gridDim.x - 1 - blockIdx.x;  // long rows of work first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
+  const int q0 = qt * BQ;
+  if (q0 >= len) return;
+  const int kh = h / (q_heads / kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kt_first = window > 0 ? max(0, q0 - window + 1) / BKV : 0;
+  const int n_tiles = qt - kt_first + 1;  // key tiles up to the diagonal one
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(kv_full + s, 1);
+      mbar_init(kv_free + s, 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 4);
+    mbar_init(pv_full, 1);
+    *bail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(256u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = *tmem_slot, tmem_pv = tmem_s + 128;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- one thread loads tiles and issues the MMAs
+      auto load_kv = [&](int j) {
+        const int s = j & 1, row = start + (kt_first + j) * BKV;
+        unsigned char* kdst = kv_tiles + s * 2 * TILE;
+        mbar_expect_tx(kv_full + s, 2 * TILE);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          tma_load_2d(kdst + db * BLOCK, &map_k, kv_full + s, kh * D + db * 64, row);
+          tma_load_2d(kdst + TILE + db * BLOCK, &map_v, kv_full + s, kh * D + db * 64, row);
+        }
+      };
+      mbar_expect_tx(q_full, TILE);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) tma_load_2d(q_tile + db * BLOCK, &map_q, q_full, h * D + db * 64, start + q0);
+      load_kv(0);
+      if (n_tiles > 1) load_kv(1);
+
+      // instruction descriptors: D float32, A and B bfloat16, M 128; S: N 128, both K-major;
+      // PV: N = head size, B (V) MN-major (bit 16)
+      constexpr uint32_t common = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BQ >> 4) << 24);
+      constexpr uint32_t idesc_s = common | (static_cast<uint32_t>(BKV >> 3) << 17);
+      constexpr uint32_t idesc_pv = common | (static_cast<uint32_t>(D >> 3) << 17) | (1u << 16);
+      auto issue_scores = [&](int j) {
+        const uint32_t qa = smem_u32(q_tile), ka = smem_u32(kv_tiles + (j & 1) * 2 * TILE);
+#pragma unroll
+        for (int k = 0; k < D / UMMA_K; ++k) {
+          const uint32_t off = (k / 4) * BLOCK + (k % 4) * UMMA_K * 2;  // 64-column block, then 32 bytes per step
+          umma_bf16(tmem_s, smem_desc(qa + off, 16), smem_desc(ka + off, 16), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+      };
+      bool ok = mbar_wait(q_full, 0, status, kStuckQ) && mbar_wait(kv_full, 0, status, kStuckKV);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        ok = mbar_wait(p_ready, j & 1, status, kStuckProbabilities);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t pa = smem_u32(p_tile), va = smem_u32(kv_tiles + s * 2 * TILE + TILE);
+#pragma unroll
+        for (int k = 0; k < BKV / UMMA_K; ++k) {
+          // P: K-major, block of 64 keys then 32 bytes per step; V: MN-major, 16 keys = 2048 bytes
+          // per step, 64-column blocks 16 KB apart
+          umma_bf16(tmem_pv, smem_desc(pa + (k / 4) * BLOCK + (k % 4) * UMMA_K * 2, 16),
+                    smem_desc(va + k * UMMA_K * 128, BLOCK), idesc_pv, k > 0 ? 1u : 0u);
+        }
+        umma_commit(pv_full);
+        umma_commit(kv_free + s);
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(kv_full + ((j + 1) & 1), ((j + 1) >> 1) & 1, status, kStuckKV);
+          if (!ok) break;
+          tc_fence_after();
+          issue_scores(j + 1);
+        }
+        if (j + 2 < n_tiles) {
+          ok = mbar_wait(kv_free + s, (j >> 1) & 1, status, kStuckStage);
+          if (!ok) break;
+          load_kv(j + 2);
+        }
+      }
+      if (!ok) *bail = 1;
+    }
+  } else {
+    // ---- softmax and output: one query row per thread
+    const int row = q0 + warp * 32 + lane;       // position in the sequence
+    float o[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = !*bail && mbar_wait(s_full, j & 1, status, kStuckScores);
+      if (!ok) break;
+      tc_fence_after();
+      const int key0 = (kt_first + j) * BKV;
+      const bool edge = key0 + BKV - 1 > q0 || (window > 0 && key0 <= q0 + BQ - 1 - window);
+      // pass 1: the row's maximum (only tiles on the diagonal or the window's edge need the mask)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(tmem_s + lane_base + c * 32, r);
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            if (key <= row && (window <= 0 || key > row - window)) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m, mx * scale_log2);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_use);
+      // pass 2: probabilities, rounded to bfloat16, into the operand tile (row = this thread,
+      // 16-byte chunk c of a 128-byte row goes to chunk c ^ (row & 7))
+      float sum = 0.f;
+      unsigned char* prow = p_tile + (warp * 32 + lane) * 128;
+      const int swz = (warp * 32 + lane) & 7;
+#pragma unroll 1
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(tmem_s + lane_base + c * 32, r);
+        uint32_t packed[16];
+        if (edge) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int key = key0 + c * 32 + i;
+            const bool v0 = key <= row && (window <= 0 || key > row - window);
+            const bool v1 = key + 1 <= row && (window <= 0 || key + 1 > row - window);
+            const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(r[i]), scale_log2, -m_use)) : 0.f;
+            const float p1 = v1 ? fast_exp2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m_use)) : 0.f;
+            sum += p0 + p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m_use));
+            sum += p0 + p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+          }
+        }
+        // 32 keys = 4 chunks of 16 bytes; keys 0..63 live in block 0, 64..127 in block 1
+        unsigned char* blk = prow + (c >> 1) * BLOCK;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int chunk = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(blk + ((chunk ^ swz) << 4)) =
+              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      tc_fence_before();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> tensor core reads
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+      // rescale while the tensor core multiplies
+#pragma unroll
+      for (int d = 0; d < D; ++d) o[d] *= alpha;
+      ok = mbar_wait(pv_full, j & 1, status, kStuckValues);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_load32(tmem_pv + lane_base + c * 32, r);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+    }
+    if (!ok) *bail = 1;
+    if (ok && row < len) {
+      const float inv = 1.0f / l;
+      __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
+#pragma unroll
+      for (int d = 0; d < D; d += 8)
+        *reinterpret_cast<uint4*>(dst + d) =
+            make_uint4(pack_bf16(o[d] * inv, o[d + 1] * inv), pack_bf16(o[d + 2] * inv, o[d + 3] * inv),
+                       pack_bf16(o[d + 4] * inv, o[d + 5] * inv), pack_bf16(o[d + 6] * inv, o[d + 7] * inv));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(256u));
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    looked = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+// [tokens, heads * d] bfloat16, boxes of 128 tokens x 64 columns, 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* map, const void* base, int tokens, int width) {
+  EncodeTiledFn fn = encode_tiled();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(width) * 2};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int D>
+int launch(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens, int tokens,
+           int seqs, int max_seq_len, int q_heads, int kv_heads, float scale, int window, int* status,
+           cudaStream_t stream) {
+  CUtensorMap map_q, map_k, map_v;
+  if (!make_map(&map_q, q, tokens, q_heads * D) || !make_map(&map_k, k, tokens, kv_heads * D) ||
+      !make_map(&map_v, v, tokens, kv_heads * D))
+    return LRM_UNSUPPORTED;
+  constexpr int smem = 5 * BQ * D * 2 + 2 * BQ * 64 * 2 + 256;
+  auto kernel = attention_prefill_umma_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  const dim3 grid((max_seq_len + BQ - 1) / BQ, q_heads, seqs);
+  kernel<<<grid, 160, smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
+                                     q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
+  LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+}  // namespace
+
+LRM_API int lrm_attention_prefill_umma_supports(int head_dim) {
+  return (head_dim == 64 || head_dim == 128) && encode_tiled() != nullptr ? 1 : 0;
+}
+
+// q [tokens, q_heads, d], k, v [tokens, kv_heads, d] packed bfloat16, 16-byte aligned; `status` as
+// in lrm_gemm_bf16_umma.
+LRM_API int lrm_attention_prefill_umma(const void* q, const void* k, const void* v, void* out,
+                                       const int* cu_seqlens, int tokens, int seqs, int max_seq_len,
+                                       int q_heads, int kv_heads, int d, float scale, int window,
+                                       int* status, cudaStream_t stream) {
+  if (seqs <= 0 || max_seq_len <= 0 || tokens <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || status == nullptr) return LRM_BAD_ARGUMENT;
+  if (q_heads > 65535 || seqs > 65535) return LRM_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(k) % 16 ||
+      reinterpret_cast<uintptr_t>(v) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
+    return LRM_UNSUPPORTED;
+  if (d == 64)
+    return launch<64>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
+                      status, stream);
+  if (d == 128)
+    return launch<128>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
+                       status, stream);
+  return LRM_UNSUPPORTED;
+}

@@ -2,8 +2,9 @@
 
 The row-wise kernel (csrc/attention_rowwise.cu) takes every head size up to
 512 and both dtypes, and is the only attention of the float32 path. bfloat16
-with head size 32, 64 or 128 and 64-token pages runs the tiled kernels
-(csrc/attention_tiled.cu).
+prompts with head size 64 or 128 run the TMA + tcgen05 kernel
+(csrc/attention_prefill_umma.cu); bfloat16 with head size 32, 64 or 128 and
+64-token pages otherwise runs the warp-level tiled kernels (csrc/attention_tiled.cu).
 """
 from __future__ import annotations
 
@@ -16,6 +17,7 @@ from .ops import _code, _done, _ptr, _stream  # noqa: PLC2701
 
 SM_COUNT = 148
 force_rowwise = False  # tests switch the tiled kernels off to compare both paths
+force_warp_level = False  # tests keep prompts off the tcgen05 kernel to cover the warp-level one
 
 
 def _tiled(q, page_size: int) -> bool:
@@ -26,6 +28,17 @@ def _tiled(q, page_size: int) -> bool:
 def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: float, window: int) -> None:
     T, Hq, d = q.shape
     lib = library.load()
+    aligned = all(t.data_ptr() % 16 == 0 for t in (q, k, v, out))
+    if (not force_rowwise and not force_warp_level and q.dtype == torch.bfloat16 and aligned
+            and lib.lrm_attention_prefill_umma_supports(d)):
+        from . import gemm_dispatch
+        gemm_dispatch._status_dirty = True
+        _done(lib.lrm_attention_prefill_umma(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), T,
+                                             cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
+                                             ctypes.c_float(scale), window,
+                                             _ptr(gemm_dispatch._status_word(q.device)), _stream()),
+              "attention_prefill_umma")
+        return
     if _tiled(q, 64):
         _done(lib.lrm_attention_prefill_tiled(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens),
                                               cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,

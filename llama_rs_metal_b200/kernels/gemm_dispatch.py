@@ -45,8 +45,11 @@ def check_status() -> None:
         code = int(word.item())
         if code != 0:
             word.zero_()
-            names = {1: "a free stage", 2: "operand tiles", 3: "the accumulator", 4: "copies in flight"}
-            raise LlamaError(f"gemm_bf16_umma gave up waiting for {names.get(code, code)}; its result is invalid")
+            names = {1: "a free stage", 2: "operand tiles", 3: "the accumulator", 4: "copies in flight",
+                     5: "a free accumulator", 11: "the query tile", 12: "a key/value tile", 13: "scores",
+                     14: "probabilities", 15: "weighted values", 16: "a free key/value stage"}
+            kernel = "attention_prefill_umma" if code >= 11 else "gemm_bf16_umma"
+            raise LlamaError(f"{kernel} gave up waiting for {names.get(code, code)}; its result is invalid")
 
 
 def _wide(M: int, N: int) -> bool:

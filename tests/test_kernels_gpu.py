@@ -91,14 +91,18 @@ def test_linear_float32_row_does_not_depend_on_the_batch(ops):
         assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w)[0], full[r])
 
 
-@pytest.fixture(params=["fast kernels", "fallback kernels"])
+@pytest.fixture(params=["fast kernels", "warp-level attention", "fallback kernels"])
 def kernel_choice(request, monkeypatch):
-    """Run a test once with the kernels the dispatchers pick and once with the fallbacks forced."""
+    """Run a test with the kernels the dispatchers pick, with prompts kept off the tcgen05
+    attention, and with every fallback forced."""
     from llama_rs_metal_b200.kernels import attention_dispatch, gemm_dispatch
     if request.param == "fallback kernels":
         monkeypatch.setattr(gemm_dispatch, "force_tiled", True)
         monkeypatch.setattr(attention_dispatch, "force_rowwise", True)
-    return request.param
+    if request.param == "warp-level attention":
+        monkeypatch.setattr(attention_dispatch, "force_warp_level", True)
+    yield request.param
+    gemm_dispatch.check_status()
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES + [(64, 128, 2048), (5, 48, 8), (8, 3072, 2048), (33, 40, 1160)])
@@ -215,19 +219,20 @@ def plain_packed(q, k, v, cu, window=None):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (6, 6, 80), (8, 2, 128), (3, 1, 32), (10, 5, 64)])
-@pytest.mark.parametrize("window", [None, 5, 64])
+@pytest.mark.parametrize("window", [None, 5, 64, 200])
 def test_attention_prefill(ops, kernel_choice, dtype, Hq, Hk, d, window):
-    lengths = [1, 9, 70, 33, 130]
+    lengths = [1, 9, 70, 33, 130, 400, 128, 257]
     q, k, v, cu, seq_of = packed_case(lengths, Hq, Hk, d, dtype)
     got = ops.attention_prefill(q, k, v, i32(cu), i32(seq_of), max(lengths), d ** -0.5, window)
     close(got, plain_packed(q, k, v, cu, window), TOL[dtype], f"prefill window {window}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_attention_prefill_finds_one_far_key_among_hundreds(ops, kernel_choice, dtype):
+@pytest.mark.parametrize("d", [32, 64])
+def test_attention_prefill_finds_one_far_key_among_hundreds(ops, kernel_choice, dtype, d):
     # One key far back is scaled so that its score stands out: the output must be its value.
     lengths = [300, 257]
-    q, k, v, cu, seq_of = packed_case(lengths, 4, 2, 32, dtype, seed=9)
+    q, k, v, cu, seq_of = packed_case(lengths, 4, 2, d, dtype, seed=9)
     far = {0: 3, 1: 300 + 64}                 # packed index of the far key of each sequence
     for s, idx in far.items():
         k[idx] = 0
@@ -236,8 +241,8 @@ def test_attention_prefill_finds_one_far_key_among_hundreds(ops, kernel_choice, 
     q[cu[1] - 1, :, 0] = 40.0                 # last query of sequence 0
     q[cu[2] - 1, :, :] = 0
     q[cu[2] - 1, :, 0] = 40.0
-    got = ops.attention_prefill(q, k, v, i32(cu), i32(seq_of), 300, 32 ** -0.5).view(-1, 4, 32)
-    close(got, plain_packed(q, k, v, cu).view(-1, 4, 32), TOL[dtype], "far key")
+    got = ops.attention_prefill(q, k, v, i32(cu), i32(seq_of), 300, d ** -0.5).view(-1, 4, d)
+    close(got, plain_packed(q, k, v, cu).view(-1, 4, d), TOL[dtype], "far key")
     for s, idx in far.items():
         last = cu[s + 1] - 1
         for h in range(4):
