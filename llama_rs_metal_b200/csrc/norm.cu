@@ -51,10 +51,86 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const W* __restrict__ w, 
   }
 }
 
+// The same with 16-byte accesses: a thread keeps PER4 groups of four consecutive elements.
+// Needs hidden % 4 == 0 and 16-byte aligned rows.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <typename W, typename O, int PER4>
+__global__ void rms_norm_vec_kernel(float* __restrict__ x, const W* __restrict__ w, O* __restrict__ out,
+                                    const int* __restrict__ rows, const float* __restrict__ partials,
+                                    int n_partials, size_t partial_stride, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int groups = hidden >> 2;
+  float4 wv[PER4];
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {  // weights do not depend on the kernel before this one
+    const int c = threadIdx.x + e * blockDim.x;
+    wv[e] = c < groups ? load4(w + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_trigger();  // a small kernel: let the next one start (and prefetch its weights) right away
+  pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = static_cast<size_t>(rows ? rows[r] : r) * hidden;
+  float* xr = x + src;
+  O* yr = out + static_cast<size_t>(r) * hidden;
+  float4 xv[PER4];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    float4 v = c < groups ? load4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n_partials > 0 && c < groups) {
+      for (int p = 0; p < n_partials; ++p) {
+        const float4 d = load4(partials + p * partial_stride + src + 4 * c);
+        v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+      }
+      if (rows == nullptr) store4(xr + 4 * c, v);  // the folded sum becomes the residual stream
+    }
+    xv[e] = v;
+    ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+#pragma unroll
+  for (int e = 0; e < PER4; ++e) {
+    const int c = threadIdx.x + e * blockDim.x;
+    if (c < groups)
+      store4(yr + 4 * c, make_float4((xv[e].x * inv) * wv[e].x, (xv[e].y * inv) * wv[e].y,
+                                     (xv[e].z * inv) * wv[e].z, (xv[e].w * inv) * wv[e].w));
+  }
+}
+
 template <typename W, typename O>
 static int launch_norm(float* x, const void* w, void* out, const int* rows, const float* partials,
                         int n_partials, size_t partial_stride, int n_rows, int hidden, float eps,
                         cudaStream_t stream) {
+  auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  if (hidden % 4 == 0 && aligned(x) && aligned(w) && aligned(out) && aligned(partials)) {
+    const int groups = hidden / 4;
+    const int vthreads = groups >= 1024 ? 1024 : (groups >= 512 ? 256 : (groups >= 64 ? 128 : 32));
+    const int per4 = (groups + vthreads - 1) / vthreads;
+#define LRM_NORM_VEC(P4)                                                                               \
+  return static_cast<int>(lrm_launch(rms_norm_vec_kernel<W, O, P4>, n_rows, vthreads, 0, stream, x,   \
+                                     static_cast<const W*>(w), static_cast<O*>(out), rows, partials,  \
+                                     n_partials, partial_stride, hidden, eps))
+    if (per4 <= 2) LRM_NORM_VEC(2);
+    if (per4 <= 8) LRM_NORM_VEC(8);
+#undef LRM_NORM_VEC
+  }
   // up to 8 elements per thread for rows up to 8192 long, 32 beyond
   int threads = hidden >= 8192 ? 1024 : (hidden > 2048 ? 1024 : (hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32)));
 #define LRM_NORM_PER(PER)                                                                         \
