@@ -153,7 +153,8 @@ class Cache:
         self.pages = -(-max_tokens // page_size)
         pages_per_sequence = min(self.pages, -(-max_sequence // page_size))
         self.slots = FreeList(max_slots, "slot")
-        self.lengths = [0] * max_slots
+        self.lengths = np.zeros(max_slots, dtype=np.int64)  # tokens cached per slot
+        self.open_mask = np.zeros(max_slots, dtype=bool)      # slot is held by a sequence
         self.kv_groups: List[KeyValueGroup] = []
         self.state_groups: List[StateGroup] = []
         self._where: Dict[int, Tuple[str, int]] = {}
@@ -180,6 +181,7 @@ class Cache:
     def open_slot(self) -> int:
         (slot,) = self.slots.take(1)
         self.lengths[slot] = 0
+        self.open_mask[slot] = True
         for group in self.state_groups:
             group.clear(slot)
         return slot
@@ -189,6 +191,7 @@ class Cache:
         for group in self.kv_groups:
             group.release(slot)
         self.lengths[slot] = 0
+        self.open_mask[slot] = False
 
     def reset_slot(self, slot: int) -> None:
         """Forget a sequence's tokens but keep the slot (reference: Session::reset)."""
@@ -201,7 +204,7 @@ class Cache:
 
     def length(self, slot: int) -> int:
         self._require(slot)
-        return self.lengths[slot]
+        return int(self.lengths[slot])
 
     def _require(self, slot: int) -> None:
         if not (0 <= slot < self.max_slots) or not self.slots.is_held(slot):
@@ -230,6 +233,38 @@ class Cache:
                 group.release_stale(slot, new_length)
             for slot, new_length in growth:
                 group.take_missing(slot, new_length)
+
+    def grow_by_one(self, slots: np.ndarray):
+        """The decode step's bookkeeping for many sequences at once: every listed (open, distinct,
+        non-empty) slot grows by one token. Checks capacity and pages first and changes nothing
+        if the step does not fit. Returns (lengths before, per key/value group the row each new
+        token is stored at), or None when a group has a window (the general path handles those).
+        The caller commits with commit_lengths()."""
+        if any(g.request.window is not None for g in self.kv_groups):
+            return None
+        before = self.lengths[slots]
+        if int(before.max()) + 1 > self.max_sequence:
+            raise ContextError(self.max_sequence, int(before.max()) + 1)
+        ps = self.page_size
+        index = before // ps
+        missing = []
+        for group in self.kv_groups:
+            lacking = np.nonzero(group.table_host[slots, index] < 0)[0]
+            if len(lacking) > group.pool.available:
+                raise CacheMemoryError(f"step needs {len(lacking)} pages of {ps} tokens, "
+                                       f"{group.pool.available} free of {group.pool.count}")
+            missing.append(lacking)
+        rows = []
+        for group, lacking in zip(self.kv_groups, missing):
+            if len(lacking):
+                pages = group.pool.take(len(lacking))
+                group.table_host[slots[lacking], index[lacking]] = pages
+                group.dirty = True
+            rows.append((group.table_host[slots, index].astype(np.int64) * ps + before % ps).astype(np.int32))
+        return before, rows
+
+    def commit_lengths(self, slots: np.ndarray, lengths: np.ndarray) -> None:
+        self.lengths[slots] = lengths
 
     def commit(self, growth: Sequence[Tuple[int, int]]) -> None:
         for slot, new_length in growth:

@@ -114,6 +114,10 @@ class StepRunner:
             raise PoisonedError("a device error poisoned this session; reset it")
         entries = list(entries)
         cache = self.cache
+        if self.use_graphs and entries and all(len(e.tokens) == 1 for e in entries):
+            logits = self._decode_vectorized(entries, borrow)
+            if logits is not None:
+                return logits
         validate_entries(entries, self.model.plan.vocab_size)
         before = [cache.length(e.slot) for e in entries]
         phase = classify_step(entries, before)
@@ -147,12 +151,65 @@ class StepRunner:
             self.poisoned = True
             raise
 
+    # -- decode, host side in a few array operations -----------------------------------
+    def _decode_vectorized(self, entries: List[StepEntry], borrow: bool) -> Optional[torch.Tensor]:
+        """The decode step for sequences that each bring one token, with the same checks and
+        the same effects as the general path, but without a Python loop per sequence. Returns
+        None when the general path has to take over (a sequence at its first token, a window)."""
+        cache, batch = self.cache, len(entries)
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=batch)
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=batch)
+        if slots.min() < 0 or slots.max() >= cache.max_slots or not cache.open_mask[slots].all():
+            return None  # the general path names the slot that is not open
+        if len(np.unique(slots)) != batch:
+            raise InvalidError("a slot appears twice in one step")
+        if tokens.min() < 0 or tokens.max() >= self.model.plan.vocab_size:
+            raise InvalidError("token outside vocabulary")
+        wanted = []
+        for b, e in enumerate(entries):
+            for place in e.want:
+                if int(place) != 0:
+                    raise InvalidError(f"wanted place {place} is outside the 1 tokens of the entry")
+                wanted.append(b)
+        if (cache.lengths[slots] == 0).any():
+            return None  # a sequence at its first token: a prefill step, or a mixed one to refuse
+        grown = cache.grow_by_one(slots)
+        if grown is None:
+            return None
+        before, dest_rows = grown
+        cache.sync()
+        groups = len(dest_rows)
+        host = np.empty((7 + groups) * batch + 1, dtype=np.int32)
+        order = np.arange(batch + 1, dtype=np.int32)
+        host[0:batch] = tokens
+        host[batch:2 * batch] = before
+        host[2 * batch:3 * batch] = order[:batch]
+        host[3 * batch:4 * batch + 1] = order
+        host[4 * batch + 1:5 * batch + 1] = slots
+        host[5 * batch + 1:6 * batch + 1] = before + 1
+        host[6 * batch + 1:7 * batch + 1] = order[:batch]
+        for g, rows in enumerate(dest_rows):
+            host[(7 + g) * batch + 1:(8 + g) * batch + 1] = rows
+        try:
+            logits = self._replay(host, batch, int(before.max()) + 1, wanted, borrow)
+        except Exception:
+            self.poisoned = True
+            raise
+        cache.commit_lengths(slots, before + 1)
+        self.steps_run += 1
+        return logits
+
     # -- decode through a captured graph ---------------------------------------------
     def _decode_with_graph(self, entries: List[StepEntry], before: List[int], borrow: bool,
                            dest_rows) -> torch.Tensor:
         batch = len(entries)
         all_rows = [StepEntry(e.slot, e.tokens, (0,)) for e in entries]
         host, _, _, _, _, max_kv_len = pack_host(all_rows, before, dest_rows)
+        wanted = [b for b, e in enumerate(entries) for _ in e.want]
+        return self._replay(host, batch, max_kv_len, wanted, borrow)
+
+    def _replay(self, host: np.ndarray, batch: int, max_kv_len: int, wanted: List[int],
+                borrow: bool) -> torch.Tensor:
         key = (batch, length_bucket(max_kv_len))
         graph = self._graphs.get(key)
         if graph is None:
@@ -163,7 +220,6 @@ class StepRunner:
         graph.graph.replay()
         self.last_launches = graph.launches
         logits = graph.logits
-        wanted = [b for b, e in enumerate(entries) for _ in e.want]
         if wanted != list(range(batch)):
             index = torch.tensor(wanted, dtype=torch.long, device=logits.device)
             return logits.index_select(0, index)

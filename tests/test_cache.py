@@ -168,3 +168,32 @@ def test_destination_rows_follow_the_page_table_and_skip_dropped_positions():
     cache.grow([(a, 71), (b, 301)])
     full, _ = cache.destination_rows([a, b], [70, 300], [1, 1])
     assert full.tolist() == [tf[a][1] * 64 + 6, tf[b][4] * 64 + 300 % 64]
+
+
+def test_grow_by_one_does_what_grow_does_for_a_decode_step():
+    a, b = make(requests=(FULL, FULL), max_tokens=1024), make(requests=(FULL, FULL), max_tokens=1024)
+    for cache in (a, b):
+        for n in (63, 64, 5):
+            s = cache.open_slot()
+            cache.grow([(s, n)])
+            cache.commit([(s, n)])
+    slots = np.array([2, 0, 1])
+    for _ in range(70):
+        before, rows = a.grow_by_one(slots)
+        a.commit_lengths(slots, before + 1)
+        growth = [(int(s), b.length(int(s)) + 1) for s in slots]
+        b.grow(growth)
+        want = b.destination_rows([int(s) for s in slots], [n - 1 for _, n in growth], [1, 1, 1])
+        b.commit(growth)
+        assert np.array_equal(a.kv_groups[0].table_host, b.kv_groups[0].table_host)
+        assert [r.tolist() for r in rows] == [w.tolist() for w in want]
+        assert a.lengths.tolist() == b.lengths.tolist()
+    tight = make(requests=(FULL,), max_tokens=128, max_slots=2)
+    s, t = tight.open_slot(), tight.open_slot()
+    tight.grow([(s, 64), (t, 64)])
+    tight.commit([(s, 64), (t, 64)])
+    table = tight.kv_groups[0].table_host.copy()
+    with pytest.raises(CacheMemoryError):
+        tight.grow_by_one(np.array([s, t]))               # both need a new page, none is free
+    assert np.array_equal(table, tight.kv_groups[0].table_host)
+    assert make(requests=(WINDOW,)).grow_by_one(np.array([], dtype=np.int64)) is None
