@@ -137,7 +137,9 @@ class Session:
         self.cache.close_slot(slot)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        return self.runner.step(entries)
+        """For the generation loop: the logits are sampled from at once, so they may live in a
+        buffer that the next step overwrites."""
+        return self.runner.step(entries, borrow=True)
 
     def check_device_status(self) -> None:
         self.runner.check_device_status()

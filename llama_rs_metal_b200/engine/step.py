@@ -80,6 +80,7 @@ class _DecodeGraph:
         self.turn = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
+        self.greedy: Optional[torch.Tensor] = None  # int32 [B]: argmax of every row, part of the graph
         self.launches = 0
 
     def upload(self, host: np.ndarray) -> None:
@@ -108,7 +109,9 @@ class StepRunner:
         """float32 logits [wanted places, vocab] on the device, in entry order then `want` order.
 
         With `borrow` the result may be a buffer the next step overwrites (the
-        generation loop samples from it at once); otherwise it is the caller's.
+        generation loop samples from it at once); otherwise it is the caller's. A borrowed
+        result of a decode step that wants every row carries `greedy_ids`, the int32 argmax
+        of each row (lowest id on ties, -1 for a row with a non-finite logit).
         """
         if self.poisoned:
             raise PoisonedError("a device error poisoned this session; reset it")
@@ -236,5 +239,9 @@ class StepRunner:
         start = ops.launch_count()
         with torch.cuda.graph(captured, pool=self._pool):
             graph.logits = self.model.forward(graph.ctx, self.cache)
-        graph.launches = ops.launch_count() - start
+            # the greedy pick rides along (two small kernels): a sampler that wants it finds it
+            # as `logits.greedy_ids` and needs no launch of its own
+            graph.greedy = ops.argmax_rows(graph.logits)
+            graph.logits.greedy_ids = graph.greedy
+        graph.launches = ops.launch_count() - start  # the pick's two kernels included
         graph.graph = captured

@@ -31,7 +31,9 @@ class BatchSampler:
              histories: Sequence[Sequence[int]]) -> List[int]:
         o = self.options
         if o.greedy:
-            ids = ops.argmax_rows(logits).tolist()
+            ready = getattr(logits, "greedy_ids", None)  # a decode step computes it in its graph
+            ids = (ready if ready is not None and ready.shape[0] == logits.shape[0]
+                   else ops.argmax_rows(logits)).tolist()
             if any(i < 0 for i in ids):
                 raise OptionsError("invalid GPU logits")
             return ids
