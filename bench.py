@@ -125,8 +125,8 @@ def prefill_flops(config, layers, tokens):
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
-    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--steps", type=int, default=256)
+    parser.add_argument("--warmup", type=int, default=16)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--layers", type=int, default=FULL_LAYERS,
@@ -221,9 +221,12 @@ def main() -> int:
     def time_e2e(batch, steps):
         session = model.session(context=CONTEXT, max_batch=batch)
         prompts = [rng.integers(0, vocab, size=n).tolist() for n in start_lengths(batch)]
+        options = GenerationOptions(max_tokens=steps + 1, sampling=Sampling(temperature=0.0))
+        session.generate(prompts, options, stop_token_ids=())   # warm-up: the same steps once, untimed
+        torch.cuda.synchronize()
         stamps = []
-        session.generate(prompts, GenerationOptions(max_tokens=steps + 1, sampling=Sampling(temperature=0.0)),
-                         stop_token_ids=(), on_token=lambda request, token: stamps.append(time.perf_counter()))
+        session.generate(prompts, options, stop_token_ids=(),
+                         on_token=lambda request, token: stamps.append(time.perf_counter()))
         torch.cuda.synchronize()
         done = time.perf_counter()
         first = stamps[batch - 1]           # every request's first token (the prefill's) is out

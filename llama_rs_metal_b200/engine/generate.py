@@ -14,6 +14,9 @@ batch is empty the next one starts, reusing those slots.
 
 The loop owns no device code: it drives a `stepper` (open_slot, close_slot,
 step) and a `sampler` (pick), so its decisions are testable with stand-ins.
+A stepper that can enqueue a decode step whose tokens are still on the device
+(`can_decode_ahead`, `decode_ahead`) and a sampler that can choose on the device
+(`device_picker`) are driven one step ahead of the host; the results are the same.
 """
 from __future__ import annotations
 
@@ -110,9 +113,36 @@ def _finish(stepper, seq: _Live, reason: str) -> None:
     seq.slot = None
 
 
+def _settle(stepper, seqs: List[_Live], picked: Sequence[int], options, stop, on_token) -> List[_Live]:
+    """Take one chosen token per sequence: a stop id ends it, else the token is emitted and
+    becomes pending unless the budget is used up. Returns the sequences that go on."""
+    if len(picked) != len(seqs):
+        raise InvalidError("sampler returned a different number of tokens than rows")
+    still = []
+    for seq, token in zip(seqs, picked):
+        token = int(token)
+        if token < 0:
+            raise OptionsError("invalid GPU logits")  # a row without a finite maximum
+        if token in stop:
+            _finish(stepper, seq, "eos")  # not emitted, not counted, not fed
+            continue
+        seq.result.tokens.append(token)
+        if on_token is not None:
+            on_token(seq.result.request, token)
+        if len(seq.result.tokens) >= options.max_tokens:
+            _finish(stepper, seq, "length")
+            continue
+        seq.pending = token
+        still.append(seq)
+    return still
+
+
 def _run_batch(stepper, sampler, live: List[_Live], options, stop, context, cancelled, on_token) -> None:
     active = list(live)
     first = True
+    check = getattr(stepper, "check_device_status", None)
+    run_ahead = (getattr(stepper, "can_decode_ahead", False) and hasattr(sampler, "device_picker")
+                 and sampler.device_picker([0], [0]) is not None)
     while active:
         if cancelled():
             for seq in active:
@@ -133,6 +163,9 @@ def _run_batch(stepper, sampler, live: List[_Live], options, stop, context, canc
             active = fitting
             if not active:
                 return
+            if run_ahead:
+                active = _decode_ahead(stepper, sampler, active, options, stop, context, cancelled, on_token)
+                continue
             entries = [StepEntry(seq.slot, [seq.pending], [0]) for seq in active]
             for seq in active:
                 seq.pending = None
@@ -142,23 +175,55 @@ def _run_batch(stepper, sampler, live: List[_Live], options, stop, context, canc
             [seq.result.request for seq in active],
             [len(seq.result.tokens) for seq in active],
             [seq.result.prompt + seq.result.tokens for seq in active])
-        check = getattr(stepper, "check_device_status", None)
         if check is not None:
             check()  # the pick above already synchronized with the device
-        if len(picked) != len(active):
-            raise InvalidError("sampler returned a different number of tokens than rows")
-        still = []
-        for seq, token in zip(active, picked):
-            token = int(token)
-            if token in stop:
-                _finish(stepper, seq, "eos")  # not emitted, not counted, not fed
-                continue
-            seq.result.tokens.append(token)
-            if on_token is not None:
-                on_token(seq.result.request, token)
-            if len(seq.result.tokens) >= options.max_tokens:
-                _finish(stepper, seq, "length")
-                continue
-            seq.pending = token
-            still.append(seq)
-        active = still
+        active = _settle(stepper, active, picked, options, stop, on_token)
+
+
+def _decode_ahead(stepper, sampler, active: List[_Live], options, stop, context, cancelled, on_token) -> List[_Live]:
+    """Decode steps for a set of sequences that stays the same, with one step always in flight.
+
+    The step after the current one is enqueued before the host has seen the current step's
+    tokens: it takes them from the device. What the host can foresee (the token budget, the
+    context) decides whether that next step may be enqueued at all; a stop token it cannot
+    foresee, so when one ends a sequence the step already in flight has carried that sequence
+    one token too far. That row is dropped (rows do not depend on one another, and the slot is
+    closed anyway), the other rows of that step count as usual, and the caller goes on with
+    the smaller set. The decisions per sequence are those of the plain loop, in its order.
+    Returns the sequences that go on, each with its pending token.
+    """
+    check = getattr(stepper, "check_device_status", None)
+    slots = [seq.slot for seq in active]
+    requests = [seq.result.request for seq in active]
+
+    def picker(offset: int):
+        return sampler.device_picker(requests, [len(seq.result.tokens) + offset for seq in active])
+
+    tokens = [seq.pending for seq in active]
+    for seq in active:
+        seq.pending = None
+    current = stepper.decode_ahead(slots, tokens, None, picker(0))
+    while True:
+        # may every sequence take one more step after this one, as far as the host can tell?
+        foreseeable = not cancelled() and all(
+            len(seq.result.tokens) + 1 < options.max_tokens and seq.cached < context for seq in active)
+        following = stepper.decode_ahead(slots, None, current, picker(1)) if foreseeable else None
+        picked = current.ids()
+        if check is not None:
+            check()
+        still = _settle(stepper, active, picked, options, stop, on_token)
+        if following is None:
+            return still
+        if len(still) == len(active):
+            for seq in active:
+                seq.pending = None  # fed from the device by the step in flight
+            current = following
+            continue
+        # a stop token ended some: the step in flight still carried them
+        picked = following.ids()
+        if check is not None:
+            check()
+        row_of = {id(seq): row for row, seq in enumerate(active)}
+        for seq in still:
+            seq.pending = None
+        return _settle(stepper, still, [picked[row_of[id(seq)]] for seq in still], options, stop, on_token)

@@ -144,6 +144,13 @@ class Session:
     def check_device_status(self) -> None:
         self.runner.check_device_status()
 
+    @property
+    def can_decode_ahead(self) -> bool:
+        return self.runner.can_decode_ahead
+
+    def decode_ahead(self, slots, tokens, previous, picker):
+        return self.runner.decode_ahead(slots, tokens, previous, picker)
+
     # -- many sequences -------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
                  stop_token_ids: Optional[Iterable[int]] = None,

@@ -92,6 +92,26 @@ class _DecodeGraph:
         self.events[i].record()
 
 
+class PendingPicks:
+    """Token ids a step chose on the device, on their way to a pinned host buffer."""
+
+    def __init__(self, capacity: int):
+        self.host = torch.zeros(capacity, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.device_ids: Optional[torch.Tensor] = None
+        self.batch = 0
+
+    def launch(self, device_ids: torch.Tensor, batch: int) -> None:
+        self.device_ids, self.batch = device_ids, batch
+        self.host[:batch].copy_(device_ids, non_blocking=True)
+        self.event.record()
+
+    def ids(self) -> List[int]:
+        """The chosen ids (waits for the step that chose them, not for later ones)."""
+        self.event.synchronize()
+        return self.host[:self.batch].tolist()
+
+
 class StepRunner:
     """Binds a model and a cache and runs steps on the current CUDA stream."""
 
@@ -155,25 +175,18 @@ class StepRunner:
             raise
 
     # -- decode, host side in a few array operations -----------------------------------
-    def _decode_vectorized(self, entries: List[StepEntry], borrow: bool) -> Optional[torch.Tensor]:
-        """The decode step for sequences that each bring one token, with the same checks and
-        the same effects as the general path, but without a Python loop per sequence. Returns
-        None when the general path has to take over (a sequence at its first token, a window)."""
-        cache, batch = self.cache, len(entries)
-        slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=batch)
-        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=batch)
+    def _prepare_decode(self, slots: np.ndarray, tokens: np.ndarray):
+        """Checks and bookkeeping of a decode step for `slots` (one token each): returns the
+        packed host buffer and the lengths before the step, or None when the general path has
+        to take over (a slot that is not open, a sequence at its first token, a window).
+        Pages are taken here; the caller commits the lengths after launching."""
+        cache, batch = self.cache, len(slots)
         if slots.min() < 0 or slots.max() >= cache.max_slots or not cache.open_mask[slots].all():
             return None  # the general path names the slot that is not open
         if len(np.unique(slots)) != batch:
             raise InvalidError("a slot appears twice in one step")
         if tokens.min() < 0 or tokens.max() >= self.model.plan.vocab_size:
             raise InvalidError("token outside vocabulary")
-        wanted = []
-        for b, e in enumerate(entries):
-            for place in e.want:
-                if int(place) != 0:
-                    raise InvalidError(f"wanted place {place} is outside the 1 tokens of the entry")
-                wanted.append(b)
         if (cache.lengths[slots] == 0).any():
             return None  # a sequence at its first token: a prefill step, or a mixed one to refuse
         grown = cache.grow_by_one(slots)
@@ -193,14 +206,89 @@ class StepRunner:
         host[6 * batch + 1:7 * batch + 1] = order[:batch]
         for g, rows in enumerate(dest_rows):
             host[(7 + g) * batch + 1:(8 + g) * batch + 1] = rows
+        return host, before
+
+    def _decode_vectorized(self, entries: List[StepEntry], borrow: bool) -> Optional[torch.Tensor]:
+        """The decode step for sequences that each bring one token, with the same checks and
+        the same effects as the general path, but without a Python loop per sequence. Returns
+        None when the general path has to take over."""
+        batch = len(entries)
+        slots = np.fromiter((e.slot for e in entries), dtype=np.int64, count=batch)
+        tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=batch)
+        wanted = []
+        for b, e in enumerate(entries):
+            for place in e.want:
+                if int(place) != 0:
+                    raise InvalidError(f"wanted place {place} is outside the 1 tokens of the entry")
+                wanted.append(b)
+        prepared = self._prepare_decode(slots, tokens)
+        if prepared is None:
+            return None
+        host, before = prepared
         try:
             logits = self._replay(host, batch, int(before.max()) + 1, wanted, borrow)
         except Exception:
             self.poisoned = True
             raise
-        cache.commit_lengths(slots, before + 1)
+        self.cache.commit_lengths(slots, before + 1)
         self.steps_run += 1
         return logits
+
+    # -- decode that does not wait for its own result -------------------------------------
+    @property
+    def can_decode_ahead(self) -> bool:
+        """True when decode steps can take their tokens from the device (CUDA graphs on, no
+        windowed cache group)."""
+        return self.use_graphs and all(g.request.window is None for g in self.cache.kv_groups)
+
+    def decode_ahead(self, slots: Sequence[int], tokens: Optional[Sequence[int]], previous,
+                     picker) -> "PendingPicks":
+        """Enqueue one decode step for `slots` and the choice of their next tokens; do not wait.
+
+        The step's input tokens are `tokens` (host ids), or, when `tokens` is None, the ids
+        that `previous` (the PendingPicks of the step before, for the same slots in the same
+        order) chose on the device: the host then need not have seen them yet. `picker` maps
+        the step's logits to an int32 [B] device tensor of chosen ids. The returned object
+        gives the ids on the host when asked (it waits for this step only).
+        """
+        if self.poisoned:
+            raise PoisonedError("a device error poisoned this session; reset it")
+        batch = len(slots)
+        slot_array = np.asarray(slots, dtype=np.int64)
+        token_array = np.zeros(batch, dtype=np.int64) if tokens is None else np.asarray(tokens, dtype=np.int64)
+        prepared = self._prepare_decode(slot_array, token_array)
+        if prepared is None:
+            raise UnsupportedError("decode_ahead needs open, started sequences and no windowed cache group")
+        host, before = prepared
+        try:
+            key = (batch, length_bucket(int(before.max()) + 1))
+            graph = self._graphs.get(key)
+            if graph is None:
+                graph = self._graphs[key] = _DecodeGraph(self, *key)
+            graph.upload(host)
+            if tokens is None:
+                graph.static[:batch].copy_(previous.device_ids)  # the ids chosen by the step before
+            if graph.graph is None:
+                self._capture(graph)
+            graph.graph.replay()
+            self.last_launches = graph.launches
+            device_ids = picker(graph.logits)
+            pending = self._pending_slot()
+            pending.launch(device_ids, batch)
+        except Exception:
+            self.poisoned = True
+            raise
+        self.cache.commit_lengths(slot_array, before + 1)
+        self.steps_run += 1
+        return pending
+
+    def _pending_slot(self) -> "PendingPicks":
+        if not hasattr(self, "_pending_ring"):
+            self._pending_ring = [PendingPicks(self.cache.max_slots) for _ in range(4)]
+            self._pending_turn = 0
+        slot = self._pending_ring[self._pending_turn % 4]
+        self._pending_turn += 1
+        return slot
 
     # -- decode through a captured graph ---------------------------------------------
     def _decode_with_graph(self, entries: List[StepEntry], before: List[int], borrow: bool,

@@ -27,6 +27,24 @@ class BatchSampler:
         self.options = options
         self._rngs = {}
 
+    def device_picker(self, requests: Sequence[int], steps: Sequence[int]):
+        """For greedy and plain-temperature sampling: a function logits -> int32 [rows] device
+        tensor of chosen ids that enqueues work but never waits for the device; None for the
+        host sampler. -1 in its result marks a row with non-finite logits."""
+        o = self.options
+        if o.greedy:
+            def greedy(logits):
+                ready = getattr(logits, "greedy_ids", None)
+                return ready if ready is not None and ready.shape[0] == logits.shape[0] else ops.argmax_rows(logits)
+            return greedy
+        if o.plain_temperature:
+            keys = torch.tensor([(r << 32) | s for r, s in zip(requests, steps)], dtype=torch.int64)
+
+            def gumbel(logits):
+                return ops.sample_gumbel_rows(logits, o.temperature, o.seed, keys.to(logits.device, non_blocking=True))
+            return gumbel
+        return None
+
     def pick(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int],
              histories: Sequence[Sequence[int]]) -> List[int]:
         o = self.options

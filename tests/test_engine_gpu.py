@@ -256,6 +256,31 @@ def test_stop_ids_context_and_temperature_through_the_entry_point(engine, model_
            [r.tokens for r in session.generate(prompts[:2], ref, stop_token_ids=())]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_one_step_ahead_equals_step_by_step(engine, model_dirs, dtype):
+    """With CUDA graphs the loop keeps one decode step in flight and feeds tokens on the
+    device; without them it waits for every token. Same tokens and reasons either way:
+    greedy and temperature, with stop ids that end sequences at different steps, a context
+    that ends one, and more requests than slots."""
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    model = engine.load(model_dirs["A"], dtype=dtype)
+    prompts = [helpers.random_tokens(70 + i, n, 256) for i, n in enumerate([3, 14, 40, 7, 66, 21, 1])]
+    ahead = model.session(context=80, max_batch=3)
+    plain = model.session(context=80, max_batch=3)
+    plain.runner.use_graphs = False
+    assert ahead.can_decode_ahead and not plain.can_decode_ahead
+    for sampling in (Sampling(temperature=0.0), Sampling(temperature=0.9, top_k=0, top_p=1.0, seed=4)):
+        options = GenerationOptions(max_tokens=24, sampling=sampling)
+        free = plain.generate(prompts, options, stop_token_ids=())
+        stops = sorted({free[0].tokens[5], free[1].tokens[11], free[3].tokens[0], free[5].tokens[23]})
+        for stop_ids in ((), stops):
+            want = plain.generate(prompts, options, stop_token_ids=stop_ids)
+            got = ahead.generate(prompts, options, stop_token_ids=stop_ids)
+            assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want]
+        assert {r.finish_reason for r in want} >= {"eos", "length", "context"}
+    assert ahead.cache.slots.held == 0 and ahead.cache.held_pages() == [0]
+
+
 def test_session_own_sequence_prefill_decode_reset(engine, model_dirs, plain_models):
     model = engine.load(model_dirs["A"], dtype="float32")
     session = model.session(context=96)

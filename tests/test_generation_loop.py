@@ -194,3 +194,70 @@ def test_repeat_penalty_and_top_k_change_the_choice():
     only_top = {sample_host(logits, [], SplitMix64(s), Sampling(temperature=5.0, top_k=2, top_p=1.0))
                 for s in range(200)}
     assert only_top == {0, 1}
+
+
+class AheadStepper(ScriptedStepper):
+    """The scripted stepper with a decode step whose tokens the host has not seen yet: what a
+    step chose stays 'on the device' (a list the host may only read through ids())."""
+
+    can_decode_ahead = True
+
+    class Pending:
+        def __init__(self, chosen):
+            self.device_ids, self.read = chosen, False
+
+        def ids(self):
+            self.read = True
+            return list(self.device_ids)
+
+    def decode_ahead(self, slots, tokens, previous, picker):
+        fed = list(previous.device_ids) if tokens is None else list(tokens)
+        assert len(fed) == len(slots)
+        self.log.append(("ahead" if tokens is None else "decode", [(s, [t]) for s, t in zip(slots, fed)]))
+        rows = []
+        for slot, token in zip(slots, fed):
+            seq = self.live[slot]  # a slot that was closed meanwhile would fail here
+            assert seq, "decode before the prompt"
+            seq.append(token)
+            row = np.zeros(self.vocab, dtype=np.float32)
+            row[(sum(seq) * 7 + len(seq)) % self.vocab] = 10.0
+            rows.append(row)
+        return self.Pending(picker(np.stack(rows)))
+
+
+class AheadSampler(ArgmaxSampler):
+    def device_picker(self, requests, steps):
+        return lambda logits: [int(np.argmax(r)) for r in logits]
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_running_one_step_ahead_changes_no_decision(seed):
+    rng = np.random.default_rng(seed)
+    prompts = [[int(t) for t in rng.integers(0, 50, size=int(rng.integers(1, 9)))] for _ in range(int(rng.integers(1, 8)))]
+    stop = [int(t) for t in rng.integers(0, 50, size=int(rng.integers(0, 6)))]
+    max_tokens = int(rng.integers(1, 12))
+    context = int(rng.integers(9, 16))
+    options = GenerationOptions(max_tokens=max_tokens, sampling=Sampling(temperature=0.0))
+    plain = ScriptedStepper(slots=3)
+    want = generate(plain, ArgmaxSampler(), prompts, options, stop_token_ids=stop, max_batch=3, context=context)
+    ahead = AheadStepper(slots=3)
+    emitted = []
+    got = generate(ahead, AheadSampler(), prompts, options, stop_token_ids=stop, max_batch=3, context=context,
+                   on_token=lambda request, token: emitted.append((request, token)))
+    assert not ahead.live, "a slot was not given back"
+    assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want]
+    assert sorted(emitted) == sorted((r.request, t) for r in got for t in r.tokens)
+    # no token is fed that the plain loop does not feed, except to a sequence that a stop token
+    # had just ended (its row is dropped)
+    fed_plain = sum(len(rows) for kind, rows in plain.log if kind == "decode")
+    fed_ahead = sum(len(rows) for kind, rows in ahead.log if kind != "prefill")
+    ended_by_stop = sum(r.finish_reason == "eos" for r in got)
+    assert fed_plain <= fed_ahead <= fed_plain + ended_by_stop
+
+
+def test_running_ahead_keeps_a_step_in_flight():
+    stepper = AheadStepper(slots=2)
+    options = GenerationOptions(max_tokens=6, sampling=Sampling(temperature=0.0))
+    generate(stepper, AheadSampler(), [[1, 2], [3]], options, max_batch=2)
+    kinds = [k for k, _ in stepper.log]
+    assert kinds == ["prefill", "decode", "ahead", "ahead", "ahead", "ahead"]
