@@ -5,6 +5,9 @@ The row-wise kernel (csrc/attention_rowwise.cu) takes every head size up to
 prompts with head size 64 or 128 run the TMA + tcgen05 kernel
 (csrc/attention_prefill_umma.cu); bfloat16 with head size 32, 64 or 128 and
 64-token pages otherwise runs the warp-level tiled kernels (csrc/attention_tiled.cu).
+A bfloat16 decode step of a layer that writes its own unwindowed cache runs rotation,
+cache write, attention and the merge of the splits as one cluster kernel
+(csrc/attention_decode_cluster.cu).
 """
 from __future__ import annotations
 
@@ -18,6 +21,8 @@ from .ops import _code, _done, _ptr, _stream  # noqa: PLC2701
 SM_COUNT = 148
 force_rowwise = False  # tests switch the tiled kernels off to compare both paths
 force_warp_level = False  # tests keep prompts off the tcgen05 kernel to cover the warp-level one
+force_unfused_decode = False  # tests keep decode steps on the separate rotation / attention / merge kernels
+force_cluster_size = None  # tests fix the CTAs per cluster of the fused decode kernel
 
 
 def _tiled(q, page_size: int) -> bool:
@@ -79,3 +84,44 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
                                           _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,
                                           ctypes.c_float(scale), window, _stream()),
           "attention_paged_rowwise")
+
+
+_cluster_ok = {}
+
+
+def _cluster_launchable(head_dim: int, cluster: int) -> bool:
+    key = (head_dim, cluster)
+    if key not in _cluster_ok:
+        _cluster_ok[key] = library.load().lrm_attention_decode_cluster_resident(head_dim, cluster) > 0
+    return _cluster_ok[key]
+
+
+def decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, window) -> bool:
+    """True when one cluster kernel can do rotation, cache write, attention and merge."""
+    return (not force_rowwise and not force_unfused_decode and dtype == torch.bfloat16 and not window
+            and bool(library.load().lrm_attention_decode_cluster_supports(head_dim, page_size, rotary)))
+
+
+def decode_cluster_size(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> int:
+    """CTAs per (sequence, kv head): a power of two up to 16, about CTAS_PER_SM CTAs per SM in all."""
+    if force_cluster_size is not None:
+        return force_cluster_size
+    clusters = seqs * kv_heads * -(-group // 16)
+    pages = max(1, -(-max_kv_len // 64))
+    per_sm = CTAS_PER_SM if head_dim <= 64 else 2
+    wanted = min(pages, max(1, per_sm * SM_COUNT // clusters))
+    size = 1
+    while size * 2 <= min(wanted, 16) and _cluster_launchable(head_dim, size * 2):
+        size *= 2
+    return size
+
+
+def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slots, kv_lens, max_kv_len: int,
+                 q_heads: int, scale: float) -> None:
+    B = qkv.shape[0]
+    d = kv.head_dim
+    cluster = decode_cluster_size(B, kv.kv_heads, q_heads // kv.kv_heads, d, max_kv_len)
+    _done(library.load().lrm_attention_decode_cluster(
+        _ptr(qkv), _ptr(positions), _ptr(inv_freq), rotary, _ptr(kv.k), _ptr(kv.v), _ptr(dest_rows), _ptr(out),
+        _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots), _ptr(kv_lens), B, q_heads, kv.kv_heads, d,
+        kv.page_size, ctypes.c_float(scale), cluster, _stream()), "attention_decode_cluster")

@@ -282,6 +282,46 @@ def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Te
     return out
 
 
+def attention_decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, window) -> bool:
+    from . import attention_dispatch
+    return attention_dispatch.decode_fused_supported(dtype, head_dim, page_size, rotary, window)
+
+
+def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[torch.Tensor], rotary: int,
+                           positions: torch.Tensor, kv, dest_rows: torch.Tensor, slots: torch.Tensor,
+                           kv_lens: torch.Tensor, max_kv_len: int, scale: float) -> torch.Tensor:
+    """A decode step's attention from its fused, unrotated [B, (Hq+2Hk)*d] projection: rotates q and
+    the new k, stores the new k and v at `dest_rows`, attends over the cache (kv_lens counts the new
+    token) and merges the splits, in one launch. -> [B, Hq*d]"""
+    _check(qkv, "qkv", torch.bfloat16, 2)
+    d, Hk = kv.head_dim, kv.kv_heads
+    if qkv.shape[1] != (q_heads + 2 * Hk) * d or q_heads % Hk:
+        raise InvalidError("attention_decode_fused: qkv width does not match the head geometry")
+    _check(kv.k, "k pages", qkv.dtype, 4)
+    _check(kv.v, "v pages", qkv.dtype, 4)
+    if tuple(kv.k.shape[1:]) != (Hk, kv.page_size, d):
+        raise InvalidError("attention_decode_fused: cache pages do not match the head geometry")
+    _check(kv.page_table, "page table", torch.int32, 2)
+    B = qkv.shape[0]
+    for name, t in (("positions", positions), ("dest_rows", dest_rows), ("slots", slots), ("kv_lens", kv_lens)):
+        _check(t, name, torch.int32, 1)
+        if t.numel() != B:
+            raise InvalidError(f"attention_decode_fused: one entry of {name} per sequence")
+    if inv_freq is not None:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.numel() != rotary // 2:
+            raise InvalidError("attention_decode_fused: inv_freq must have rotary/2 entries")
+    else:
+        rotary = 0
+    if not attention_decode_fused_supported(qkv.dtype, d, kv.page_size, rotary, kv.window):
+        raise UnsupportedError("attention_decode_fused: geometry not supported; use rope_store and attention_decode")
+    out = torch.empty((B, q_heads * d), dtype=qkv.dtype, device=qkv.device)
+    from . import attention_dispatch
+    attention_dispatch.decode_fused(qkv, positions, inv_freq, rotary, kv, dest_rows, out, slots, kv_lens,
+                                    max_kv_len, q_heads, scale)
+    return out
+
+
 # --------------------------------------------------------------------------- sampling
 def _pick_scratch(logits: torch.Tensor):
     pieces = _lib().lrm_pick_pieces(logits.shape[1])

@@ -74,6 +74,15 @@ class Attention(Mixer):
             qkv = self.qkv(x)
             if self.position is not None and table is None:
                 qkv = self._apply_other_position(qkv, ctx)
+            if (not prefill and cache is not None and qkv.dtype == torch.bfloat16
+                    and ops.attention_decode_fused_supported(qkv.dtype, self.head_dim, cache.page_size,
+                                                             rotary if inv_freq is not None else 0,
+                                                             self.window or cache.window)):
+                # rotation, cache write, attention and the merge of the splits in one launch
+                mixed = ops.attention_decode_fused(qkv, self.num_heads, inv_freq, rotary, ctx.positions, cache,
+                                                   ctx.dest_rows[cache.group], ctx.slots, ctx.kv_lens,
+                                                   ctx.max_kv_len, self.scale)
+                return self.out(mixed, epilogue=ops.ADD, out=residual)
             q, k, v = ops.rope_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim, inv_freq,
                                      rotary, ctx.positions, kv=cache,
                                      dest_rows=ctx.dest_rows[cache.group] if cache is not None else None,

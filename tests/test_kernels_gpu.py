@@ -326,6 +326,77 @@ def test_float32_decode_equals_prefill_bit_for_bit(ops):
         assert torch.equal(pre[-1], dec[b])
 
 
+@pytest.mark.parametrize("cluster", [None, 1, 2, 8])
+@pytest.mark.parametrize("Hq,Hk,d,rotary", [(32, 8, 64, 64), (8, 2, 128, 128), (3, 1, 32, 32), (40, 2, 64, 32),
+                                             (6, 3, 128, 64), (6, 3, 128, 96), (4, 4, 64, 0)])
+def test_attention_decode_fused_rotates_stores_attends_and_merges(ops, Hq, Hk, d, rotary, cluster):
+    """The one-launch decode attention against the plain rotation and attention, and against the
+    separate kernels: the new key/value row it leaves in the cache is bit-equal to rope_store's.
+    Sequences shorter than the cluster (CTAs without a page), page edges, poisoned free rows."""
+    from llama_rs_metal_b200.kernels import attention_dispatch
+    dtype = torch.bfloat16
+    lengths = [1, 64, 65, 300, 129, 1000]
+    B = len(lengths)
+    _, view, slots, ks, vs = paged_case(ops, lengths, Hq, Hk, d, dtype, seed=11)
+    qkv = rnd(B, (Hq + 2 * Hk) * d, dtype=dtype, seed=77)
+    inv = (1.0 / (10000.0 ** (torch.arange(0, rotary, 2, dtype=torch.float64) / max(rotary, 1)))).float() if rotary else None
+    positions = [n - 1 for n in lengths]
+    table = view.page_table.cpu()
+    dest = [int(table[slots[b], (n - 1) // 64]) * 64 + (n - 1) % 64 for b, n in enumerate(lengths)]
+    for b, n in enumerate(lengths):                    # the new row is not in the cache yet
+        view.k[dest[b] // 64, :, dest[b] % 64] = float("nan")
+        view.v[dest[b] // 64, :, dest[b] % 64] = float("nan")
+    # what the separate kernels do with the same input, in a copy of the cache
+    twin = View(view.k.shape[0], Hk, 64, d, dtype, slots=6, per_seq=view.page_table.shape[1])
+    twin.k.copy_(view.k), twin.v.copy_(view.v), twin.page_table.copy_(view.page_table)
+    inv_dev = inv.to(DEV) if inv is not None else None
+    q_rot, _, _ = ops.rope_store(qkv, Hq, Hk, d, inv_dev, rotary, i32(positions), kv=twin, dest_rows=i32(dest),
+                                 keep_packed=False)
+    want_unfused = ops.attention_decode(q_rot, twin, i32(slots), i32(lengths), max(lengths), d ** -0.5)
+    attention_dispatch.force_cluster_size = cluster
+    try:
+        got = ops.attention_decode_fused(qkv, Hq, inv_dev, rotary, i32(positions), view, i32(dest), i32(slots),
+                                         i32(lengths), max(lengths), d ** -0.5)
+    finally:
+        attention_dispatch.force_cluster_size = None
+    assert torch.equal(view.k.view(torch.int16), twin.k.view(torch.int16)), "the cache's keys differ from rope_store's"
+    assert torch.equal(view.v.view(torch.int16), twin.v.view(torch.int16))
+    # against the plain implementation: rotate in float64, round as the cache does
+    x = qkv.double().cpu().view(B, Hq + 2 * Hk, d)
+    for b, n in enumerate(lengths):
+        heads = x[b:b + 1, :Hq + Hk]
+        rotated = P.rope(heads, [n - 1], inv.numpy(), rotary) if rotary else heads
+        ks[b][n - 1] = rotated[0, Hq:].to(dtype)
+        vs[b][n - 1] = x[b, Hq + Hk:].to(dtype)
+        x[b, :Hq] = rotated[0, :Hq].to(dtype).double()
+    want = plain_decode(x[:, :Hq], ks, vs)
+    close(got, want, TOL[dtype], "fused decode attention")
+    close(got, want_unfused.double().cpu(), TOL[dtype], "fused against separate kernels")
+
+
+def test_attention_decode_fused_far_key_and_new_key(ops):
+    """One old key far back, or the new key itself, must carry the whole output."""
+    dtype, Hq, Hk, d = torch.bfloat16, 8, 2, 64
+    lengths = [900, 513]
+    _, view, slots, ks, vs = paged_case(ops, lengths, Hq, Hk, d, dtype, seed=5)
+    table = view.page_table.cpu()
+    dest = [int(table[slots[b], (n - 1) // 64]) * 64 + (n - 1) % 64 for b, n in enumerate(lengths)]
+    qkv = torch.zeros(2, (Hq + 2 * Hk) * d, dtype=dtype, device=DEV)
+    x = qkv.view(2, Hq + 2 * Hk, d)
+    x[:, :Hq, 3] = 40.0                                  # every query looks along dimension 3
+    x[:, Hq + Hk:] = rnd(2, Hk, d, dtype=dtype, seed=9)  # the new values
+    x[1, Hq:Hq + Hk, 3] = 40.0                           # sequence 1: its new key wins
+    far = 70                                             # sequence 0: the key at position 70 wins
+    ks[0][far] = 0
+    ks[0][far, :, 3] = 40.0
+    view.k[int(table[slots[0], far // 64]), :, far % 64] = ks[0][far]
+    got = ops.attention_decode_fused(qkv, Hq, None, 0, i32([n - 1 for n in lengths]), view, i32(dest), i32(slots),
+                                     i32(lengths), max(lengths), d ** -0.5).view(2, Hq, d)
+    for h in range(Hq):
+        close(got[0, h], vs[0][far, h // 4].double(), 2e-2, "the far key's value")
+        close(got[1, h], x[1, Hq + Hk + h // 4].double().cpu(), 2e-2, "the new key's value")
+
+
 # --------------------------------------------------------------------------- sampling
 def test_argmax_rows_ties_and_non_finite(ops):
     logits = rnd(5, 5003)
