@@ -8,8 +8,8 @@
 // so the activation fragment is loaded with the same address pattern and the
 // products pair up correctly without any shuffle or shared-memory staging.
 //
-// A CTA owns 16 weight rows; its warps split K in interleaved 64- or 128-wide chunks
-// (so many loads are in flight per SM) and their partial sums are added in
+// A CTA owns 16 weight rows; its warps split K into contiguous ranges, streamed in 64- or
+// 128-wide chunks (so many loads are in flight per SM), and their partial sums are added in
 // warp order through shared memory (no atomics: the result is deterministic).
 //
 // For the add epilogue blockIdx.y may cut K into slices handled by different CTAs that meet in
@@ -75,11 +75,16 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
+  // Each warp streams one contiguous range of k (so that what it has in flight is adjacent in
+  // memory): [k0, k_end), a whole number of chunks except at the end of the slice.
+  const int per_warp = ((K - k_lo + WARPS - 1) / WARPS + kChunk - 1) / kChunk * kChunk;
+  int k0 = k_lo + warp * per_warp;
+  const int k_end = min(K, k0 + per_warp);
   auto load_w = [&](int k0, uint4 (&a)[kSub], uint4 (&b)[kSub]) {
 #pragma unroll
     for (int s = 0; s < kSub; ++s) {
       const int k = k0 + 32 * s + 8 * t;
-      const bool in = k < K;  // K is a multiple of 8: a 16-byte piece is inside or outside
+      const bool in = k < k_end;  // a multiple of 8: a 16-byte piece is inside or outside
       a[s] = in && ok_a ? ldg_stream(wa + k) : zero;
       b[s] = in && ok_b ? ldg_stream(wb + k) : zero;
     }
@@ -89,9 +94,8 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
   // for the predecessor (which produced X and may still be writing `out`). Each warp keeps the
   // next chunk in flight while it multiplies the current one.
   uint4 cur_a[kSub], cur_b[kSub], nxt_a[kSub], nxt_b[kSub];
-  int k0 = k_lo + warp * kChunk;
-  if (k0 < K) load_w(k0, cur_a, cur_b);
-  if (k0 + WARPS * kChunk < K) load_w(k0 + WARPS * kChunk, nxt_a, nxt_b);
+  if (k0 < k_end) load_w(k0, cur_a, cur_b);
+  if (k0 + kChunk < k_end) load_w(k0 + kChunk, nxt_a, nxt_b);
   pdl_wait();
   // mode 2 adds into `out`: fetch the old values now so their latency hides behind the stream
   float old[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
@@ -106,9 +110,9 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
       }
   }
   bool first = true;
-  while (k0 < K) {
-    const int k_next = k0 + WARPS * kChunk;
-    if (!first && k_next < K) load_w(k_next, nxt_a, nxt_b);  // the first pair was fetched before the wait
+  while (k0 < k_end) {
+    const int k_next = k0 + kChunk;
+    if (!first && k_next < k_end) load_w(k_next, nxt_a, nxt_b);  // the first pair was fetched before the wait
     first = false;
 #pragma unroll
     for (int s = 0; s < kSub; ++s) {
@@ -116,7 +120,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
         const int m = 8 * j + g;
-        const uint4 x = (m < M && k < K) ? ldg_keep(X + static_cast<size_t>(m) * K_total + k) : zero;
+        const uint4 x = (m < M && k < k_end) ? ldg_keep(X + static_cast<size_t>(m) * K_total + k) : zero;
         mma16816(acc[j], cur_a[s].x, cur_b[s].x, cur_a[s].y, cur_b[s].y, x.x, x.y);
         mma16816(acc[j], cur_a[s].z, cur_b[s].z, cur_a[s].w, cur_b[s].w, x.z, x.w);
       }
