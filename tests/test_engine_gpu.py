@@ -474,3 +474,176 @@ def test_a_schedule_may_run_a_layer_twice_and_share_another_layers_cache(engine,
     straight, cache2, _ = open_runner(engine, plain_folder, "float32", max_tokens=512, max_slots=2)
     other = straight.step([entry(cache2.open_slot(), tokens)])
     assert not torch.allclose(other, whole, atol=1e-3)
+
+
+# --------------------------------------------------------------------------- other parts, defined here
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_feed_forward_position_norm_and_block_are_registered_from_outside(engine, tmp_path, dtype):
+    """A feed-forward with routing (top-1 of three experts), a learned absolute position added to q
+    and k, a LayerNorm with bias and a block that feeds mixer and feed-forward from one norm, all
+    defined here and registered under new names: a model of them loads, steps with the library's
+    attention, cache and step function, and agrees with a plain restatement, whole and cut into
+    steps, alone and in a batch of unequal lengths. No file of the library changes."""
+    from dataclasses import dataclass
+    from llama_rs_metal_b200.config.base import read_int
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.parts import (Block, FeedForward, LayerSpec, ModelPlan, Norm, PartSpec, PositionEncoding,
+                                           ScheduleEntry)
+    from llama_rs_metal_b200.registry import (register_architecture, register_block, register_feed_forward,
+                                              register_norm, register_position_encoding)
+    from llama_rs_metal_b200.weights import TensorSpec
+
+    E, F_, H, HEADS, KV, D, MAXPOS = 3, 20, 40, 4, 2, 32, 96
+
+    @register_feed_forward("toy_routed")
+    class Routed(FeedForward):
+        def __init__(self, hidden_size, experts, inner):
+            self.h, self.e, self.f = hidden_size, experts, inner
+
+        def tensors(self):
+            return {"router.weight": TensorSpec((self.e, self.h)), "up.weight": TensorSpec((self.e, self.f, self.h)),
+                    "down.weight": TensorSpec((self.e, self.h, self.f))}
+
+        def bind(self, weights, runtime):
+            self.w = {k: v.float() for k, v in weights.items()}
+
+        def forward(self, x, ctx, residual):
+            xs = x.float()
+            prob = torch.softmax(xs @ self.w["router.weight"].T, dim=-1)        # router in float32
+            best = prob.argmax(dim=-1)
+            for e in range(self.e):
+                rows = (best == e).nonzero().flatten()
+                if rows.numel():
+                    inner = torch.relu(xs[rows] @ self.w["up.weight"][e].T)
+                    residual[rows] += (inner @ self.w["down.weight"][e].T) * prob[rows, e:e + 1]
+            return residual
+
+    @register_position_encoding("toy_learned")
+    class Learned(PositionEncoding):
+        def __init__(self, head_dim, positions):
+            self.d, self.n = head_dim, positions
+
+        def tensors(self):
+            return {"table": TensorSpec((self.n, self.d))}
+
+        def bind(self, weights, runtime):
+            self.table = weights["table"]
+
+        def rotary_table(self):
+            return None
+
+        def apply(self, q, k, ctx):
+            add = self.table[ctx.positions.long()][:, None, :]
+            return (q.float() + add.float()).to(q.dtype), (k.float() + add.float()).to(k.dtype)
+
+    @register_norm("toy_layer_norm")
+    class LayerNorm(Norm):
+        def __init__(self, size, eps):
+            self.size, self.eps = size, eps
+
+        def tensors(self):
+            return {"weight": TensorSpec((self.size,)), "bias": TensorSpec((self.size,))}
+
+        def bind(self, weights, runtime):
+            self.w, self.b, self.dtype = weights["weight"].float(), weights["bias"].float(), runtime.dtype
+
+        def forward(self, hidden, ctx, rows=None):
+            x = hidden if rows is None else hidden[rows.long()]
+            return torch.nn.functional.layer_norm(x, (self.size,), self.w, self.b, self.eps).to(self.dtype)
+
+    @register_block("toy_parallel")
+    class Parallel(Block):
+        def forward(self, hidden, ctx, cache):
+            x = self.mixer_norm.forward(hidden, ctx)
+            hidden = self.mixer.forward(x, ctx, cache, residual=hidden)
+            return self.feed_forward.forward(x, ctx, residual=hidden)
+
+    @dataclass(frozen=True)
+    class Config:
+        layers: int
+        vocab: int
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(read_int(d, "layers"), read_int(d, "vocab"))
+
+        def to_dict(self):
+            return dict(architectures=["ToyPartsForCausalLM"], layers=self.layers, vocab=self.vocab)
+
+    def plan(c):
+        layers = []
+        for i in range(c.layers):
+            p = f"l{i}."
+            norm = PartSpec("toy_layer_norm", dict(size=H, eps=1e-4), prefix=p + "norm.")
+            layers.append(LayerSpec(
+                "toy_parallel",
+                PartSpec("attention", dict(hidden_size=H, num_heads=HEADS, num_kv_heads=KV, head_dim=D,
+                                           position=PartSpec("toy_learned", dict(head_dim=D, positions=MAXPOS))),
+                         prefix=p + "attn."),
+                PartSpec("toy_routed", dict(hidden_size=H, experts=E, inner=F_), prefix=p + "ff."), norm, norm))
+        return ModelPlan(H, c.vocab, MAXPOS, "embed.weight", tuple(layers),
+                         tuple(ScheduleEntry(i, i) for i in range(c.layers)),
+                         PartSpec("toy_layer_norm", dict(size=H, eps=1e-4), prefix="final."), "head.weight")
+
+    register_architecture("ToyPartsForCausalLM", Config, plan)
+    folder = write_random_model(str(tmp_path), dict(architectures=["ToyPartsForCausalLM"], layers=2, vocab=70),
+                                seed=3, std=0.3)
+    _, w = P.read_model(folder)
+    if dtype == "bfloat16":
+        w = {k: v.to(torch.bfloat16).double() for k, v in w.items()}
+
+    margin = 1e-4 if dtype == "float32" else 0.015
+
+    def oracle(tokens):
+        """Logits, and how many leading rows are safe to compare: a router decision that hangs
+        on less than `margin` may fall the other way in the engine's precision, and every later
+        token sees that token through attention."""
+        n = len(tokens)
+        safe = n
+        hidden = w["embed.weight"][torch.tensor(tokens)]
+        ln = lambda x, p: torch.nn.functional.layer_norm(x, (H,), w[p + "weight"], w[p + "bias"], 1e-4)
+        for i in range(2):
+            p = f"l{i}."
+            x = ln(hidden, p + "norm.")
+            add = w[p + "attn.position.table"][:n][:, None, :]
+            q = (x @ w[p + "attn.q_proj.weight"].T).view(n, HEADS, D) + add
+            k = (x @ w[p + "attn.k_proj.weight"].T).view(n, KV, D) + add
+            v = (x @ w[p + "attn.v_proj.weight"].T).view(n, KV, D)
+            mixed = P.attention(q, k, v).reshape(n, HEADS * D) @ w[p + "attn.o_proj.weight"].T
+            prob = torch.softmax(x @ w[p + "ff.router.weight"].T, dim=-1)
+            best = prob.argmax(dim=-1)
+            top2 = prob.topk(2, dim=-1).values
+            close_call = ((top2[:, 0] - top2[:, 1]) < margin).nonzero().flatten()
+            if close_call.numel():
+                safe = min(safe, int(close_call[0]))
+            routed = torch.zeros_like(hidden)
+            for t in range(n):
+                e = int(best[t])
+                routed[t] = (torch.relu(x[t] @ w[p + "ff.up.weight"][e].T) @ w[p + "ff.down.weight"][e].T) * prob[t, e]
+            hidden = hidden + mixed + routed
+        return ln(hidden, "final.") @ w["head.weight"].T, safe
+
+    runner, cache, model = open_runner(engine, folder, dtype, max_tokens=512, max_slots=3)
+    seqs = [helpers.random_tokens(80 + i, n, 70) for i, n in enumerate([70, 9, 33])]
+    refs, safe = zip(*[oracle(s) for s in seqs])
+    assert sum(safe) >= 40, "the test's weights leave too few unambiguous router decisions"
+    for s, ref, ok in zip(seqs, refs, safe):                         # each alone and whole
+        slot = cache.open_slot()
+        helpers.assert_logits_close(runner.step([entry(slot, s)]).cpu()[:ok], ref[:ok], dtype, "toy parts, whole")
+        cache.close_slot(slot)
+    slots = [cache.open_slot() for _ in seqs]                        # unequal prompts in one step, then one token each
+    prompts = [40, 3, 20]
+    out = runner.step([entry(sl, s[:p]) for sl, s, p in zip(slots, seqs, prompts)]).cpu()
+    at = 0
+    for s, ref, p, ok in zip(seqs, refs, prompts, safe):
+        helpers.assert_logits_close(out[at:at + min(p, ok)], ref[:min(p, ok)], dtype, "toy parts, prompts in a batch")
+        at += p
+    for step in range(30):
+        live = [b for b in range(3) if prompts[b] + step < len(seqs[b])]
+        out = runner.step([entry(slots[b], [seqs[b][prompts[b] + step]]) for b in live]).cpu()
+        for r, b in enumerate(live):
+            if prompts[b] + step < safe[b]:
+                helpers.assert_logits_close(out[r:r + 1], refs[b][prompts[b] + step][None], dtype, "toy parts, decoding")
+        for b in range(3):
+            if prompts[b] + step + 1 == len(seqs[b]):
+                cache.close_slot(slots[b])
