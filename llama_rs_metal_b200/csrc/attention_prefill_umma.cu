@@ -144,8 +144,11 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* bail = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int qt = gridDim.x - 1 - blockIdx.x;  // long rows of work first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // CTAs are handed out in the order x, y, z: all heads and sequences of the last query tile
+  // (the longest rows of work under the causal mask) first, the first query tile last, so the
+  // tail of the grid is made of short CTAs.
+  const int qt = gridDim.z - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
   const int q0 = qt * BQ;
   if (q0 >= len) return;
@@ -398,7 +401,8 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
   auto kernel = attention_prefill_umma_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const dim3 grid((max_seq_len + BQ - 1) / BQ, q_heads, seqs);
+  if (seqs > 65535 || (max_seq_len + BQ - 1) / BQ > 65535) return LRM_UNSUPPORTED;
+  const dim3 grid(q_heads, seqs, (max_seq_len + BQ - 1) / BQ);
   kernel<<<grid, 160, smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
                                      q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
   LRM_LAUNCH_CHECK();

@@ -35,8 +35,10 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
   __nv_bfloat16* Vs = Ks + 2 * TILE;
 
   pdl_wait();
-  const int qt = gridDim.x - 1 - blockIdx.x;  // long rows of work first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // CTAs are handed out in the order x, y, z: the last query tile (the longest row of work under
+  // the causal mask) of every head and sequence first, so the grid's tail is made of short CTAs.
+  const int qt = gridDim.z - 1 - blockIdx.z;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
   const int q0 = qt * kTile;
   if (q0 >= len) return;
@@ -282,7 +284,8 @@ template <int D> int prefill_launch(const void* q, const void* k, const void* v,
   auto kernel = attention_prefill_tiled_kernel<D>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const dim3 grid((max_seq_len + kTile - 1) / kTile, q_heads, seqs);
+  if (seqs > 65535 || (max_seq_len + kTile - 1) / kTile > 65535) return LRM_UNSUPPORTED;
+  const dim3 grid(q_heads, seqs, (max_seq_len + kTile - 1) / kTile);
   LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
              static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
              static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads, kv_heads,

@@ -102,6 +102,22 @@ def decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, wi
             and bool(library.load().lrm_attention_decode_cluster_supports(head_dim, page_size, rotary)))
 
 
+def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> bool:
+    """Whether the one-launch cluster kernel or the separate kernels are the faster way through a
+    decode step's attention. A cluster has at most 16 CTAs, so a few sequences with a long context
+    leave each CTA with many pages to walk, while the separate kernels may cut a sequence into as
+    many splits as fill the device. Measured costs: about 8 us fixed for the cluster kernel, 17 us
+    for the three separate launches, and 0.9 us per page a CTA walks."""
+    if force_cluster_size is not None:
+        return True
+    pages = max(1, -(-max_kv_len // 64))
+    cluster = decode_cluster_size(seqs, kv_heads, group, head_dim, max_kv_len)
+    splits = decode_splits(seqs, kv_heads, group, max_kv_len, 0)
+    fused = 8.0 + 0.9 * -(-pages // cluster)
+    separate = 17.0 + 0.9 * -(-pages // splits)
+    return fused <= separate
+
+
 def decode_cluster_size(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> int:
     """CTAs per (sequence, kv head): a power of two up to 16, about CTAS_PER_SM CTAs per SM in all."""
     if force_cluster_size is not None:

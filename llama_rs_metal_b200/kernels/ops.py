@@ -287,6 +287,12 @@ def attention_decode_fused_supported(dtype, head_dim: int, page_size: int, rotar
     return attention_dispatch.decode_fused_supported(dtype, head_dim, page_size, rotary, window)
 
 
+def attention_decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> bool:
+    """Whether the one-launch kernel is expected to beat the separate kernels for this step's geometry."""
+    from . import attention_dispatch
+    return attention_dispatch.decode_prefers_fused(seqs, kv_heads, group, head_dim, max_kv_len)
+
+
 def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[torch.Tensor], rotary: int,
                            positions: torch.Tensor, kv, dest_rows: torch.Tensor, slots: torch.Tensor,
                            kv_lens: torch.Tensor, max_kv_len: int, scale: float) -> torch.Tensor:

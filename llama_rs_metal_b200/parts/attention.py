@@ -77,7 +77,10 @@ class Attention(Mixer):
             if (not prefill and cache is not None and qkv.dtype == torch.bfloat16
                     and ops.attention_decode_fused_supported(qkv.dtype, self.head_dim, cache.page_size,
                                                              rotary if inv_freq is not None else 0,
-                                                             self.window or cache.window)):
+                                                             self.window or cache.window)
+                    and ops.attention_decode_prefers_fused(qkv.shape[0], self.num_kv_heads,
+                                                           self.num_heads // self.num_kv_heads, self.head_dim,
+                                                           ctx.max_kv_len)):
                 # rotation, cache write, attention and the merge of the splits in one launch
                 mixed = ops.attention_decode_fused(qkv, self.num_heads, inv_freq, rotary, ctx.positions, cache,
                                                    ctx.dest_rows[cache.group], ctx.slots, ctx.kv_lens,
