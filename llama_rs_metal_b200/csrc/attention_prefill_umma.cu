@@ -3,12 +3,15 @@
 // One CTA = 128 queries of one head of one sequence; keys and values arrive in tiles of 128
 // through TMA (cp.async.bulk.tensor, 128-byte swizzle, two stages). Per key tile:
 //   S = Q K^T      tcgen05.mma, M 128 x N 128, K = head size, into tensor memory
-//   softmax        four warps, one query row per thread: tcgen05.ld of the row, scale, causal and
-//                  window mask, running max and mass in float32 (log2 domain), P = 2^(s - m)
-//                  rounded to bfloat16 and written to shared memory in the operand layout
+//   softmax        eight warps, two threads per query row (each takes 64 of the tile's keys; the
+//                  two exchange the row's maximum through a spare column of tensor memory):
+//                  tcgen05.ld of the half row, scale, causal and window mask, running max and mass
+//                  in float32 (log2 domain), P = 2^(s - m) rounded to bfloat16 and written to
+//                  shared memory in the operand layout
 //   PV = P V       tcgen05.mma, M 128 x N = head size, K 128, V read as an MN-major operand
 //                  exactly as TMA laid it down ([key][d] rows of 128 bytes)
-//   O = O a + PV   in registers (a = 2^(m_old - m_new)), tcgen05.ld of PV
+//   O = O a + PV   in registers, half of the head's columns per thread (a = 2^(m_old - m_new)),
+//                  tcgen05.ld of PV
 // The next tile's S is issued as soon as the probabilities of the current one are written, so
 // it runs under the current tile's PV and rescale. Head sizes 64 and 128.
 // Rows and keys outside a sequence are zero-filled by TMA or belong to a neighbouring sequence
@@ -98,6 +101,19 @@ __device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t (&r)[32]) {
       : "r"(addr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_store1(uint32_t addr, uint32_t value) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(addr), "r"(value) : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t tmem_load1(uint32_t addr) {
+  uint32_t value;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(value) : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  return value;
+}
+__device__ __forceinline__ void pair_barrier(int id) {  // the two warps that share a row quadrant
+  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
 // 2^x on the special-function unit (2 ulp; the probabilities are rounded to bfloat16 anyway)
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -109,6 +125,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+constexpr int kSoftmaxWarps = 8;   // two per 32 query rows: each takes half of a tile's keys
+constexpr int kThreadsPerCta = (kSoftmaxWarps + 1) * 32;
+
 enum : int { kStuckQ = 11, kStuckKV = 12, kStuckScores = 13, kStuckProbabilities = 14, kStuckValues = 15,
              kStuckStage = 16, kMisaligned = 17 };
 
@@ -116,7 +135,7 @@ enum : int { kStuckQ = 11, kStuckKV = 12, kStuckScores = 13, kStuckProbabilities
 // P [2 blocks of 64 keys][128 rows][64] | barriers. A [128][D] tile with D = 128 is two
 // [128][64] blocks of 16 KB one after the other (a swizzle row is 128 bytes = 64 elements).
 template <int D>
-__global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_kernel(
+__global__ __launch_bounds__(kThreadsPerCta, D == 64 ? 2 : 1) void attention_prefill_umma_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window,
@@ -143,6 +162,7 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
   uint64_t* pv_full = bars + 7;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
   volatile int* bail = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* pair_fail = bail + 1;  // [2 parities][4 pairs of warps]
 
   // CTAs are handed out in the order x, y, z: all heads and sequences of the last query tile
   // (the longest rows of work under the causal mask) first, the first query tile last, so the
@@ -164,23 +184,25 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
       mbar_init(kv_free + s, 1);
     }
     mbar_init(s_full, 1);
-    mbar_init(p_ready, 4);
+    mbar_init(p_ready, kSoftmaxWarps);
     mbar_init(pv_full, 1);
     *bail = 0;
+    for (int i = 0; i < 8; ++i) pair_fail[i] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 4) {
+  constexpr uint32_t kTmemColumns = D == 64 ? 256u : 512u;  // scores 128 | weighted values D | 2 to exchange
+  if (warp == kSoftmaxWarps) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(256u));
+                 "r"(kTmemColumns));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_s = *tmem_slot, tmem_pv = tmem_s + 128;
+  const uint32_t tmem_s = *tmem_slot, tmem_pv = tmem_s + 128, tmem_x = tmem_pv + D;
 
-  if (warp == 4) {
+  if (warp == kSoftmaxWarps) {
     if (lane == 0) {
       // ---- one thread loads tiles and issues the MMAs
       auto load_kv = [&](int j) {
@@ -248,30 +270,40 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
       if (!ok) *bail = 1;
     }
   } else {
-    // ---- softmax and output: one query row per thread
-    const int row = q0 + warp * 32 + lane;       // position in the sequence
-    float o[D];
+    // ---- softmax and output: two threads per query row. Warps w and w + 4 own the same 32 rows
+    // (TMEM lanes): warp w < 4 takes the first 64 keys of every tile and the first half of the
+    // head's columns, warp w + 4 the rest. The pair exchanges the row's maximum (and at the end
+    // its mass) through two spare TMEM columns and meets at a named barrier of its own.
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = q0 + quad * 32 + lane;       // position in the sequence
+    constexpr int DH = D / 2;                    // output columns per thread
+    float o[DH];
 #pragma unroll
-    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    for (int d = 0; d < DH; ++d) o[d] = 0.f;
     float m = -INFINITY, l = 0.f;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = !*bail && mbar_wait(s_full, j & 1, status, kStuckScores);
-      if (!ok) break;
+      // A wait that gave up is told to the partner warp before the pair's barrier, in a flag that
+      // only this pair writes and only for this parity, so both warps leave the loop together.
+      if (!(!*bail && mbar_wait(s_full, j & 1, status, kStuckScores))) {
+        pair_fail[(j & 1) * 4 + quad] = 1;
+        *bail = 1;
+      }
       tc_fence_after();
       const int key0 = (kt_first + j) * BKV;
       const bool edge = key0 + BKV - 1 > q0 || (window > 0 && key0 <= q0 + BQ - 1 - window);
-      // pass 1: the row's maximum (only tiles on the diagonal or the window's edge need the mask)
+      // pass 1: the maximum of this thread's half of the row (only tiles on the diagonal or the
+      // window's edge need the mask)
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_load32(tmem_s + lane_base + c * 32, r);
+        tmem_load32(tmem_s + lane_base + half * 64 + c * 32, r);
         if (edge) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
+            const int key = key0 + half * 64 + c * 32 + i;
             if (key <= row && (window <= 0 || key > row - window)) mx = fmaxf(mx, __uint_as_float(r[i]));
           }
         } else {
@@ -279,23 +311,32 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
           for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
         }
       }
+      tmem_store1(tmem_x + lane_base + half, __float_as_uint(mx));
+      tc_fence_before();
+      pair_barrier(1 + quad);
+      tc_fence_after();
+      if (pair_fail[(j & 1) * 4 + quad]) {
+        ok = false;
+        break;
+      }
+      mx = fmaxf(mx, __uint_as_float(tmem_load1(tmem_x + lane_base + (half ^ 1))));
       const float m_new = fmaxf(m, mx * scale_log2);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_use);
-      // pass 2: probabilities, rounded to bfloat16, into the operand tile (row = this thread,
-      // 16-byte chunk c of a 128-byte row goes to chunk c ^ (row & 7))
+      // pass 2: probabilities, rounded to bfloat16, into the operand tile: keys 64 half .. + 63 are
+      // block `half` (row = this thread's; 16-byte chunk c of a 128-byte row goes to chunk c ^ (row & 7))
       float sum = 0.f;
-      unsigned char* prow = p_tile + (warp * 32 + lane) * 128;
-      const int swz = (warp * 32 + lane) & 7;
+      unsigned char* prow = p_tile + half * BLOCK + (quad * 32 + lane) * 128;
+      const int swz = (quad * 32 + lane) & 7;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_load32(tmem_s + lane_base + c * 32, r);
+        tmem_load32(tmem_s + lane_base + half * 64 + c * 32, r);
         uint32_t packed[16];
         if (edge) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const int key = key0 + c * 32 + i;
+            const int key = key0 + half * 64 + c * 32 + i;
             const bool v0 = key <= row && (window <= 0 || key > row - window);
             const bool v1 = key + 1 <= row && (window <= 0 || key + 1 > row - window);
             const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(r[i]), scale_log2, -m_use)) : 0.f;
@@ -312,12 +353,10 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
             packed[i >> 1] = pack_bf16(p0, p1);
           }
         }
-        // 32 keys = 4 chunks of 16 bytes; keys 0..63 live in block 0, 64..127 in block 1
-        unsigned char* blk = prow + (c >> 1) * BLOCK;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(blk + ((chunk ^ swz) << 4)) =
+        for (int q4 = 0; q4 < 4; ++q4) {  // 32 keys = 4 chunks of 16 bytes
+          const int chunk = c * 4 + q4;
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ swz) << 4)) =
               make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
@@ -329,25 +368,37 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
       if (lane == 0) mbar_arrive(p_ready);
       // rescale while the tensor core multiplies
 #pragma unroll
-      for (int d = 0; d < D; ++d) o[d] *= alpha;
-      ok = mbar_wait(pv_full, j & 1, status, kStuckValues);
-      if (!ok) break;
-      tc_fence_after();
+      for (int d = 0; d < DH; ++d) o[d] *= alpha;
+      if (mbar_wait(pv_full, j & 1, status, kStuckValues)) {
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_load32(tmem_pv + lane_base + c * 32, r);
+        for (int c = 0; c < DH / 32; ++c) {
+          uint32_t r[32];
+          tmem_load32(tmem_pv + lane_base + half * DH + c * 32, r);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+      } else {  // seen by both warps of the pair after the next barrier
+        pair_fail[((j + 1) & 1) * 4 + quad] = 1;
+        *bail = 1;
       }
+    }
+    // the pair adds up the row's mass; both warps are here for the same reason
+    if (ok) {
+      tmem_store1(tmem_x + lane_base + half, __float_as_uint(l));
       tc_fence_before();
+      pair_barrier(1 + quad);
+      tc_fence_after();
+      ok = !pair_fail[(n_tiles & 1) * 4 + quad];
+      l += __uint_as_float(tmem_load1(tmem_x + lane_base + (half ^ 1)));
     }
     if (!ok) *bail = 1;
     if (ok && row < len) {
       const float inv = 1.0f / l;
-      __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
+      __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D + half * DH;
 #pragma unroll
-      for (int d = 0; d < D; d += 8)
+      for (int d = 0; d < DH; d += 8)
         *reinterpret_cast<uint4*>(dst + d) =
             make_uint4(pack_bf16(o[d] * inv, o[d + 1] * inv), pack_bf16(o[d + 2] * inv, o[d + 3] * inv),
                        pack_bf16(o[d + 4] * inv, o[d + 5] * inv), pack_bf16(o[d + 6] * inv, o[d + 7] * inv));
@@ -355,8 +406,8 @@ __global__ __launch_bounds__(160, D == 64 ? 2 : 1) void attention_prefill_umma_k
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 4)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(256u));
+  if (warp == kSoftmaxWarps)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(kTmemColumns));
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -403,7 +454,7 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
   if (e != cudaSuccess) return static_cast<int>(e);
   if (seqs > 65535 || (max_seq_len + BQ - 1) / BQ > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(q_heads, seqs, (max_seq_len + BQ - 1) / BQ);
-  kernel<<<grid, 160, smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
+  kernel<<<grid, kThreadsPerCta, smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
                                      q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
   LRM_LAUNCH_CHECK();
   return 0;
