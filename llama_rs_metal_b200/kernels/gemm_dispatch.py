@@ -4,9 +4,9 @@
   (csrc/gemm_bf16_stream.cu); it also takes 17-64 rows when the tensor-core kernel would
   leave most SMs idle and cannot split K (few output columns, epilogue other than "add");
 * more rows (prompts, larger decode batches): the TMA + tcgen05 kernel
-  (csrc/gemm_bf16_umma.cu), with 128 x 128 or 128 x 256 tiles, whichever leaves fewer idle
-  SMs in the last wave; with at most 64 rows and few columns it cuts K into slices that
-  meet by atomic adds in the float32 residual stream;
+  (csrc/gemm_bf16_umma.cu), with 128 x 128 or 128 x 256 tiles, whichever needs less time by a
+  count of rounds over the SMs and the measured cost of a tile; with at most 64 rows and few
+  columns it cuts K into slices that meet by atomic adds in the float32 residual stream;
 * every shape the others refuse (K not a multiple of 8, unaligned views): the
   warp-level tiled kernel (csrc/gemm_bf16_mma.cu), which takes any M, N, K.
 """
@@ -55,9 +55,12 @@ def check_status() -> None:
 def _wide(M: int, N: int) -> bool:
     if umma_width is not None:
         return umma_width == 256
+    # Rounds of tiles over the SMs, times what a tile costs: a 128 x 256 tile has twice the work of
+    # a 128 x 128 one but needs a third less operand traffic from L2 per product, which is what
+    # bounds these kernels; measured, it costs about 1.4 narrow tiles.
     rows = -(-M // 128)
     narrow = -(-(rows * -(-N // 128)) // SM_COUNT)
-    wide = 2 * -(-(rows * -(-N // 256)) // SM_COUNT)
+    wide = 1.4 * -(-(rows * -(-N // 256)) // SM_COUNT)
     return wide <= narrow
 
 
