@@ -1,0 +1,70 @@
+"""Which kernel runs for which geometry: the host-side choices, without a GPU."""
+import pytest
+
+from llama_rs_metal_b200.kernels import attention_dispatch, gemm_dispatch
+
+
+@pytest.fixture(autouse=True)
+def every_cluster_size_launchable(monkeypatch):
+    monkeypatch.setattr(attention_dispatch, "_cluster_launchable", lambda head_dim, size: True)
+
+
+def test_cluster_size_fills_the_device_and_never_exceeds_the_pages():
+    size = attention_dispatch.decode_cluster_size
+    assert size(1, 8, 4, 64, 4096) == 16           # few sequences: the largest cluster
+    assert size(8, 8, 4, 64, 4096) == 8            # 64 clusters x 8 = 512 CTAs, about 4 per SM
+    assert size(64, 8, 4, 64, 4096) == 1           # 512 (sequence, head) pairs already fill it
+    assert size(1, 8, 4, 64, 100) == 2             # two pages: no more CTAs than pages
+    assert size(1, 8, 4, 64, 1) == 1
+    assert size(8, 8, 4, 128, 4096) == 4           # head size 128: two CTAs per SM
+    for seqs in (1, 3, 8, 20, 64, 200):
+        for keys in (1, 64, 65, 1000, 40000):
+            s = size(seqs, 8, 4, 64, keys)
+            assert s in (1, 2, 4, 8, 16) and s <= max(1, -(-keys // 64))
+
+
+def test_cluster_size_respects_what_the_device_can_launch(monkeypatch):
+    monkeypatch.setattr(attention_dispatch, "_cluster_launchable", lambda head_dim, size: size <= 4)
+    assert attention_dispatch.decode_cluster_size(1, 8, 4, 64, 4096) == 4
+
+
+def test_split_count_of_the_separate_kernels():
+    splits = attention_dispatch.decode_splits
+    assert splits(1, 8, 4, 4096, 0) == 64          # one page each
+    assert splits(1, 8, 4, 131072, 0) == 74        # 592 CTAs over 8 pairs
+    assert splits(64, 8, 4, 4096, 0) == 2
+    assert splits(8, 8, 4, 4096, 64) == 2          # a window of 64 keys spans at most two pages
+    assert splits(8, 8, 40, 4096, 0) == 4          # 40 query heads per kv head: three row groups per pair
+
+
+def test_one_launch_or_three():
+    fused = attention_dispatch.decode_prefers_fused
+    assert fused(1, 8, 4, 64, 4096) and fused(8, 8, 4, 64, 4096) and fused(64, 8, 4, 64, 4096)
+    assert fused(64, 8, 4, 64, 32768)              # bound by bandwidth either way: fewer launches win
+    assert not fused(1, 8, 4, 64, 32768)           # 16 CTAs per pair would walk 32 pages each
+    assert not fused(1, 8, 4, 64, 131072)
+    attention_dispatch.force_cluster_size = 2      # tests pin the cluster size: always the one launch
+    try:
+        assert fused(1, 8, 4, 64, 131072)
+    finally:
+        attention_dispatch.force_cluster_size = None
+
+
+def test_tile_width_of_prompt_products():
+    wide = gemm_dispatch._wide
+    assert wide(2048, 3072) and wide(2048, 2048) and wide(2048, 16384) and wide(8192, 2048)
+    assert not wide(256, 2048)                     # 32 narrow tiles keep more SMs busy than 16 wide ones
+    assert not wide(128, 128)
+    gemm_dispatch.umma_width = 128
+    try:
+        assert not wide(2048, 16384)
+    finally:
+        gemm_dispatch.umma_width = None
+
+
+def test_few_rows_plan():
+    plan = gemm_dispatch._few_rows_plan
+    assert plan(64, 16384, 2048, 3) == (True, 1)   # many column tiles: the tensor-core kernel as it is
+    assert plan(64, 3072, 2048, 0) == (False, 1)   # few tiles and nothing to split: the streaming kernel
+    use, slices = plan(64, 2048, 8192, 2)          # adds into the residual: K in slices
+    assert use and 2 <= slices <= 64
