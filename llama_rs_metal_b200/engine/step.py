@@ -123,6 +123,9 @@ class StepRunner:
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self._pool = None
         self.last_launches = 0  # kernels of this library launched by the last step
+        # pinned buffers for the ids of steps that do not wait (two are in flight at most)
+        self._pending_ring: List[PendingPicks] = []
+        self._pending_turn = 0
 
     # -- the public step ----------------------------------------------------------
     def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
@@ -283,9 +286,8 @@ class StepRunner:
         return pending
 
     def _pending_slot(self) -> "PendingPicks":
-        if not hasattr(self, "_pending_ring"):
+        if not self._pending_ring:
             self._pending_ring = [PendingPicks(self.cache.max_slots) for _ in range(4)]
-            self._pending_turn = 0
         slot = self._pending_ring[self._pending_turn % 4]
         self._pending_turn += 1
         return slot
