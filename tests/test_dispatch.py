@@ -11,21 +11,22 @@ def every_cluster_size_launchable(monkeypatch):
 
 def test_cluster_size_fills_the_device_and_never_exceeds_the_pages():
     size = attention_dispatch.decode_cluster_size
-    assert size(1, 8, 4, 64, 4096) == 16           # few sequences: the largest cluster
-    assert size(8, 8, 4, 64, 4096) == 8            # 64 clusters x 8 = 512 CTAs, about 4 per SM
+    assert size(1, 8, 4, 64, 4096) == 14           # few sequences: the largest cluster
+    assert size(8, 8, 4, 64, 4096) == 6            # 64 clusters x 6 = 384 CTAs, under 3 per SM
     assert size(64, 8, 4, 64, 4096) == 1           # 512 (sequence, head) pairs already fill it
     assert size(1, 8, 4, 64, 100) == 2             # two pages: no more CTAs than pages
     assert size(1, 8, 4, 64, 1) == 1
-    assert size(8, 8, 4, 128, 4096) == 4           # head size 128: two CTAs per SM
-    for seqs in (1, 3, 8, 20, 64, 200):
+    assert size(8, 8, 4, 128, 4096) == 4           # head size 128: two CTAs per SM fit
+    for seqs in (1, 3, 8, 20, 33, 64, 200):
         for keys in (1, 64, 65, 1000, 40000):
             s = size(seqs, 8, 4, 64, keys)
-            assert s in (1, 2, 4, 8, 16) and s <= max(1, -(-keys // 64))
+            assert 1 <= s <= attention_dispatch.MAX_CLUSTER and s <= max(1, -(-keys // 64))
+            assert s == 1 or seqs * 8 * s <= 4 * 148      # what runs at once
 
 
 def test_cluster_size_respects_what_the_device_can_launch(monkeypatch):
-    monkeypatch.setattr(attention_dispatch, "_cluster_launchable", lambda head_dim, size: size <= 4)
-    assert attention_dispatch.decode_cluster_size(1, 8, 4, 64, 4096) == 4
+    monkeypatch.setattr(attention_dispatch, "_cluster_launchable", lambda head_dim, size: size <= 5)
+    assert attention_dispatch.decode_cluster_size(1, 8, 4, 64, 4096) == 5
 
 
 def test_split_count_of_the_separate_kernels():
@@ -41,7 +42,7 @@ def test_one_launch_or_three():
     fused = attention_dispatch.decode_prefers_fused
     assert fused(1, 8, 4, 64, 4096) and fused(8, 8, 4, 64, 4096) and fused(64, 8, 4, 64, 4096)
     assert fused(64, 8, 4, 64, 32768)              # bound by bandwidth either way: fewer launches win
-    assert not fused(1, 8, 4, 64, 32768)           # 16 CTAs per pair would walk 32 pages each
+    assert not fused(1, 8, 4, 64, 32768)           # 14 CTAs per pair would walk 37 pages each
     assert not fused(1, 8, 4, 64, 131072)
     attention_dispatch.force_cluster_size = 2      # tests pin the cluster size: always the one launch
     try:

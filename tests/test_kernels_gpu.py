@@ -326,7 +326,7 @@ def test_float32_decode_equals_prefill_bit_for_bit(ops):
         assert torch.equal(pre[-1], dec[b])
 
 
-@pytest.mark.parametrize("cluster", [None, 1, 2, 8])
+@pytest.mark.parametrize("cluster", [None, 1, 2, 7, 8, 16])
 @pytest.mark.parametrize("Hq,Hk,d,rotary", [(32, 8, 64, 64), (8, 2, 128, 128), (3, 1, 32, 32), (40, 2, 64, 32),
                                              (6, 3, 128, 64), (6, 3, 128, 96), (4, 4, 64, 0)])
 def test_attention_decode_fused_rotates_stores_attends_and_merges(ops, Hq, Hk, d, rotary, cluster):
