@@ -217,24 +217,36 @@ LRM_API int lrm_gemm_bf16_stream_supports(int M, int N, int K) {
   return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 ? 1 : 0;
 }
 
-LRM_API int lrm_gemm_bf16_stream(const void* X, const void* W, void* out, int M, int N, int K,
-                                 int mode, cudaStream_t stream) {
+// `warps` (1, 2, 4, 8, 16) and `splits` (K slices, add epilogue only) choose the launch shape;
+// 0 leaves the choice to the rule below.
+LRM_API int lrm_gemm_bf16_stream_shaped(const void* X, const void* W, void* out, int M, int N, int K,
+                                        int mode, int warps, int splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lrm_gemm_bf16_stream_supports(M, N, K)) return LRM_UNSUPPORTED;
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0)) return LRM_BAD_ARGUMENT;
+  if (warps < 0 || warps > 16 || splits < 0 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
   // The add epilogue may cut K across CTAs (slices of at least 1024) until about 28 warps per SM
   // stream weights; then enough warps per CTA that each has at least one chunk.
   const int tiles = (N + 15) / 16;
-  int splits = 1;
-  if (mode == 2)
-    while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 1024) splits *= 2;
+  if (splits == 0) {
+    splits = 1;
+    if (mode == 2)
+      while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 1024) splits *= 2;
+  }
   const int chunks = ((K + splits - 1) / splits + 127) / 128;
-  int warps = 4;
-  while (warps < 16 && tiles * splits * warps < 148 * 12 && warps * 2 <= chunks) warps *= 2;
-  while (warps > 1 && warps > chunks) warps /= 2;
+  if (warps == 0) {
+    warps = 4;
+    while (warps < 16 && tiles * splits * warps < 148 * 16 && warps * 2 <= chunks) warps *= 2;
+    while (warps > 1 && warps > chunks) warps /= 2;
+  }
   if (M <= 8) return launch_stream<1>(X, W, out, M, N, K, mode, warps, splits, stream);
   if (M <= 16) return launch_stream<2>(X, W, out, M, N, K, mode, warps, splits, stream);
   if (M <= 32) return launch_stream<4>(X, W, out, M, N, K, mode, warps, splits, stream);
   return launch_stream<8>(X, W, out, M, N, K, mode, warps < 8 ? warps : 8, splits, stream);
+}
+
+LRM_API int lrm_gemm_bf16_stream(const void* X, const void* W, void* out, int M, int N, int K,
+                                 int mode, cudaStream_t stream) {
+  return lrm_gemm_bf16_stream_shaped(X, W, out, M, N, K, mode, 0, 0, stream);
 }

@@ -66,6 +66,7 @@ def _wide(M: int, N: int) -> bool:
 
 STREAM_ROWS = 16  # up to this many rows the streaming kernel is the faster one
 force_stream = False  # tests: keep 17-64 rows on the streaming kernel
+stream_shape = None  # tests and tuning: (warps per CTA, K slices) of the streaming kernel instead of its own rule
 
 
 def _few_rows_plan(M: int, N: int, K: int, mode: int):
@@ -95,8 +96,9 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
         stream_ok = not use_umma
         wide = False if umma_width is None else wide
     if stream_ok:
-        _done(lib.lrm_gemm_bf16_stream(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, _stream()),
-              "gemm_bf16_stream")
+        warps, slices = stream_shape if stream_shape is not None else (0, 0)
+        _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, warps,
+                                              slices if mode == 2 else 0, _stream()), "gemm_bf16_stream")
         return
     if umma_ok:
         _status_dirty = True
