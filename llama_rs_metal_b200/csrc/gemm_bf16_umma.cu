@@ -1,11 +1,14 @@
 // bfloat16 matrix product on the 5th-generation tensor cores:
 //   D[M,N] = X[M,K] . W[N,K]^T, float32 accumulation in tensor memory.
 //
-// A persistent kernel, one CTA per SM, each working through 128 x BN tiles.
-// Operand tiles (128 x 64 of X, BN x 64 of W, 128-byte swizzle) are brought
+// A persistent kernel, one CTA per SM, each working through (128 MT) x BN tiles.
+// Operand tiles (128 MT x 64 of X, BN x 64 of W, 128-byte swizzle) are brought
 // into a ring of shared-memory stages by TMA (cp.async.bulk.tensor) issued by
 // one thread; one other thread issues tcgen05.mma (M 128, N = BN, K 16) from
-// shared-memory descriptors into one of two TMEM accumulators of BN columns;
+// shared-memory descriptors into TMEM accumulators of BN columns, MT of them per tile
+// (one per 128 rows, sharing the W tile: a 256 x 256 tile needs a third less operand traffic
+// from L2 per product than a 128 x 256 one, and that traffic is what bounds these products);
+// with MT BN <= 256 two sets of accumulators alternate;
 // tcgen05.commit signals both "stage free" to the loader and "accumulator
 // ready" to the epilogue. Four epilogue warps read their 32 TMEM lanes
 // (tcgen05.ld, one row per thread) while the next tile's MMAs fill the other
@@ -185,27 +188,29 @@ __device__ __forceinline__ void store_piece(const uint32_t (&r)[32], void* __res
 // Persistent: CTA b works on items b, b + gridDim.x, ...; an item is (K slice, column tile, row
 // tile) with the row tile fastest, so CTAs that run together share a tile of W in L2.
 // Warp 0: TMA loader. Warp 1: MMA issuer (and owner of the tensor memory). Warps 2-5: epilogue.
-// Two accumulators of BN columns alternate, so the epilogue of one item runs under the MMAs of
-// the next.
-template <int BN, int STAGES>
+// Where two sets of accumulators fit in the 512 columns of tensor memory they alternate, so the
+// epilogue of one item runs under the MMAs of the next; a 256 x 256 tile fills it alone.
+template <int BN, int STAGES, int MT>
 __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
     void* __restrict__ out, int M, int N, int K, int mode, int kb_per_split, int splits,
     int* __restrict__ status) {
-  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t SET = MT * BN;                      // columns of one set of accumulators
+  constexpr uint32_t NBUF = 2 * SET <= 512 ? 2 : 1;      // sets that fit in tensor memory
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // operand ring first (1024-byte aligned for the swizzle), then barriers
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(tiles + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;   // [2] accumulator written
-  uint64_t* acc_free = acc_full + 2;     // [2] accumulator read back by all four epilogue warps
+  uint64_t* acc_full = empty + STAGES;   // [2] accumulators written
+  uint64_t* acc_free = acc_full + 2;     // [2] accumulators read back by all four epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
   volatile int* bail = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int m_tiles = (M + MT * BM - 1) / (MT * BM), n_tiles = (N + BN - 1) / BN;
   const int items = m_tiles * n_tiles * splits;
   const int k_blocks = (K + BK - 1) / BK;
   const bool atomic = splits > 1;
@@ -224,7 +229,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_alloc(tmem_slot, NBUF * SET);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -237,7 +242,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
       // ---- loader: one thread feeds the ring with TMA, straight through all items
       uint32_t it = 0;  // k blocks issued so far by this CTA
       for (int item = blockIdx.x; item < items && !*bail; item += gridDim.x) {
-        const int m0 = (item % m_tiles) * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
+        const int m0 = (item % m_tiles) * MT * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
         const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
         const int num_kb = min(k_blocks - kb_begin, kb_per_split);
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -248,7 +253,10 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
             break;
           }
           mbar_expect_tx(full + s, STAGE_BYTES);
-          tma_load_2d(tiles + s * STAGE_BYTES, &map_x, full + s, (kb_begin + kb) * BK, m0);
+#pragma unroll
+          for (int i = 0; i < MT; ++i)  // 128 rows of X per accumulator (rows beyond M read as zero)
+            tma_load_2d(tiles + s * STAGE_BYTES + i * BM * BK * 2, &map_x, full + s, (kb_begin + kb) * BK,
+                        m0 + i * BM);
           tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &map_w, full + s, (kb_begin + kb) * BK, n0);
         }
       }
@@ -270,14 +278,14 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
       for (int item = blockIdx.x; item < items && !*bail; item += gridDim.x, ++local) {
         const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
         const int num_kb = min(k_blocks - kb_begin, kb_per_split);
-        const uint32_t acc = local & 1, use = local >> 1;
-        // the epilogue must have emptied this accumulator (its previous use)
+        const uint32_t acc = local % NBUF, use = local / NBUF;
+        // the epilogue must have emptied these accumulators (their previous use)
         if (use > 0 && !mbar_wait(acc_free + acc, (use - 1) & 1, status, kStuckTmemFree)) {
           *bail = 1;
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + acc * BN;
+        const uint32_t tmem_d = tmem_base + acc * SET;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full + s, (it / STAGES) & 1, status, kStuckFull)) {
@@ -288,8 +296,10 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
           const uint32_t a = smem_u32(tiles + s * STAGE_BYTES), b = a + A_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_d, smem_desc(a + k * UMMA_K * 2), smem_desc(b + k * UMMA_K * 2), idesc,
-                      (kb > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+            for (int i = 0; i < MT; ++i)  // the 128-row blocks of X share the tile of W
+              umma_bf16(tmem_d + i * BN, smem_desc(a + i * BM * BK * 2 + k * UMMA_K * 2),
+                        smem_desc(b + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           umma_commit(empty + s);  // arrives when these MMAs have finished reading the stage
         }
         umma_commit(acc_full + acc);  // arrives when every MMA issued so far has completed
@@ -301,22 +311,22 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
     const int quarter = warp & 3;
     uint32_t local = 0;
     for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
-      const int m0 = (item % m_tiles) * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
+      const int m0 = (item % m_tiles) * MT * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
       const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
       const int num_kb = min(k_blocks - kb_begin, kb_per_split);
-      const uint32_t acc = local & 1, use = local >> 1;
+      const uint32_t acc = local % NBUF, use = local / NBUF;
       if (*bail || !mbar_wait(acc_full + acc, use & 1, status, kStuckAccumulator)) {
         *bail = 1;
         break;
       }
       tc_fence_after();
-      const int m = m0 + quarter * 32 + lane;
       if (num_kb > 0) {  // an empty slice adds nothing
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < MT * BN / 32; ++c) {  // accumulator c / (BN / 32) holds rows 128 (c / (BN / 32)) ...
+          const int m = m0 + (c / (BN / 32)) * BM + quarter * 32 + lane;
           uint32_t r[32];
-          tmem_load32(tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
-          store_piece(r, out, m, n0 + c * 32, M, N, mode, atomic);
+          tmem_load32(tmem_base + acc * SET + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
+          store_piece(r, out, m, n0 + (c % (BN / 32)) * 32, M, N, mode, atomic);
         }
       }
       tc_fence_before();
@@ -326,7 +336,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (warp == 1) tmem_dealloc(tmem_base, NBUF * SET);
 }
 
 // ------------------------------------------------------------------------- host side
@@ -363,19 +373,19 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows)
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT = 1>
 int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode, int splits,
                 int* status, cudaStream_t stream) {
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
-  constexpr int smem = STAGES * (BM * BK * 2 + BN * BK * 2) + 1024 + 256;
-  auto kernel = gemm_bf16_umma_kernel<BN, STAGES>;
+  constexpr int smem = STAGES * (MT * BM * BK * 2 + BN * BK * 2) + 1024 + 256;
+  auto kernel = gemm_bf16_umma_kernel<BN, STAGES, MT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
   const int k_blocks = (K + BK - 1) / BK;
   const int kb_per_split = (k_blocks + splits - 1) / splits;
   const int real_splits = (k_blocks + kb_per_split - 1) / kb_per_split;
-  const long long items = static_cast<long long>((N + BN - 1) / BN) * ((M + BM - 1) / BM) * real_splits;
+  const long long items = static_cast<long long>((N + BN - 1) / BN) * ((M + MT * BM - 1) / (MT * BM)) * real_splits;
   static int sm_count = 0;
   if (sm_count == 0) {
     int device = 0;
@@ -399,13 +409,16 @@ LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
 // `status`: one int in device memory, 0 before the launch; a kernel that gave up on a wait
 // writes a nonzero code there (the result is then invalid and the caller must raise).
 // `splits` > 1 cuts K into that many slices that meet by atomic adds (epilogue 2 only).
+// `tile`: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256 (rows x columns of the output per item).
 LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode,
-                               int wide, int splits, int* status, cudaStream_t stream) {
+                               int tile, int splits, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
   if (splits < 1 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
-  if (wide) return launch_umma<256, 4>(X, W, out, M, N, K, mode, splits, status, stream);
+  if (tile < 0 || tile > 2) return LRM_BAD_ARGUMENT;
+  if (tile == 2) return launch_umma<256, 3, 2>(X, W, out, M, N, K, mode, splits, status, stream);
+  if (tile == 1) return launch_umma<256, 4>(X, W, out, M, N, K, mode, splits, status, stream);
   return launch_umma<128, 6>(X, W, out, M, N, K, mode, splits, status, stream);
 }

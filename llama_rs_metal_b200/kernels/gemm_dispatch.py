@@ -4,8 +4,8 @@
   (csrc/gemm_bf16_stream.cu); it also takes 17-64 rows when the tensor-core kernel would
   leave most SMs idle and cannot split K (few output columns, epilogue other than "add");
 * more rows (prompts, larger decode batches): the TMA + tcgen05 kernel
-  (csrc/gemm_bf16_umma.cu), with 128 x 128 or 128 x 256 tiles, whichever needs less time by a
-  count of rounds over the SMs and the measured cost of a tile; with at most 64 rows and few
+  (csrc/gemm_bf16_umma.cu), with 128 x 128, 128 x 256 or 256 x 256 tiles, whichever needs less
+  time by a count of rounds over the SMs and the measured cost of a tile; with at most 64 rows and few
   columns it cuts K into slices that meet by atomic adds in the float32 residual stream;
 * every shape the others refuse (K not a multiple of 8, unaligned views): the
   warp-level tiled kernel (csrc/gemm_bf16_mma.cu), which takes any M, N, K.
@@ -22,7 +22,7 @@ from .ops import _done, _ptr, _stream  # noqa: PLC2701  (same package)
 
 SM_COUNT = 148
 force_tiled = False  # tests switch the fast kernels off to compare both paths
-umma_width: Optional[int] = None  # tests pin the tile width (128 or 256)
+umma_width: Optional[int] = None  # tests pin the tile: 128 (128 x 128), 256 (128 x 256), 512 (256 x 256)
 
 _status: Dict[int, torch.Tensor] = {}
 _status_dirty = False
@@ -52,16 +52,32 @@ def check_status() -> None:
             raise LlamaError(f"{kernel} gave up waiting for {names.get(code, code)}; its result is invalid")
 
 
-def _wide(M: int, N: int) -> bool:
+# What an output tile costs relative to a 128 x 128 one. Operand traffic from L2 bounds these
+# products (measured: the tensor pipe is busy 38-44 % of the time with 128 x 128 tiles, 66-71 %
+# with 128 x 256), so a larger tile does more work per byte. A 256 x 256 tile fills the tensor
+# memory, so its epilogue does not run under the next tile's MMAs: it pays only when K is long
+# (measured at 8,192 rows: 0.85 of the 128 x 256 time at K = 8192, 1.05 at K = 2048 with a plain
+# epilogue, 1.3 with the SiLU gate).
+def _tile_costs(K: int, mode: int):
+    k_blocks = max(1, -(-K // 64))
+    epilogue = 1.1 if mode == 3 else 0.55
+    return ((128, 128, 1.0), (128, 256, 1.4), (256, 256, 1.4 * (1.55 + epilogue * 32 / k_blocks)))
+
+
+def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0) -> int:
+    """0: 128 x 128, 1: 128 x 256, 2: 256 x 256 output tiles: least rounds over the SMs times cost."""
     if umma_width is not None:
-        return umma_width == 256
-    # Rounds of tiles over the SMs, times what a tile costs: a 128 x 256 tile has twice the work of
-    # a 128 x 128 one but needs a third less operand traffic from L2 per product, which is what
-    # bounds these kernels; measured, it costs about 1.4 narrow tiles.
-    rows = -(-M // 128)
-    narrow = -(-(rows * -(-N // 128)) // SM_COUNT)
-    wide = 1.4 * -(-(rows * -(-N // 256)) // SM_COUNT)
-    return wide <= narrow
+        return {128: 0, 256: 1, 512: 2}[umma_width]
+    best, best_cost = 0, None
+    for index, (rows, columns, cost) in enumerate(_tile_costs(K, mode)):
+        rounds = -(-(-(-M // rows) * -(-N // columns)) // SM_COUNT)
+        if best_cost is None or rounds * cost < best_cost:
+            best, best_cost = index, rounds * cost
+    return best
+
+
+def _wide(M: int, N: int) -> bool:
+    return tile_choice(M, N) >= 1
 
 
 STREAM_ROWS = 16  # up to this many rows the streaming kernel is the faster one
@@ -90,11 +106,11 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
     fast = not force_tiled and aligned
     stream_ok = fast and lib.lrm_gemm_bf16_stream_supports(M, N, K)
     umma_ok = fast and lib.lrm_gemm_bf16_umma_supports(M, N, K)
-    wide, splits = _wide(M, N), 1
+    tile, splits = tile_choice(M, N, K, mode), 1
     if stream_ok and umma_ok and M > STREAM_ROWS and not force_stream:
         use_umma, splits = _few_rows_plan(M, N, K, mode)
         stream_ok = not use_umma
-        wide = False if umma_width is None else wide
+        tile = 0 if umma_width is None else tile
     if stream_ok:
         warps, slices = stream_shape if stream_shape is not None else (0, 0)
         _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, warps,
@@ -103,7 +119,7 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
     if umma_ok:
         _status_dirty = True
         _done(lib.lrm_gemm_bf16_umma(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode,
-                                     1 if wide else 0, splits, _ptr(_status_word(x.device)), _stream()),
+                                     tile, splits, _ptr(_status_word(x.device)), _stream()),
               "gemm_bf16_umma")
         return
     _done(lib.lrm_gemm_bf16_mma(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, _stream()),

@@ -51,14 +51,17 @@ def test_one_launch_or_three():
         attention_dispatch.force_cluster_size = None
 
 
-def test_tile_width_of_prompt_products():
-    wide = gemm_dispatch._wide
-    assert wide(2048, 3072) and wide(2048, 2048) and wide(2048, 16384) and wide(8192, 2048)
-    assert not wide(256, 2048)                     # 32 narrow tiles keep more SMs busy than 16 wide ones
-    assert not wide(128, 128)
+def test_tile_shape_of_prompt_products():
+    choice = gemm_dispatch.tile_choice              # 0: 128 x 128, 1: 128 x 256, 2: 256 x 256
+    assert choice(2048, 16384, 2048, 3) == 1 and choice(2048, 3072, 2048, 0) == 1
+    assert choice(2048, 2048, 8192, 2) == 1         # 64 large tiles would leave most SMs idle
+    assert choice(8192, 2048, 8192, 2) == 2         # long K: the 256 x 256 tile pays
+    assert choice(8192, 16384, 2048, 3) == 1        # short K and a costly epilogue: it does not
+    assert choice(256, 2048) == 0                   # 32 small tiles keep more SMs busy than 16 or 8 larger ones
+    assert choice(128, 128) == 0
     gemm_dispatch.umma_width = 128
     try:
-        assert not wide(2048, 16384)
+        assert choice(2048, 16384, 2048, 3) == 0
     finally:
         gemm_dispatch.umma_width = None
 
