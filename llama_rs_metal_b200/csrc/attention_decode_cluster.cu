@@ -93,8 +93,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
       const size_t page = static_cast<size_t>(table[page_index]);
       const size_t base = (page * kv_heads + kh) * kTile * D;
       const int stage = i % kStages;
-      load_tile<D>(Ks + stage * TILE, k_pages + base, D, len - page_index * kTile);
-      load_tile<D>(Vs + stage * TILE, v_pages + base, D, len - page_index * kTile);
+      load_page<D>(Ks + stage * TILE, k_pages + base, len - page_index * kTile);
+      load_page<D>(Vs + stage * TILE, v_pages + base, len - page_index * kTile);
     }
     cp_async_commit();
   };
@@ -191,12 +191,19 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
     scores<D, 2>(s, qa, Ks + stage * TILE + 16 * warp * STRIDE);
+    if ((page_index + 1) * kTile <= len) {  // a full page: every key counts
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = page_index * kTile + 16 * warp + 8 * nt + 2 * t + (e & 1);
-        s[nt][e] = key < len ? s[nt][e] * scale_log2 : -INFINITY;
+        for (int e = 0; e < 4; ++e) s[nt][e] *= scale_log2;
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = page_index * kTile + 16 * warp + 8 * nt + 2 * t + (e & 1);
+          s[nt][e] = key < len ? s[nt][e] * scale_log2 : -INFINITY;
+        }
       }
     }
     softmax_update<D, 2>(s, o, m, l);

@@ -58,6 +58,26 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat1
   }
 }
 
+// The same for one page of the cache (64 rows of D elements, contiguous): a thread's copies differ
+// by constants, and a full page needs no test per row.
+template <int D>
+__device__ __forceinline__ void load_page(__nv_bfloat16* dst, const __nv_bfloat16* src, int valid_rows) {
+  constexpr int STRIDE = D + 8, CHUNKS = D / 8, ROWS = kThreads / CHUNKS;  // rows covered per pass
+  const int r0 = threadIdx.x / CHUNKS, c8 = (threadIdx.x % CHUNKS) * 8;
+  const __nv_bfloat16* s = src + r0 * D + c8;
+  __nv_bfloat16* d = dst + r0 * STRIDE + c8;
+  if (valid_rows >= kTile) {
+#pragma unroll
+    for (int i = 0; i < kTile / ROWS; ++i) cp_async16(d + i * ROWS * STRIDE, s + i * ROWS * D, 16);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kTile / ROWS; ++i) {
+      const bool ok = r0 + i * ROWS < valid_rows;
+      cp_async16(d + i * ROWS * STRIDE, ok ? s + i * ROWS * D : src, ok ? 16 : 0);
+    }
+  }
+}
+
 // Query fragments of 16 rows x D from global memory: row r lives at base + r * pitch.
 template <int D>
 __device__ __forceinline__ void load_q(uint32_t (&qa)[D / 16][4], const __nv_bfloat16* base,

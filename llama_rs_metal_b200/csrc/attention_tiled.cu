@@ -146,8 +146,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   auto issue = [&](int page_index, int stage) {
     const size_t page = static_cast<size_t>(table[page_index]);
     const size_t base = (page * kv_heads + kh) * kTile * D;
-    load_tile<D>(Ks + stage * TILE, k_pages + base, D, len - page_index * kTile);
-    load_tile<D>(Vs + stage * TILE, v_pages + base, D, len - page_index * kTile);
+    load_page<D>(Ks + stage * TILE, k_pages + base, len - page_index * kTile);
+    load_page<D>(Vs + stage * TILE, v_pages + base, len - page_index * kTile);
     cp_async_commit();
   };
   // Lengths, slots and the page table were set before the step; only q and the newest
