@@ -206,7 +206,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
         }
       }
     }
-    softmax_update<D, 2>(s, o, m, l);
+    if (rows > 8) softmax_update<D, 2, 2>(s, o, m, l);
+    else softmax_update<D, 2, 1>(s, o, m, l);  // query heads 8..15 of the tile are padding
     weighted_values<D, 2>(o, s, Vs + stage * TILE + 16 * warp * STRIDE);
     __syncthreads();
   }

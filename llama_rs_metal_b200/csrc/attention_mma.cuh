@@ -142,13 +142,21 @@ __device__ __forceinline__ void weighted_values(float (&o)[D / 8][4], const floa
   }
 }
 
+// 2^x on the special-function unit (x <= 0 here; results below the normal range flush to zero).
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One streaming-softmax update of rows g and g+8 with NT score tiles (already masked to -inf
 // where a key is not visible). m, l: running max (log2 domain) and this thread's share of the mass.
-template <int D, int NT>
+// HALVES = 1 leaves rows g+8 alone (a caller whose rows 8..15 are padding).
+template <int D, int NT, int HALVES = 2>
 __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
                                                float (&l)[2]) {
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
+  for (int half = 0; half < HALVES; ++half) {
     float mx = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * half], s[nt][2 * half + 1]));
@@ -156,12 +164,12 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[D /
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[half], mx);
     const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no visible key yet
-    const float alpha = exp2f(m[half] - m_use);
+    const float alpha = exp2_fast(m[half] - m_use);
     float sum = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
-      s[nt][2 * half] = exp2f(s[nt][2 * half] - m_use);
-      s[nt][2 * half + 1] = exp2f(s[nt][2 * half + 1] - m_use);
+      s[nt][2 * half] = exp2_fast(s[nt][2 * half] - m_use);
+      s[nt][2 * half + 1] = exp2_fast(s[nt][2 * half + 1] - m_use);
       sum += s[nt][2 * half] + s[nt][2 * half + 1];
     }
     l[half] = l[half] * alpha + sum;
@@ -171,6 +179,10 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&o)[D /
       o[dn][2 * half] *= alpha;
       o[dn][2 * half + 1] *= alpha;
     }
+  }
+  if (HALVES == 1) {  // rows g+8 are padding: their probabilities must not reach the products
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) s[nt][2] = s[nt][3] = 0.f;
   }
 }
 
