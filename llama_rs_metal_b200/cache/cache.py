@@ -61,8 +61,10 @@ class KeyValueGroup:
                                        device=device)
         self.dirty = False
         shape = (pages, request.kv_heads, page_size, request.head_dim)
-        self.k = {e: torch.empty(shape, dtype=dtype, device=device) for e in entries}
-        self.v = {e: torch.empty(shape, dtype=dtype, device=device) for e in entries}
+        # zeroed once: a kernel may load rows of a page that no token was ever stored in (they are
+        # masked, but 0 x NaN would still be NaN)
+        self.k = {e: torch.zeros(shape, dtype=dtype, device=device) for e in entries}
+        self.v = {e: torch.zeros(shape, dtype=dtype, device=device) for e in entries}
 
     def first_kept_page(self, length: int) -> int:
         """Lowest logical page a sequence of `length` tokens still needs."""

@@ -172,9 +172,9 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
   for (int i = 0; i < n_mine; ++i) {
     const int stage = i % kStages;
     const int page_index = rank + i * n_ranks;
-    issue(i + kStages - 1);           // into the slot that iteration i - 1 finished with
-    cp_async_wait<kStages - 1>();     // all but the newest kStages - 1 groups: page i is here
-    __syncthreads();
+    cp_async_wait<kStages - 2>();     // all but the newest kStages - 2 groups: page i is here
+    __syncthreads();                  // ... for every thread, and everyone is done with page i - 1
+    issue(i + kStages - 1);           // into the slot page i - 1 was in
     if (page_index == n_pages - 1) {  // the owner's last page: put the new row where its tile expects it
       __nv_bfloat16* k_row = Ks + stage * TILE + new_row * STRIDE;
       __nv_bfloat16* v_row = Vs + stage * TILE + new_row * STRIDE;
@@ -209,7 +209,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
     if (rows > 8) softmax_update<D, 2, 2>(s, o, m, l);
     else softmax_update<D, 2, 1>(s, o, m, l);  // query heads 8..15 of the tile are padding
     weighted_values<D, 2>(o, s, Vs + stage * TILE + 16 * warp * STRIDE);
-    __syncthreads();
   }
   cp_async_wait<0>();  // only empty groups can be left
   if (n_ranks == 1) pdl_trigger();  // the cache has been read: the next kernel may be scheduled

@@ -59,20 +59,23 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* dst, const __nv_bfloat1
 }
 
 // The same for one page of the cache (64 rows of D elements, contiguous): a thread's copies differ
-// by constants, and a full page needs no test per row.
+// by constants, and a page whose rows all count needs no test per row. Rows outside
+// [first_row, valid_rows) are zero-filled: behind a sequence's end, and before a window's first
+// key, the cache may hold anything (rows never written, even NaN bit patterns).
 template <int D>
-__device__ __forceinline__ void load_page(__nv_bfloat16* dst, const __nv_bfloat16* src, int valid_rows) {
+__device__ __forceinline__ void load_page(__nv_bfloat16* dst, const __nv_bfloat16* src, int valid_rows,
+                                          int first_row = 0) {
   constexpr int STRIDE = D + 8, CHUNKS = D / 8, ROWS = kThreads / CHUNKS;  // rows covered per pass
   const int r0 = threadIdx.x / CHUNKS, c8 = (threadIdx.x % CHUNKS) * 8;
   const __nv_bfloat16* s = src + r0 * D + c8;
   __nv_bfloat16* d = dst + r0 * STRIDE + c8;
-  if (valid_rows >= kTile) {
+  if (valid_rows >= kTile && first_row <= 0) {
 #pragma unroll
     for (int i = 0; i < kTile / ROWS; ++i) cp_async16(d + i * ROWS * STRIDE, s + i * ROWS * D, 16);
   } else {
 #pragma unroll
     for (int i = 0; i < kTile / ROWS; ++i) {
-      const bool ok = r0 + i * ROWS < valid_rows;
+      const bool ok = r0 + i * ROWS < valid_rows && r0 + i * ROWS >= first_row;
       cp_async16(d + i * ROWS * STRIDE, ok ? s + i * ROWS * D : src, ok ? 16 : 0);
     }
   }

@@ -146,8 +146,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
   auto issue = [&](int page_index, int stage) {
     const size_t page = static_cast<size_t>(table[page_index]);
     const size_t base = (page * kv_heads + kh) * kTile * D;
-    load_page<D>(Ks + stage * TILE, k_pages + base, len - page_index * kTile);
-    load_page<D>(Vs + stage * TILE, v_pages + base, len - page_index * kTile);
+    load_page<D>(Ks + stage * TILE, k_pages + base, len - page_index * kTile, first_key - page_index * kTile);
+    load_page<D>(Vs + stage * TILE, v_pages + base, len - page_index * kTile, first_key - page_index * kTile);
     cp_async_commit();
   };
   // Lengths, slots and the page table were set before the step; only q and the newest
@@ -169,32 +169,34 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
 
   for (int p = p_begin; p < p_end; ++p) {
     const int stage = (p - p_begin) & 1;
-    if (p + 1 < p_end) {
-      issue(p + 1, stage ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    cp_async_wait<0>();  // page p is here
+    __syncthreads();     // ... for every thread, and everyone is done with page p - 1
+    if (p + 1 < p_end) issue(p + 1, stage ^ 1);  // into the buffer page p - 1 was in
     float s[2][4];
 #pragma unroll
     for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
     scores<D, 2>(s, qa, Ks + stage * TILE + 16 * warp * STRIDE);
+    if ((p + 1) * kTile <= len && p * kTile >= first_key) {  // a page wholly inside the visible range
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int key = p * kTile + 16 * warp + 8 * nt + 2 * t + (e & 1);
-        const bool visible = key < len && key >= first_key;
-        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+        for (int e = 0; e < 4; ++e) s[nt][e] *= scale_log2;
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int key = p * kTile + 16 * warp + 8 * nt + 2 * t + (e & 1);
+          const bool visible = key < len && key >= first_key;
+          s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+        }
       }
     }
     if (rows > 8) softmax_update<D, 2, 2>(s, o, m, l);
     else softmax_update<D, 2, 1>(s, o, m, l);  // query heads 8..15 of the tile are padding
     weighted_values<D, 2>(o, s, Vs + stage * TILE + 16 * warp * STRIDE);
-    __syncthreads();
   }
 
   pdl_trigger();  // the cache has been read: the next kernel may be scheduled during the merge

@@ -312,6 +312,15 @@ def test_attention_decode_window_edge(ops, kernel_choice, dtype):
     close(got, plain_decode(q, ks, vs, window).view(2, 4, 32), TOL[dtype], "window edge")
     for b, n in enumerate(lengths):
         close(got[b, 0], vs[b][n - window, 0].double(), 2e-2, "the key at the window's edge")
+    # rows before the window may never have been written (a prompt longer than the window stores
+    # only its tail): whatever they hold, even NaN, must not reach the result
+    for b, n in enumerate(lengths):
+        for pos in range(n - window):
+            page = int(table[slots[b], pos // 64])
+            view.k[page, :, pos % 64] = float("nan")
+            view.v[page, :, pos % 64] = float("nan")
+    again = ops.attention_decode(q, view, i32(slots), i32(lengths), max(lengths), 32 ** -0.5, window).view(2, 4, 32)
+    assert torch.equal(again, got)
 
 
 def test_float32_decode_equals_prefill_bit_for_bit(ops):
