@@ -107,7 +107,7 @@ def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, ma
     decode step's attention. A cluster has at most 16 CTAs, so a few sequences with a long context
     leave each CTA with many pages to walk, while the separate kernels may cut a sequence into as
     many splits as fill the device. Measured costs: about 8 us fixed for the cluster kernel, 17 us
-    for the three separate launches, and 0.9 us per page a CTA walks (CTAs beyond what the device
+    for the three separate launches, and 0.55 us per page a CTA walks (CTAs beyond what the device
     holds at once wait their turn), and neither way reads the cache faster than about 6 TB/s."""
     if force_cluster_size is not None:
         return True
@@ -119,7 +119,7 @@ def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, ma
     stream = pairs * pages * (4 * 64 * head_dim) / 6.0e6            # us to read every K/V page at 6 TB/s
 
     def walk(ctas_per_pair: int) -> float:  # more CTAs than fit run in turns
-        return max(stream, 0.9 * -(-pages // ctas_per_pair) * max(1.0, pairs * ctas_per_pair / slots))
+        return max(stream, 0.55 * -(-pages // ctas_per_pair) * max(1.0, pairs * ctas_per_pair / slots))
 
     return 8.0 + walk(cluster) <= 17.0 + walk(splits)
 
