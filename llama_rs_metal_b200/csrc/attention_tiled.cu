@@ -121,6 +121,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     const int* __restrict__ page_table, int table_stride, const int* __restrict__ slots,
     const int* __restrict__ kv_lens, int q_heads, int kv_heads, int row_groups, float scale_log2,
     int window, int n_splits) {
+  pdl_trigger();  // the next kernel may be scheduled at once; it waits for this one where it must
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -199,7 +200,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     weighted_values<D, 2>(o, s, Vs + stage * TILE + 16 * warp * STRIDE);
   }
 
-  pdl_trigger();  // the cache has been read: the next kernel may be scheduled during the merge
   // Combine the four warps (each saw 16 keys of every page) through shared memory, which the
   // K/V tiles no longer need: per warp [16 rows][D + 2] floats.
   __syncthreads();

@@ -56,6 +56,8 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
     const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
     int M, int N, int K_total, int mode, int k_per_split) {
   extern __shared__ float red[];  // [WARPS][NT][32 lanes][4]
+  pdl_trigger();  // the next kernel may be scheduled at once (its CTAs fetch their first weights while
+                  // this kernel streams); it waits for this one where it must
   constexpr int kChunk = Chunk<NT>::kK, kSub = kChunk / 32;  // kSub: 16-byte pieces per thread and row
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -133,7 +135,6 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
     }
   }
 
-  pdl_trigger();  // the stream is done: the next kernel may be scheduled while the sums are added
   // add the warps' partial sums in warp order
 #pragma unroll
   for (int j = 0; j < NT; ++j)

@@ -45,6 +45,8 @@ __global__ void pick_pieces_kernel(const float* __restrict__ logits, float* __re
   __shared__ float s_value[32];
   __shared__ int s_id[32];
   __shared__ int s_bad;
+  pdl_trigger();  // let the next kernel be scheduled; it waits for this one where it must
+  pdl_wait();
   const int row = blockIdx.y;
   const float* x = logits + static_cast<size_t>(row) * vocab;
   const uint64_t key = GUMBEL ? static_cast<uint64_t>(keys[row]) : 0ull;
@@ -86,6 +88,8 @@ __global__ void pick_pieces_kernel(const float* __restrict__ logits, float* __re
 __global__ void pick_reduce_kernel(const float* __restrict__ piece_value,
                                    const int* __restrict__ piece_id, int* __restrict__ out,
                                    int pieces) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   Best best{-INFINITY, -1};
   bool bad = false;
@@ -115,14 +119,12 @@ static int pick_rows(const float* logits, int* out, float* piece_value, int* pie
   if (rows > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(pieces, rows);
   if (gumbel)
-    pick_pieces_kernel<true><<<grid, 256, 0, stream>>>(logits, piece_value, piece_id, vocab, kPiece,
-                                                       inv_temperature, seed, keys);
+    LRM_LAUNCH(pick_pieces_kernel<true>, grid, 256, 0, stream, logits, piece_value, piece_id, vocab, kPiece,
+               inv_temperature, seed, keys);
   else
-    pick_pieces_kernel<false><<<grid, 256, 0, stream>>>(logits, piece_value, piece_id, vocab, kPiece,
-                                                        1.f, 0ull, nullptr);
-  LRM_LAUNCH_CHECK();
-  pick_reduce_kernel<<<rows, 32, 0, stream>>>(piece_value, piece_id, out, pieces);
-  LRM_LAUNCH_CHECK();
+    LRM_LAUNCH(pick_pieces_kernel<false>, grid, 256, 0, stream, logits, piece_value, piece_id, vocab, kPiece,
+               1.f, static_cast<uint64_t>(0), static_cast<const long long*>(nullptr));
+  LRM_LAUNCH(pick_reduce_kernel, dim3(rows), 32, 0, stream, piece_value, piece_id, out, pieces);
   return 0;
 }
 
