@@ -198,6 +198,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   constexpr uint32_t A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t SET = MT * BN;                      // columns of one set of accumulators
   constexpr uint32_t NBUF = 2 * SET <= 512 ? 2 : 1;      // sets that fit in tensor memory
+  pdl_trigger();  // the next kernel may be scheduled as soon as an SM has room; it waits where it must
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // operand ring first (1024-byte aligned for the swizzle), then barriers
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -236,6 +237,9 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Barriers and tensor memory are set up while the kernel before this one may still run; what it
+  // produced (X, and `out` where the epilogue adds) is touched only after the wait.
+  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -394,8 +398,8 @@ int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, in
     if (sm_count <= 0) sm_count = 148;
   }
   const int grid = static_cast<int>(items < sm_count ? items : sm_count);
-  kernel<<<grid, 192, smem, stream>>>(map_x, map_w, out, M, N, K, mode, kb_per_split, real_splits, status);
-  LRM_LAUNCH_CHECK();
+  LRM_LAUNCH(kernel, dim3(grid), 192, smem, stream, map_x, map_w, out, M, N, K, mode, kb_per_split, real_splits,
+             status);
   return 0;
 }
 
