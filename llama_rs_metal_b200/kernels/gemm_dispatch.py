@@ -86,13 +86,18 @@ stream_shape = None  # tests and tuning: (warps per CTA, K slices) of the stream
 
 
 def _few_rows_plan(M: int, N: int, K: int, mode: int):
-    """For 17-64 rows: (use the tensor-core kernel?, K slices)."""
+    """For 17-64 rows: (use the tensor-core kernel?, K slices). Measured at the 1B layer sizes:
+    many column tiles run as they are; a product that adds into the residual is cut into as many K
+    slices as keep every item in one round over the SMs, except a small one (8 MB of weights, up to
+    32 rows), which the streaming kernel does faster; the rest streams."""
     tiles = -(-N // 128)
     if tiles >= SM_COUNT // 2:
         return True, 1
     if mode == 2:
+        if M <= 32 and N * K <= 4 * 1024 * 1024:
+            return False, 1
         k_blocks = -(-K // 64)
-        return True, max(1, min(k_blocks, 64, -(-SM_COUNT // tiles)))
+        return True, max(1, min(k_blocks, 64, SM_COUNT // tiles))
     return False, 1
 
 
