@@ -1,10 +1,14 @@
 """A plain, slow Llama 3 decoder: whole sequences, no cache, float64 on the CPU.
 
-This file rests on the reference's formulas, read from its sources (the Rust
-crates and Metal shaders cannot be compiled or run here: no Rust toolchain, no
-Metal). Each function cites the file and lines it restates. It shares no code
-with the package: it reads model folders with the `safetensors` library and
-plain `json`, and computes with basic torch CPU tensor arithmetic.
+This file rests on the reference's formulas, read from its sources: the Rust
+crates cannot be compiled or run here (no Rust toolchain, no Metal), so the
+model as a whole is not run. Its Metal shaders, however, compile as plain C++
+on the CPU with a few definitions; tests/golden/make_golden.py does that and
+tests/test_golden.py checks the functions below (norm, products, rotation,
+attention, gate, embedding, greedy pick) against the shaders' own arithmetic.
+Each function cites the file and lines it restates. It shares no code with the
+package: it reads model folders with the `safetensors` library and plain
+`json`, and computes with basic torch CPU tensor arithmetic.
 
 Precision: weights are taken as stored and widened to float64; every sum,
 softmax and norm is float64. The rotation angle is the one exception by
@@ -206,9 +210,11 @@ def forward(config, tensors, tokens, window=None):
 
 # --------------------------------------------------------------------------- sampling
 def argmax_lowest(logits):
-    """Greedy pick, lowest id on ties (crates/metal-backend/src/shaders/sampling.metal:39-80;
-    crates/llama-rs/src/sampling.rs:41-48)."""
+    """Greedy pick, lowest id on ties, -1 when any logit is not finite
+    (crates/metal-backend/src/shaders/sampling.metal:39-80; crates/llama-rs/src/sampling.rs:41-48)."""
     values = [float(v) for v in logits]
+    if not all(math.isfinite(v) for v in values):
+        return -1
     best = max(values)
     return values.index(best)
 
