@@ -50,6 +50,7 @@ class LlamaConfig:
     rope_theta: float = 10000.0
     rotary_dim: int = 0  # head_dim * partial_rotary_factor
     rope_scaling: RopeScaling = field(default_factory=RopeScaling)
+    rope_adjacent_pairs: bool = False  # config key rope_traditional
     tie_word_embeddings: bool = False
     eos_token_ids: Tuple[int, ...] = ()
     bos_token_id: Optional[int] = None
@@ -71,10 +72,9 @@ class LlamaConfig:
         act = text.get("hidden_act")
         if isinstance(act, str) and act != "silu":
             raise UnsupportedError("activation other than SiLU")  # mlx/config.rs:58-64
-        if text.get("rope_traditional") is True:
-            # The reference would pair adjacent elements (mlx/config.rs:222-226);
-            # Hugging Face Llama checkpoints are split-half, the only layout built here.
-            raise UnsupportedError("rope_traditional=true (adjacent rotary pairs)")
+        # rope_traditional=true pairs adjacent elements (2i, 2i+1); otherwise the halves of a head
+        # pair up, as in Hugging Face checkpoints (mlx/config.rs:222-226)
+        adjacent = text.get("rope_traditional") is True
 
         hidden = read_int(text, "hidden_size")
         heads = read_int(text, "num_attention_heads")
@@ -140,7 +140,7 @@ class LlamaConfig:
             hidden_size=hidden, intermediate_size=intermediate, num_hidden_layers=layers,
             num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
             vocab_size=vocab, max_position_embeddings=context, rms_norm_eps=eps,
-            rope_theta=theta, rotary_dim=rotary, rope_scaling=scaling,
+            rope_theta=theta, rotary_dim=rotary, rope_scaling=scaling, rope_adjacent_pairs=adjacent,
             tie_word_embeddings=read_bool(text, "tie_word_embeddings", False),
             eos_token_ids=normalize_token_ids(text.get("eos_token_id")),
             bos_token_id=bos if isinstance(bos, int) and not isinstance(bos, bool) else None,
@@ -170,6 +170,8 @@ class LlamaConfig:
         }
         if self.rotary_dim != self.head_dim:
             out["partial_rotary_factor"] = self.rotary_dim / self.head_dim
+        if self.rope_adjacent_pairs:
+            out["rope_traditional"] = True
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids)
         if self.bos_token_id is not None:

@@ -20,7 +20,8 @@ def llama_plan(config: LlamaConfig) -> ModelPlan:
         head_dim=config.head_dim, rotary_dim=config.rotary_dim, theta=config.rope_theta,
         scaling=scaling.kind, factor=scaling.factor, low_freq_factor=scaling.low_freq_factor,
         high_freq_factor=scaling.high_freq_factor,
-        original_max_position_embeddings=scaling.original_max_position_embeddings))
+        original_max_position_embeddings=scaling.original_max_position_embeddings,
+        adjacent_pairs=config.rope_adjacent_pairs))
     layers = []
     for i in range(config.num_hidden_layers):
         p = f"model.layers.{i}."

@@ -53,8 +53,15 @@ class Attention(Mixer):
     def bind(self, weights, runtime) -> None:
         # One [q + 2kv, h] matrix: rows of the three projections one after another,
         # so each output element is the same dot product as with separate matrices.
-        fused = torch.cat([weights["q_proj.weight"], weights["k_proj.weight"],
-                           weights["v_proj.weight"]], dim=0).contiguous()
+        q_weight, k_weight = weights["q_proj.weight"], weights["k_proj.weight"]
+        order = self.position.head_permutation() if self.position is not None else None
+        if order is not None:
+            # the position scheme wants each head's dimensions reordered: the same reordering of
+            # the rows of the query and key projections leaves every score q.k as it was
+            index = torch.tensor(order, dtype=torch.long, device=q_weight.device)
+            q_weight = q_weight.view(self.num_heads, self.head_dim, -1)[:, index].reshape(q_weight.shape)
+            k_weight = k_weight.view(self.num_kv_heads, self.head_dim, -1)[:, index].reshape(k_weight.shape)
+        fused = torch.cat([q_weight, k_weight, weights["v_proj.weight"]], dim=0).contiguous()
         self.qkv = LinearWeight(fused)
         self.q_only = LinearWeight(fused[: self.num_heads * self.head_dim])
         self.out = LinearWeight(weights["o_proj.weight"])

@@ -122,6 +122,13 @@ class PositionEncoding(Part):
         itself; None for every other scheme."""
         return None
 
+    def head_permutation(self) -> Optional[List[int]]:
+        """A reordering of a head's dimensions under which the scheme takes the form the kernels
+        implement (new dimension j is old dimension permutation[j]), or None. The mixer applies
+        it once to the rows of its query and key projections; scores do not change, because
+        queries and keys are reordered alike."""
+        return None
+
     def apply(self, q: torch.Tensor, k: torch.Tensor, ctx) -> Tuple[torch.Tensor, torch.Tensor]:
         """Any scheme that is not a rotary table transforms q and k here."""
         return q, k

@@ -1,4 +1,4 @@
-"""Rotary position encoding, split-half, with linear and llama3 frequency scaling."""
+"""Rotary position encoding (split-half or adjacent pairs) with linear and llama3 frequency scaling."""
 from __future__ import annotations
 
 import math
@@ -22,13 +22,19 @@ class RotaryEmbedding(PositionEncoding):
     wavelen = 2 pi theta^(2i/R); below original/high -> 1; above original/low
     -> factor; between, smooth = (original/wavelen - low)/(high - low) and
     1/((1-smooth)/factor + smooth). `linear`: scale = 1/factor (config.rs:166-172).
+
+    Pairing (attention.metal:14-16): split-half rotates dimension i with i + R/2; adjacent
+    rotates 2i with 2i + 1 (config key rope_traditional). The kernels rotate split-half; for
+    adjacent pairs the mixer reorders each head's query and key rows once (even dimensions of
+    the rotary part first, then the odd ones), after which pair i is again (i, i + R/2) with
+    the same frequency, and every score q.k is unchanged.
     """
 
     graph_safe = True
 
     def __init__(self, head_dim: int, rotary_dim: int, theta: float, scaling: str = "default",
                  factor: float = 1.0, low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
-                 original_max_position_embeddings: int = 0):
+                 original_max_position_embeddings: int = 0, adjacent_pairs: bool = False):
         if rotary_dim <= 0 or rotary_dim > head_dim or rotary_dim % 2:
             raise InvalidError("rotary width must be even and at most the head size")
         if theta <= 0:
@@ -39,6 +45,7 @@ class RotaryEmbedding(PositionEncoding):
         self.scaling, self.factor = scaling, float(factor)
         self.low, self.high = float(low_freq_factor), float(high_freq_factor)
         self.original = int(original_max_position_embeddings)
+        self.adjacent_pairs = bool(adjacent_pairs)
         self.inv_freq: Optional[torch.Tensor] = None
 
     def inverse_frequencies(self) -> List[float]:
@@ -64,6 +71,12 @@ class RotaryEmbedding(PositionEncoding):
     def bind(self, weights, runtime) -> None:
         self.inv_freq = torch.tensor(self.inverse_frequencies(), dtype=torch.float64) \
             .to(torch.float32).to(runtime.device)
+
+    def head_permutation(self) -> Optional[List[int]]:
+        if not self.adjacent_pairs:
+            return None
+        R = self.rotary_dim
+        return list(range(0, R, 2)) + list(range(1, R, 2)) + list(range(R, self.head_dim))
 
     def rotary_table(self) -> Optional[Tuple[torch.Tensor, int]]:
         return self.inv_freq, self.rotary_dim

@@ -110,20 +110,27 @@ def rope_inverse_frequencies(config, rotary):
     return np.asarray(out, dtype=np.float64).astype(np.float32)
 
 
-def rope(x, positions, inv_freq, rotary):
-    """Split-half rotation of x [T, heads, d] at the given positions
-    (crates/metal-backend/src/shaders/attention.metal:3-25, split-half branch):
+def rope(x, positions, inv_freq, rotary, adjacent=False):
+    """Rotation of x [T, heads, d] at the given positions
+    (crates/metal-backend/src/shaders/attention.metal:3-25). Split-half (the default):
     pair = j mod R/2; y[pair] = x[pair] cos - x[pair+R/2] sin;
-    y[pair+R/2] = x[pair] sin + x[pair+R/2] cos; dims >= R are copied."""
+    y[pair+R/2] = x[pair] sin + x[pair+R/2] cos. Adjacent (config key rope_traditional,
+    crates/model-format/src/mlx/config.rs:222-226): pair i is (2i, 2i+1), same angles.
+    Dims >= R are copied."""
     half = rotary // 2
     pos32 = np.asarray(positions, dtype=np.float32)
     angle = (pos32[:, None] * inv_freq[None, :]).astype(np.float32)  # one float32 product
     angle = torch.from_numpy(angle.astype(np.float64))
     cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
-    first, second = x[..., :half], x[..., half:rotary]
     out = x.clone()
-    out[..., :half] = first * cos - second * sin
-    out[..., half:rotary] = first * sin + second * cos
+    if adjacent:
+        first, second = x[..., 0:rotary:2], x[..., 1:rotary:2]
+        out[..., 0:rotary:2] = first * cos - second * sin
+        out[..., 1:rotary:2] = first * sin + second * cos
+    else:
+        first, second = x[..., :half], x[..., half:rotary]
+        out[..., :half] = first * cos - second * sin
+        out[..., half:rotary] = first * sin + second * cos
     return out
 
 
@@ -185,6 +192,7 @@ def forward(config, tensors, tokens, window=None):
     eps = cfg.get("rms_norm_eps", 1e-5)
     rotary = int(d * cfg.get("partial_rotary_factor", 1.0))
     inv_freq = rope_inverse_frequencies(cfg, rotary)
+    adjacent = cfg.get("rope_traditional") is True  # crates/model-format/src/mlx/config.rs:222-226
     T = len(tokens)
     positions = list(range(T))
     hidden = embedding(tensors["model.embed_tokens.weight"], tokens)
@@ -194,8 +202,8 @@ def forward(config, tensors, tokens, window=None):
         q = linear(x, tensors[p + "self_attn.q_proj.weight"]).view(T, Hq, d)
         k = linear(x, tensors[p + "self_attn.k_proj.weight"]).view(T, Hk, d)
         v = linear(x, tensors[p + "self_attn.v_proj.weight"]).view(T, Hk, d)
-        q = rope(q, positions, inv_freq, rotary)
-        k = rope(k, positions, inv_freq, rotary)
+        q = rope(q, positions, inv_freq, rotary, adjacent)
+        k = rope(k, positions, inv_freq, rotary, adjacent)
         a = attention(q, k, v, window=window).reshape(T, Hq * d)
         hidden = hidden + linear(a, tensors[p + "self_attn.o_proj.weight"])
         x = rms_norm(hidden, tensors[p + "post_attention_layernorm.weight"], eps)

@@ -81,11 +81,22 @@ def test_invalid_values_are_rejected(changes):
 @pytest.mark.parametrize("changes", [
     dict(attention_bias=True), dict(mlp_bias=True), dict(sliding_window=128),
     dict(hidden_act="gelu"), dict(rope_scaling=dict(rope_type="yarn", factor=2.0)),
-    dict(rope_traditional=True), dict(layer_types=["full_attention", "linear_attention", "full_attention"]),
+    dict(layer_types=["full_attention", "linear_attention", "full_attention"]),
 ])
 def test_unsupported_options_are_rejected(changes):
     with pytest.raises(UnsupportedError):
         LlamaConfig.from_dict(cfg(**changes))
+
+
+def test_rotary_pairing_follows_rope_traditional():
+    assert LlamaConfig.from_dict(cfg()).rope_adjacent_pairs is False
+    adjacent = LlamaConfig.from_dict(cfg(rope_traditional=True))
+    assert adjacent.rope_adjacent_pairs is True and adjacent.to_dict()["rope_traditional"] is True
+    assert LlamaConfig.from_dict(adjacent.to_dict()) == adjacent
+    from llama_rs_metal_b200.parts.rope import RotaryEmbedding
+    assert RotaryEmbedding(12, 8, 10000.0, adjacent_pairs=True).head_permutation() == \
+        [0, 2, 4, 6, 1, 3, 5, 7, 8, 9, 10, 11]
+    assert RotaryEmbedding(12, 8, 10000.0).head_permutation() is None
 
 
 def test_eos_ids_int_or_list():

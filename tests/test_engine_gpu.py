@@ -302,6 +302,33 @@ def test_session_own_sequence_prefill_decode_reset(engine, model_dirs, plain_mod
     helpers.assert_logits_close(session.prefill(tokens[:30]).cpu().numpy()[None], ref[29:30], "float32")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_adjacent_rotary_pairs_match_the_plain_implementation(engine, tmp_path, dtype):
+    """rope_traditional=true pairs dimensions (2i, 2i+1); the engine reorders the query and key
+    rows once and rotates split-half. Whole prompts, prompts in a batch and decoding must match
+    the plain implementation, which rotates adjacent pairs directly (partial rotary width too)."""
+    from llama_rs_metal_b200.engine.session import write_random_model
+    cfg = dict(helpers.TINY["B"]["config"], rope_traditional=True, partial_rotary_factor=0.5)
+    folder = write_random_model(str(tmp_path), cfg, seed=8, std=0.05, norm_std=0.1)
+    plain_cfg, tensors = P.read_model(folder)
+    assert plain_cfg["rope_traditional"] is True
+    runner, cache, model = open_runner(engine, folder, dtype, max_tokens=1024, max_slots=3)
+    seqs = [helpers.random_tokens(90 + i, n, 512) for i, n in enumerate([70, 9])]
+    refs = [P.forward(plain_cfg, tensors, s).numpy() for s in seqs]
+    straight = [P.forward(dict(plain_cfg, rope_traditional=False), tensors, s).numpy() for s in seqs]
+    assert np.abs(refs[0] - straight[0]).max() > 1e-3          # the pairing matters for these weights
+    slots = [cache.open_slot() for _ in seqs]
+    prompts = [40, 4]
+    out = runner.step([entry(sl, s[:p]) for sl, s, p in zip(slots, seqs, prompts)]).cpu()
+    helpers.assert_logits_close(out[:40], refs[0][:40], dtype, "adjacent pairs, prompt")
+    helpers.assert_logits_close(out[40:], refs[1][:4], dtype, "adjacent pairs, short prompt")
+    for step in range(30):
+        live = [b for b in (0, 1) if prompts[b] + step < len(seqs[b])]
+        out = runner.step([entry(slots[b], [seqs[b][prompts[b] + step]]) for b in live]).cpu()
+        for r, b in enumerate(live):
+            helpers.assert_logits_close(out[r:r + 1], refs[b][prompts[b] + step][None], dtype, "adjacent pairs, decoding")
+
+
 # --------------------------------------------------------------------------- a toy mixer with state
 def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(engine, tmp_path):
     """A running-mean mixer, defined here: per-sequence state = (sum of inputs, count).

@@ -58,17 +58,17 @@ def test_linear(name):
     close(P.linear(x, w.view(rows, cols)), c["y"], tol=2e-6 * cols)
 
 
-@pytest.mark.parametrize("name", ["rope_split", "rope_partial"])
+@pytest.mark.parametrize("name", ["rope_split", "rope_partial", "rope_adjacent"])
 def test_rope(name):
     c = case(name)
     tokens, heads, d, rotary, split, start, theta, scale = c["args"]
     tokens, heads, d, rotary, start = int(tokens), int(heads), int(d), int(rotary), int(start)
-    assert split == 1
+    assert (split == 0) == (name == "rope_adjacent")
     # the shader's angle: float(position) * scale * theta^(-2 pair / R) / factors[pair]
     pairs = np.arange(rotary // 2, dtype=np.float64)
     inv = (scale * theta ** (-2.0 * pairs / rotary) / c["factors"].astype(np.float64)).astype(np.float32)
     x = torch.from_numpy(c["x"].astype(np.float64)).view(tokens, heads, d)
-    got = P.rope(x, [start + t for t in range(tokens)], inv, rotary)
+    got = P.rope(x, [start + t for t in range(tokens)], inv, rotary, adjacent=split == 0)
     # float32 pow/cos/sin of angles up to a few units: agree to a few float32 ulps of the angle
     close(got, c["y"], tol=5e-5)
 
