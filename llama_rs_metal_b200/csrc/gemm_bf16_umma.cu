@@ -378,10 +378,10 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows)
 }
 
 template <int BN, int STAGES, int MT = 1>
-int launch_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode, int splits,
+int launch_umma(const void* X, const void* W, void* out, int M, int x_rows, int N, int K, int mode, int splits,
                 int* status, cudaStream_t stream) {
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, X, M, K, BM) || !make_map(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
+  if (!make_map(&map_x, X, x_rows, K, BM) || !make_map(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
   constexpr int smem = STAGES * (MT * BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   auto kernel = gemm_bf16_umma_kernel<BN, STAGES, MT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -414,15 +414,24 @@ LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
 // writes a nonzero code there (the result is then invalid and the caller must raise).
 // `splits` > 1 cuts K into that many slices that meet by atomic adds (epilogue 2 only).
 // `tile`: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256 (rows x columns of the output per item).
-LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode,
-                               int tile, int splits, int* status, cudaStream_t stream) {
+// `x_rows` >= M: rows of X that may be read (the tensor map is built over them; rows from M on only
+// feed accumulator rows that are never stored). TMA was measured slower on maps of fewer than 32
+// rows, so a caller whose buffer holds 32 rows says so.
+LRM_API int lrm_gemm_bf16_umma_rows(const void* X, const void* W, void* out, int M, int x_rows, int N, int K,
+                                    int mode, int tile, int splits, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
   if (splits < 1 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
   if (tile < 0 || tile > 2) return LRM_BAD_ARGUMENT;
-  if (tile == 2) return launch_umma<256, 3, 2>(X, W, out, M, N, K, mode, splits, status, stream);
-  if (tile == 1) return launch_umma<256, 4>(X, W, out, M, N, K, mode, splits, status, stream);
-  return launch_umma<128, 6>(X, W, out, M, N, K, mode, splits, status, stream);
+  if (x_rows < M) return LRM_BAD_ARGUMENT;
+  if (tile == 2) return launch_umma<256, 3, 2>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
+  if (tile == 1) return launch_umma<256, 4>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
+  return launch_umma<128, 6>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
+}
+
+LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode,
+                               int tile, int splits, int* status, cudaStream_t stream) {
+  return lrm_gemm_bf16_umma_rows(X, W, out, M, M, N, K, mode, tile, splits, status, stream);
 }

@@ -123,8 +123,10 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
         return
     if umma_ok:
         _status_dirty = True
-        _done(lib.lrm_gemm_bf16_umma(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode,
-                                     tile, splits, _ptr(_status_word(x.device)), _stream()),
+        # rows of x that its storage holds beyond M may be named in the tensor map (see the kernel)
+        held = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // K
+        _done(lib.lrm_gemm_bf16_umma_rows(_ptr(x), _ptr(weight), _ptr(out), M, min(max(M, 32), max(M, held)), N, K,
+                                          mode, tile, splits, _ptr(_status_word(x.device)), _stream()),
               "gemm_bf16_umma")
         return
     _done(lib.lrm_gemm_bf16_mma(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, _stream()),

@@ -69,6 +69,17 @@ def _done(code: int, what: str, launches: int = 1) -> None:
     raise RuntimeError(f"{what}: CUDA error {code}")
 
 
+
+ROW_RESERVE = 32  # rows an activation buffer holds at least (see _activation)
+
+
+def _activation(rows: int, width: int, dtype: torch.dtype, device) -> torch.Tensor:
+    """An uninitialised [rows, width] activation whose storage holds at least ROW_RESERVE rows: the
+    tensor-core product may then name 32 rows in its tensor map of this operand, which TMA handles
+    faster than fewer (the rows beyond `rows` only feed accumulator rows that are never stored)."""
+    return torch.empty((max(rows, ROW_RESERVE), width), dtype=dtype, device=device)[:rows]
+
+
 # --------------------------------------------------------------------------- embedding
 def embed_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     """float32 [T, h] rows of `table` ([vocab, h], float32 or bfloat16) at int32 ids [T]."""
@@ -99,7 +110,7 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch
         if tuple(partials.shape[1:]) != tuple(x.shape):
             raise InvalidError("partials must be [n, T, h]")
         n_partials, stride = partials.shape[0], x.numel()
-    out = torch.empty((n_rows, hidden), dtype=out_dtype, device=x.device)
+    out = _activation(n_rows, hidden, out_dtype, x.device)
     _done(_lib().lrm_rms_norm(_ptr(x), _ptr(weight), _code(weight.dtype), _ptr(out), _code(out_dtype),
                               _ptr(rows), _ptr(partials), n_partials, ctypes.c_longlong(stride),
                               n_rows, hidden, ctypes.c_float(eps), _stream()), "rms_norm")
@@ -149,7 +160,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, epilogue: str = STORE,
         raise UnsupportedError(f"linear: dtype {x.dtype}")
     if epilogue == STORE:
         out_dtype = out_dtype or torch.bfloat16
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = _activation(M, N, out_dtype, x.device)
         mode = 0 if out_dtype == torch.bfloat16 else 1
         if out_dtype not in (torch.bfloat16, torch.float32):
             raise UnsupportedError(f"linear: out dtype {out_dtype}")
@@ -158,7 +169,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, epilogue: str = STORE,
     elif epilogue == SILU_GATE:
         if N % 16 != 0:
             raise UnsupportedError("linear: the fused gate epilogue needs a multiple of 16 rows")
-        out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        out = _activation(M, N // 2, torch.bfloat16, x.device)
         mode = 3
     else:
         raise InvalidError(f"linear: unknown epilogue {epilogue!r}")
@@ -173,7 +184,7 @@ def silu_mul(gate_up: torch.Tensor, block: int) -> torch.Tensor:
     inter = gate_up.shape[1] // 2
     if gate_up.shape[1] % 2 or inter % block:
         raise InvalidError("silu_mul: width must be 2*I with I a multiple of the block")
-    out = torch.empty((gate_up.shape[0], inter), dtype=gate_up.dtype, device=gate_up.device)
+    out = _activation(gate_up.shape[0], inter, gate_up.dtype, gate_up.device)
     _done(_lib().lrm_silu_mul(_ptr(gate_up), _ptr(out), _code(gate_up.dtype),
                               ctypes.c_longlong(gate_up.shape[0]), inter, block, _stream()), "silu_mul")
     return out
@@ -258,7 +269,7 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
     Hk = k.shape[1]
     if k.shape != v.shape or k.shape[0] != T or k.shape[2] != d or Hq % Hk:
         raise InvalidError("attention_prefill: q, k, v shapes do not agree")
-    out = torch.empty((T, Hq * d), dtype=q.dtype, device=q.device)
+    out = _activation(T, Hq * d, q.dtype, q.device)
     from . import attention_dispatch
     attention_dispatch.prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len, scale, window or 0)
     return out
@@ -276,7 +287,7 @@ def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Te
     B, Hq, d = q.shape
     if tuple(kv.k.shape[1:]) != (kv.kv_heads, kv.page_size, d) or Hq % kv.kv_heads:
         raise InvalidError("attention_decode: cache pages do not match the query geometry")
-    out = torch.empty((B, Hq * d), dtype=q.dtype, device=q.device)
+    out = _activation(B, Hq * d, q.dtype, q.device)
     from . import attention_dispatch
     attention_dispatch.decode(q, kv, out, slots, kv_lens, max_kv_len, scale, window or 0)
     return out
@@ -321,7 +332,7 @@ def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[t
         rotary = 0
     if not attention_decode_fused_supported(qkv.dtype, d, kv.page_size, rotary, kv.window):
         raise UnsupportedError("attention_decode_fused: geometry not supported; use rope_store and attention_decode")
-    out = torch.empty((B, q_heads * d), dtype=qkv.dtype, device=qkv.device)
+    out = _activation(B, q_heads * d, qkv.dtype, qkv.device)
     from . import attention_dispatch
     attention_dispatch.decode_fused(qkv, positions, inv_freq, rotary, kv, dest_rows, out, slots, kv_lens,
                                     max_kv_len, q_heads, scale)
