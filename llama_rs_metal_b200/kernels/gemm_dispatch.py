@@ -1,7 +1,7 @@
 """Which bfloat16 matrix-product kernel runs for a shape.
 
-* up to 16 rows (small decode batches): the weight-streaming kernel
-  (csrc/gemm_bf16_stream.cu); it also takes 17-64 rows when the tensor-core kernel would
+* up to 8 rows (small decode batches): the weight-streaming kernel
+  (csrc/gemm_bf16_stream.cu); it also takes 9-64 rows when the tensor-core kernel would
   leave most SMs idle and cannot split K (few output columns, epilogue other than "add");
 * more rows (prompts, larger decode batches): the TMA + tcgen05 kernel
   (csrc/gemm_bf16_umma.cu), with 128 x 128, 128 x 256 or 256 x 256 tiles, whichever needs less
@@ -80,19 +80,19 @@ def _wide(M: int, N: int) -> bool:
     return tile_choice(M, N) >= 1
 
 
-STREAM_ROWS = 16  # up to this many rows the streaming kernel is the faster one
+STREAM_ROWS = 8  # up to this many rows the streaming kernel is always the faster one
 force_stream = False  # tests: keep 17-64 rows on the streaming kernel
 stream_shape = None  # tests and tuning: (warps per CTA, K slices) of the streaming kernel instead of its own rule
 
 
 def _few_rows_plan(M: int, N: int, K: int, mode: int):
-    """For 17-64 rows: (use the tensor-core kernel?, K slices). Measured at the 1B layer sizes:
-    many column tiles run as they are; a product that adds into the residual is cut into as many K
-    slices as keep every item in one round over the SMs, except a small one (8 MB of weights, up to
-    32 rows), which the streaming kernel does faster; the rest streams."""
+    """For 9-64 rows: (use the tensor-core kernel?, K slices). Measured at the 1B layer sizes:
+    many column tiles run as they are from 13 rows on; a product that adds into the residual is cut
+    into as many K slices as keep every item in one round over the SMs, except a small one (8 MB of
+    weights, up to 32 rows), which the streaming kernel does faster; the rest streams."""
     tiles = -(-N // 128)
     if tiles >= SM_COUNT // 2:
-        return True, 1
+        return M > 12, 1
     if mode == 2:
         if M <= 32 and N * K <= 4 * 1024 * 1024:
             return False, 1
