@@ -31,7 +31,9 @@ def _lib():
 
 
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of torch's current stream; the Stream object torch.cuda.current_stream()
+    # builds costs several microseconds per launch, which a short prompt's ~150 launches feel
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
