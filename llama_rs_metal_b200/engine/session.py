@@ -13,7 +13,6 @@ results are token ids.
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass
 from typing import Callable, Iterable, List, Optional, Sequence
 
@@ -26,7 +25,7 @@ from ..errors import (CancelledError, ContextError, InvalidError, KernelUnavaila
 from ..registry import find_architecture
 from ..runtime import Runtime, parse_dtype
 from ..sampling.device import BatchSampler
-from ..sampling.options import GenerationOptions, Sampling
+from ..sampling.options import GenerationOptions
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_tensors, write_model_folder
 from .batch import StepEntry

@@ -23,7 +23,7 @@ from ..cache import Cache
 from ..errors import InvalidError, PoisonedError, UnsupportedError
 from ..kernels import ops
 from ..runtime import Runtime
-from .batch import StepContext, StepEntry, context_over, pack_host, pack_step
+from .batch import StepEntry, context_over, pack_host, pack_step
 from .model import DecoderModel
 
 

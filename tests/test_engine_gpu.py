@@ -1,5 +1,4 @@
 """The engine in-process: parts alone, cutting invariance, long decoding, generation, a toy mixer."""
-import math
 
 import numpy as np
 import pytest
@@ -334,7 +333,6 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(engine, tmp_
     """A running-mean mixer, defined here: per-sequence state = (sum of inputs, count).
     It is registered, put into every second layer of a toy architecture next to the
     library's attention, and stepped; no file of the library changes."""
-    import json
     from dataclasses import dataclass
     from llama_rs_metal_b200.config.base import read_int
     from llama_rs_metal_b200.engine.session import write_random_model
@@ -443,7 +441,6 @@ def _llama_like_plan(config, window=None, schedule=None):
 def test_windowed_attention_in_a_whole_model_matches_the_plain_implementation(engine, tmp_path, dtype):
     """A window of 40 keys on every layer: the windowed cache group drops pages, prompts longer
     than the window and decoding across page boundaries must still match the oracle."""
-    import json
     from llama_rs_metal_b200.config import LlamaConfig
     from llama_rs_metal_b200.engine.session import write_random_model
     from llama_rs_metal_b200.registry import register_architecture

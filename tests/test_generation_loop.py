@@ -1,7 +1,6 @@
 """The generation loop's decisions, with stand-ins for the device (no GPU)."""
 import numpy as np
 import pytest
-import torch
 
 from llama_rs_metal_b200.engine.generate import generate, plan_batches
 from llama_rs_metal_b200.errors import CacheMemoryError, CancelledError, ContextError, OptionsError

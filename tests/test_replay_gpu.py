@@ -4,7 +4,6 @@ The same requests are replayed whole, with their last 32 tokens one by one, and 
 batches of unequal lengths that run one after another so that slots and pages are
 used again; in float32 and in bfloat16; on every tiny configuration.
 """
-import numpy as np
 import pytest
 
 import helpers
