@@ -122,6 +122,28 @@ def prefill_flops(config, layers, tokens):
     return layers * (linear + attention) + 2 * config["vocab_size"] * h
 
 
+def correctness_gate(engine, model_dir) -> str:
+    """Numbers are recorded only from a build whose logits agree with the plain implementation
+    (the reference times only what passed its numerical gate, tools/benchmarks/run.py:130-145).
+    The first two layers of the very weights that are timed, at their full widths, run in true
+    float32 and in bfloat16, whole prompts, an unequal batch with decoding, and portions, against
+    the plain CPU implementation under tests/. Takes some seconds; raises AssertionError."""
+    tests = os.path.join(ROOT, "tests")
+    if tests not in sys.path:
+        sys.path.insert(0, tests)
+    import helpers
+    started = time.perf_counter()
+    small = helpers.narrowed_copy(model_dir, model_dir + "_gate", min(2, json.load(
+        open(os.path.join(model_dir, "config.json")))["num_hidden_layers"]))
+    worst = {}
+    for dtype in ("float32", "bfloat16"):
+        worst[dtype] = helpers.parity_with_plain(engine, small, dtype, prompt_lengths=(150, 70, 9), decode_steps=3)
+    return (f"passed: 2 layers at full widths vs the plain CPU implementation, worst error "
+            f"{worst['float32']:.1e} (float32, allowed {helpers.TOLERANCE['float32']:.0e}) and "
+            f"{worst['bfloat16']:.1e} (bfloat16, allowed {helpers.TOLERANCE['bfloat16']:.0e}) of the largest "
+            f"logit, {time.perf_counter() - started:.0f} s")
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -132,6 +154,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=FULL_LAYERS,
                         help="fewer layers than the configuration's 16 (named in config when used)")
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill extras")
+    parser.add_argument("--no-gate", action="store_true",
+                        help="skip the correctness gate (profiling runs only; the line then says so)")
     parser.add_argument("--only", choices=["prefill"], default=None,
                         help="run just this part (a small case for profiling); prints a shorter line")
     args = parser.parse_args()
@@ -157,12 +181,19 @@ def main() -> int:
     peaks, peak_source = load_peaks()
     config = dict(LLAMA_1B, num_hidden_layers=args.layers)
     scratch = tempfile.mkdtemp(prefix="bench_model_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    gate = "skipped (--no-gate)"
     try:
         write_random_model(scratch, config, seed=0, std=0.02)
         engine = Engine(0)
+        if not args.no_gate:
+            gate = correctness_gate(engine, scratch)   # raises: no numbers from a build that computes wrongly
         model = engine.load(scratch, dtype="bfloat16")
+    except AssertionError as failure:
+        print(f"correctness gate failed, nothing was timed: {failure}", file=sys.stderr)
+        return 1
     finally:
         shutil.rmtree(scratch, ignore_errors=True)
+        shutil.rmtree(scratch + "_gate", ignore_errors=True)
     vocab = config["vocab_size"]
     rng = np.random.default_rng(0)
 
@@ -253,7 +284,8 @@ def main() -> int:
         flops = prefill_flops(config, args.layers, PREFILL_TOKENS)
         print(json.dumps({"metric": "prefill tok/s, one 2048-token prompt", "value": round(PREFILL_TOKENS / (ms * 1e-3), 1),
                           "unit": "tok/s", "ms": round(ms, 3), "layers": args.layers,
-                          "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "peaks": peak_source}))
+                          "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "peaks": peak_source,
+                          "gate": gate}))
         return 0
     main_run = time_decode(args.batch, args.steps, args.warmup, sample_clocks=True)
     e2e_value, h2d, d2h = time_e2e(args.batch, args.steps)
@@ -263,7 +295,7 @@ def main() -> int:
         "value": round(main_run["tokens_per_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
-        "impl": "ours",
+        "impl": "ours", "gate": gate,
         "config": {
             "model": "Llama-3.2-1B shape", "layers": args.layers, "layers_of_config": FULL_LAYERS,
             "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192,

@@ -72,32 +72,46 @@ class KeyValueGroup:
             return 0
         return max(0, length - self.request.window) // self.page_size
 
-    def pages_needed(self, slot: int, new_length: int) -> int:
+    def first_needed_page(self, new_length: int, reads_from: Optional[int]) -> int:
+        """Lowest logical page a step needs that takes a sequence to `new_length` tokens.
+
+        `reads_from` is the position of the first query of the step that reads this
+        sequence's keys from the cache (every key its window still shows must then be
+        there), or None when the step's attention reads the step's own keys and the
+        cache only has to keep what later steps will see."""
+        seen_by = new_length if reads_from is None else min(new_length, reads_from + 1)
+        return self.first_kept_page(seen_by)
+
+    def pages_needed(self, slot: int, new_length: int, reads_from: Optional[int] = None) -> int:
         """How many new pages taking the sequence to `new_length` tokens costs."""
+        if new_length <= 0:
+            return 0
         row = self.table_host[slot]
         last = (new_length - 1) // self.page_size
-        first = self.first_kept_page(new_length)
-        return int(np.count_nonzero(row[first:last + 1] < 0)) if new_length > 0 else 0
+        first = self.first_needed_page(new_length, reads_from)
+        if last >= len(row):
+            return last + 1 - first  # more than the table can name: more than any pool holds
+        return int(np.count_nonzero(row[first:last + 1] < 0))
 
-    def pages_released(self, slot: int, new_length: int) -> int:
-        first = self.first_kept_page(new_length)
+    def pages_released(self, slot: int, new_length: int, reads_from: Optional[int] = None) -> int:
+        first = self.first_needed_page(new_length, reads_from)
         return int(np.count_nonzero(self.table_host[slot][:first] >= 0))
 
-    def release_stale(self, slot: int, new_length: int) -> None:
-        """Return the pages that lie wholly before the window of a sequence of `new_length`."""
+    def release_stale(self, slot: int, new_length: int, reads_from: Optional[int] = None) -> None:
+        """Return the pages that lie wholly before what a step to `new_length` still needs."""
         row = self.table_host[slot]
-        first = self.first_kept_page(new_length)
+        first = self.first_needed_page(new_length, reads_from)
         stale = [int(p) for p in row[:first] if p >= 0]
         if stale:
             self.pool.give_back(stale)
             row[:first] = -1
             self.dirty = True
 
-    def take_missing(self, slot: int, new_length: int) -> None:
+    def take_missing(self, slot: int, new_length: int, reads_from: Optional[int] = None) -> None:
         if new_length <= 0:
             return
         row = self.table_host[slot]
-        first = self.first_kept_page(new_length)
+        first = self.first_needed_page(new_length, reads_from)
         last = (new_length - 1) // self.page_size
         missing = [i for i in range(first, last + 1) if row[i] < 0]
         if missing:
@@ -153,7 +167,9 @@ class Cache:
         self.max_sequence = max_sequence
         self.max_slots = max_slots
         self.pages = -(-max_tokens // page_size)
-        pages_per_sequence = min(self.pages, -(-max_sequence // page_size))
+        # the table names every page a sequence of max_sequence tokens can have; how many pages a
+        # sequence may hold at once is the pool's business (a windowed group holds few of them)
+        pages_per_sequence = -(-max_sequence // page_size)
         self.slots = FreeList(max_slots, "slot")
         self.lengths = np.zeros(max_slots, dtype=np.int64)  # tokens cached per slot
         self.open_mask = np.zeros(max_slots, dtype=bool)      # slot is held by a sequence
@@ -213,51 +229,74 @@ class Cache:
             raise InvalidError(f"slot {slot} is not open")
 
     # -- growth --------------------------------------------------------------------
-    def check_growth(self, growth: Sequence[Tuple[int, int]]) -> None:
-        """Raise, changing nothing, unless every (slot, new_length) of a step fits."""
-        for slot, new_length in growth:
+    @staticmethod
+    def _growth(growth):
+        """(slot, new_length[, reads_from]) -> (slot, new_length, reads_from); see grow()."""
+        return [(g[0], g[1], g[2] if len(g) > 2 else None) for g in growth]
+
+    def check_growth(self, growth: Sequence[Tuple]) -> None:
+        """Raise, changing nothing, unless every (slot, new_length[, reads_from]) of a step fits."""
+        growth = self._growth(growth)
+        for slot, new_length, _ in growth:
             self._require(slot)
             if new_length > self.max_sequence:
                 raise ContextError(self.max_sequence, new_length)
         for group in self.kv_groups:
-            need = sum(group.pages_needed(s, n) for s, n in growth)
-            freed = sum(group.pages_released(s, n) for s, n in growth)
+            need = sum(group.pages_needed(s, n, r) for s, n, r in growth)
+            freed = sum(group.pages_released(s, n, r) for s, n, r in growth)
             if need > group.pool.available + freed:
                 raise CacheMemoryError(
                     f"step needs {need} pages of {self.page_size} tokens, "
                     f"{group.pool.available + freed} free of {group.pool.count}")
 
-    def grow(self, growth: Sequence[Tuple[int, int]]) -> None:
-        """Give every sequence of a step the pages it needs up to its new length."""
+    def grow(self, growth: Sequence[Tuple]) -> None:
+        """Give every sequence of a step the pages it needs up to its new length.
+
+        An entry is (slot, new_length) or (slot, new_length, reads_from): `reads_from` is
+        the position of the step's first query for that sequence when the step's attention
+        reads the cache (a windowed group then keeps every page that query still sees);
+        without it the step attends to its own keys and a windowed group keeps only what
+        later steps will see."""
+        growth = self._growth(growth)
         self.check_growth(growth)
         for group in self.kv_groups:
-            for slot, new_length in growth:  # release first so the freed pages can be reused
-                group.release_stale(slot, new_length)
-            for slot, new_length in growth:
-                group.take_missing(slot, new_length)
+            for slot, new_length, reads_from in growth:  # release first so the freed pages can be reused
+                group.release_stale(slot, new_length, reads_from)
+            for slot, new_length, reads_from in growth:
+                group.take_missing(slot, new_length, reads_from)
 
     def grow_by_one(self, slots: np.ndarray):
         """The decode step's bookkeeping for many sequences at once: every listed (open, distinct,
         non-empty) slot grows by one token. Checks capacity and pages first and changes nothing
         if the step does not fit. Returns (lengths before, per key/value group the row each new
-        token is stored at), or None when a group has a window (the general path handles those).
-        The caller commits with commit_lengths()."""
-        if any(g.request.window is not None for g in self.kv_groups):
+        token is stored at), or None for an empty step. A windowed group gives back the pages
+        that the new token no longer sees. The caller commits with commit_lengths()."""
+        if len(slots) == 0:
             return None
         before = self.lengths[slots]
         if int(before.max()) + 1 > self.max_sequence:
             raise ContextError(self.max_sequence, int(before.max()) + 1)
         ps = self.page_size
         index = before // ps
-        missing = []
+        missing, stale = [], []
         for group in self.kv_groups:
             lacking = np.nonzero(group.table_host[slots, index] < 0)[0]
-            if len(lacking) > group.pool.available:
+            leaving = np.zeros(0, dtype=np.int64)
+            if group.request.window is not None:
+                # Pages below the first one the new token still sees. Pages leave a window lowest
+                # first, so a sequence holds stale pages exactly when it holds the one right below.
+                first = np.maximum(0, before + 1 - group.request.window) // ps
+                leaving = np.nonzero((first > 0) & (group.table_host[slots, np.maximum(first - 1, 0)] >= 0))[0]
+            freed = sum(int(np.count_nonzero(group.table_host[slots[i], :first[i]] >= 0)) for i in leaving)
+            stale.append(leaving)
+            if len(lacking) > group.pool.available + freed:
                 raise CacheMemoryError(f"step needs {len(lacking)} pages of {ps} tokens, "
-                                       f"{group.pool.available} free of {group.pool.count}")
+                                       f"{group.pool.available + freed} free of {group.pool.count}")
             missing.append(lacking)
         rows = []
-        for group, lacking in zip(self.kv_groups, missing):
+        for group, lacking, leaving in zip(self.kv_groups, missing, stale):
+            for i in leaving:
+                group.release_stale(int(slots[i]), int(before[i]) + 1)
             if len(lacking):
                 pages = group.pool.take(len(lacking))
                 group.table_host[slots[lacking], index[lacking]] = pages
@@ -268,9 +307,24 @@ class Cache:
     def commit_lengths(self, slots: np.ndarray, lengths: np.ndarray) -> None:
         self.lengths[slots] = lengths
 
-    def commit(self, growth: Sequence[Tuple[int, int]]) -> None:
-        for slot, new_length in growth:
-            self.lengths[slot] = new_length
+    def commit(self, growth: Sequence[Tuple]) -> None:
+        for entry in growth:
+            self.lengths[entry[0]] = entry[1]
+
+    def shorten(self, slots: Sequence[int], tokens: int = 1) -> None:
+        """Take the last `tokens` tokens of some sequences back: only the lengths change. The
+        pages stay with their sequences and the rows are written again when those positions are
+        fed again (a windowed group keeps the same pages for the same position). Fixed-size
+        state cannot be taken back, so a cache with state groups refuses."""
+        if self.state_groups:
+            raise InvalidError("sequences with fixed-size state cannot be shortened")
+        slots = [int(s) for s in slots]
+        for slot in slots:
+            self._require(slot)
+            if tokens < 0 or self.lengths[slot] < tokens:
+                raise InvalidError(f"slot {slot} holds {int(self.lengths[slot])} tokens, cannot take back {tokens}")
+        for slot in slots:
+            self.lengths[slot] -= tokens
 
     def sync(self) -> None:
         for group in self.kv_groups:

@@ -6,9 +6,11 @@
 // It is the attention of the float32 path for prompts and for decoding, and
 // the bfloat16 path's fallback for sizes its tiled kernels refuse. The two
 // entry points differ only in where keys come from (the step's packed k/v, or
-// the paged cache), so a prompt and its token-by-token replay do the same
-// arithmetic in the same order. A window w lets a query at position p see keys
-// p-w+1 .. p.
+// the paged cache), so a prompt, its token-by-token replay and its replay in
+// chunks of any size do the same arithmetic in the same order. The paged entry
+// takes any number of queries per sequence (a decoded token, or a portion of
+// several tokens appended to a started sequence, whose own keys are already in
+// the cache). A window w lets a query at position p see keys p-w+1 .. p.
 #include "common.cuh"
 
 constexpr int kMaxPerLane = 16;  // head_dim <= 512
@@ -100,14 +102,19 @@ __global__ void attention_paged_kernel(const A* __restrict__ q, const A* __restr
                                        const A* __restrict__ v_pages, A* __restrict__ out,
                                        const int* __restrict__ page_table, int table_stride,
                                        const int* __restrict__ slots,
-                                       const int* __restrict__ kv_lens, int q_heads, int kv_heads,
+                                       const int* __restrict__ kv_lens,
+                                       const int* __restrict__ seq_of_token,
+                                       const int* __restrict__ positions, int q_heads, int kv_heads,
                                        int d, int page_size, float scale, int window) {
-  const int b = blockIdx.x, h = blockIdx.y;
-  const int pos = kv_lens[b] - 1;
+  // query t of the step belongs to sequence b and stands at position pos; without the two
+  // arrays there is one query per sequence, its newest token
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int b = seq_of_token != nullptr ? seq_of_token[t] : t;
+  const int pos = positions != nullptr ? positions[t] : kv_lens[b] - 1;
   const int first = window > 0 ? max(0, pos - window + 1) : 0;
   PagedKeys keys{k_pages, v_pages, page_table + static_cast<size_t>(slots[b]) * table_stride,
                  kv_heads, d, page_size};
-  const size_t qo = (static_cast<size_t>(b) * q_heads + h) * d;
+  const size_t qo = (static_cast<size_t>(t) * q_heads + h) * d;
   attend_row<A>(q + qo, out + qo, keys, h / (q_heads / kv_heads), first, pos, d, scale);
 }
 
@@ -139,25 +146,32 @@ LRM_API int lrm_attention_packed_rowwise(const void* q, const void* k, const voi
   return 0;
 }
 
+// `queries` rows of q. With seq_of_token and positions (int32 [queries]) query t belongs to
+// sequence seq_of_token[t] and sees keys up to positions[t]; with both null there is one query
+// per sequence, at position kv_lens[b] - 1.
 LRM_API int lrm_attention_paged_rowwise(const void* q, const void* k_pages, const void* v_pages,
                                         void* out, int dtype, const int* page_table,
                                         int table_stride, const int* slots, const int* kv_lens,
-                                        int seqs, int q_heads, int kv_heads, int d, int page_size,
+                                        const int* seq_of_token, const int* positions,
+                                        int queries, int q_heads, int kv_heads, int d, int page_size,
                                         float scale, int window, cudaStream_t stream) {
-  if (seqs <= 0) return 0;
+  if (queries <= 0) return 0;
   if (bad_geometry(q_heads, kv_heads, d) || page_size <= 0) return LRM_BAD_ARGUMENT;
+  if ((seq_of_token == nullptr) != (positions == nullptr)) return LRM_BAD_ARGUMENT;
+  if (positions == nullptr && kv_lens == nullptr) return LRM_BAD_ARGUMENT;
   if (q_heads > 65535) return LRM_UNSUPPORTED;
-  const dim3 grid(seqs, q_heads);
+  const dim3 grid(queries, q_heads);
   if (dtype == LRM_F32)
     attention_paged_kernel<float><<<grid, 32, 0, stream>>>(
         static_cast<const float*>(q), static_cast<const float*>(k_pages),
         static_cast<const float*>(v_pages), static_cast<float*>(out), page_table, table_stride,
-        slots, kv_lens, q_heads, kv_heads, d, page_size, scale, window);
+        slots, kv_lens, seq_of_token, positions, q_heads, kv_heads, d, page_size, scale, window);
   else if (dtype == LRM_BF16)
     attention_paged_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k_pages),
         static_cast<const __nv_bfloat16*>(v_pages), static_cast<__nv_bfloat16*>(out), page_table,
-        table_stride, slots, kv_lens, q_heads, kv_heads, d, page_size, scale, window);
+        table_stride, slots, kv_lens, seq_of_token, positions, q_heads, kv_heads, d, page_size, scale,
+        window);
   else
     return LRM_BAD_ARGUMENT;
   LRM_LAUNCH_CHECK();

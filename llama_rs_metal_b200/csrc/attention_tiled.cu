@@ -4,6 +4,9 @@
 //  * prefill: causal grouped-query flash attention over a step's own packed
 //    q, k, v (ragged batch, every sequence starts at position 0). One CTA = 64
 //    queries of one head; K/V arrive in 64-key tiles, double buffered.
+//  * extend: the same flash attention for a portion of several tokens appended to started
+//    sequences: queries are the step's packed tokens, keys and values come from the paged
+//    cache (which already holds the portion's own), one 64-key page per tile.
 //  * decode: one query per sequence over the paged cache, split over the keys.
 //    One CTA = (sequence, kv head, split); its 4 warps each take 16 keys of
 //    every 64-key page, so K/V are read once for all query heads of the group.
@@ -102,6 +105,105 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
     total += __shfl_xor_sync(0xffffffffu, total, 2);
     const int row = row0 + g + 8 * half;
     if (row >= len) continue;
+    const float inv = 1.0f / total;
+    __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
+#pragma unroll
+    for (int dn = 0; dn < D / 8; ++dn)
+      *reinterpret_cast<uint32_t*>(dst + 8 * dn + 2 * t) =
+          pack_bf16(o[dn][2 * half] * inv, o[dn][2 * half + 1] * inv);
+  }
+}
+
+// --------------------------------------------------------------------------- extend
+// Queries: the step's packed tokens (sequence b brings n = cu_seqlens[b+1] - cu_seqlens[b] of
+// them, standing at positions kv_lens[b] - n .. kv_lens[b] - 1). Keys and values: the paged cache,
+// which holds every position up to kv_lens[b] - 1, this step's included. One CTA = 64 queries of one
+// head; a key tile is one page.
+template <int D>
+__global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+    const __nv_bfloat16* __restrict__ v_pages, __nv_bfloat16* __restrict__ out,
+    const int* __restrict__ cu_seqlens, const int* __restrict__ page_table, int table_stride,
+    const int* __restrict__ slots, const int* __restrict__ kv_lens, int q_heads, int kv_heads,
+    float scale_log2, int window) {
+  constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][64][STRIDE]
+  __nv_bfloat16* Vs = Ks + 2 * TILE;
+
+  pdl_wait();
+  const int qt = gridDim.z - 1 - blockIdx.z;  // longest rows of work first
+  const int h = blockIdx.x, b = blockIdx.y;
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start;
+  const int q0 = qt * kTile;
+  if (q0 >= n) return;
+  const int len = kv_lens[b], before = len - n;
+  const int kh = h / (q_heads / kv_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int row0 = q0 + 16 * warp;  // this warp's first query, counted within the portion
+  const int* table = page_table + static_cast<size_t>(slots[b]) * table_stride;
+
+  uint32_t qa[D / 16][4];
+  load_q<D>(qa, q + (static_cast<size_t>(start + row0) * q_heads + h) * D,
+            static_cast<size_t>(q_heads) * D, n - row0);
+  float o[D / 8][4];
+#pragma unroll
+  for (int dn = 0; dn < D / 8; ++dn)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dn][e] = 0.f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+  // keys the tile's queries see: from the first query's window to the last query's own position
+  const int first_key = window > 0 ? max(0, before + q0 - window + 1) : 0;
+  const int kt_first = first_key / kTile;
+  const int kt_last = (before + min(q0 + kTile, n) - 1) / kTile;
+  auto issue = [&](int kt, int stage) {
+    const int page = table[kt];
+    const size_t base = (static_cast<size_t>(max(page, 0)) * kv_heads + kh) * kTile * D;
+    // rows behind the sequence's end, before the window, or of a page the sequence does not hold
+    // are zero-filled (the mask hides them; stale bits must not reach a product)
+    const int valid = page >= 0 ? len - kt * kTile : 0;
+    load_page<D>(Ks + stage * TILE, k_pages + base, valid, first_key - kt * kTile);
+    load_page<D>(Vs + stage * TILE, v_pages + base, valid, first_key - kt * kTile);
+    cp_async_commit();
+  };
+  issue(kt_first, 0);
+  for (int kt = kt_first; kt <= kt_last; ++kt) {
+    const int stage = (kt - kt_first) & 1;
+    if (kt < kt_last) {
+      issue(kt + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    float s[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+    scores<D, 8>(s, qa, Ks + stage * TILE);
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
+        const int query = before + row0 + g + 8 * (e >> 1);  // position in the sequence
+        const bool visible = key <= query && (window <= 0 || key > query - window);
+        s[nt][e] = visible ? s[nt][e] * scale_log2 : -INFINITY;
+      }
+    }
+    softmax_update<D, 8>(s, o, m, l);
+    weighted_values<D, 8>(o, s, Vs + stage * TILE);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    float total = l[half];
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    const int row = row0 + g + 8 * half;
+    if (row >= n) continue;
     const float inv = 1.0f / total;
     __nv_bfloat16* dst = out + (static_cast<size_t>(start + row) * q_heads + h) * D;
 #pragma unroll
@@ -296,6 +398,23 @@ template <int D> int prefill_launch(const void* q, const void* k, const void* v,
   return 0;
 }
 
+template <int D> int extend_launch(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                   const int* cu_seqlens, const int* page_table, int table_stride,
+                                   const int* slots, const int* kv_lens, int seqs, int max_seq_len,
+                                   int q_heads, int kv_heads, float scale, int window, cudaStream_t stream) {
+  const int smem = 4 * kTile * (D + 8) * 2;
+  auto kernel = attention_extend_tiled_kernel<D>;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (seqs > 65535 || (max_seq_len + kTile - 1) / kTile > 65535) return LRM_UNSUPPORTED;
+  const dim3 grid(q_heads, seqs, (max_seq_len + kTile - 1) / kTile);
+  LRM_LAUNCH(kernel, grid, kThreads, smem, stream, static_cast<const __nv_bfloat16*>(q),
+             static_cast<const __nv_bfloat16*>(k_pages), static_cast<const __nv_bfloat16*>(v_pages),
+             static_cast<__nv_bfloat16*>(out), cu_seqlens, page_table, table_stride, slots, kv_lens,
+             q_heads, kv_heads, scale * 1.4426950408889634f, window);
+  return 0;
+}
+
 template <int D> int decode_launch(const void* q, const void* k_pages, const void* v_pages,
                                    float* partials, void* out, const int* page_table,
                                    int table_stride, const int* slots, const int* kv_lens, int seqs,
@@ -334,6 +453,25 @@ LRM_API int lrm_attention_prefill_tiled(const void* q, const void* k, const void
     case 32: return prefill_launch<32>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
     case 64: return prefill_launch<64>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
     case 128: return prefill_launch<128>(q, k, v, out, cu_seqlens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    default: return LRM_UNSUPPORTED;
+  }
+}
+
+// q, out: [tokens, q_heads, d] packed bfloat16 (sequence b's rows are cu_seqlens[b] ..
+// cu_seqlens[b+1] - 1, at most max_seq_len of them); the cache holds every sequence's keys up to
+// kv_lens[b] - 1, the step's own included.
+LRM_API int lrm_attention_extend_tiled(const void* q, const void* k_pages, const void* v_pages, void* out,
+                                       const int* cu_seqlens, const int* page_table, int table_stride,
+                                       const int* slots, const int* kv_lens, int seqs, int max_seq_len,
+                                       int q_heads, int kv_heads, int d, int page_size, float scale,
+                                       int window, cudaStream_t stream) {
+  if (seqs <= 0 || max_seq_len <= 0) return 0;
+  if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) return LRM_BAD_ARGUMENT;
+  if (q_heads > 65535 || seqs > 65535 || page_size != kTile) return LRM_UNSUPPORTED;
+  switch (d) {
+    case 32: return extend_launch<32>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    case 64: return extend_launch<64>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
+    case 128: return extend_launch<128>(q, k_pages, v_pages, out, cu_seqlens, page_table, table_stride, slots, kv_lens, seqs, max_seq_len, q_heads, kv_heads, scale, window, stream);
     default: return LRM_UNSUPPORTED;
   }
 }

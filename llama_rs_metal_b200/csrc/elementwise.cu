@@ -23,6 +23,19 @@ __global__ void add_inplace_kernel(float* __restrict__ x, const D* __restrict__ 
   if (idx < n) x[idx] += to_f32(delta[idx]);
 }
 
+// x += planes[0] + planes[1] + ... in plane order (the K slices of a product whose sum belongs
+// to the residual stream), for a reader of the stream that cannot fold them itself.
+__global__ void add_planes_kernel(float* __restrict__ x, const float* __restrict__ planes, int count,
+                                  size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= n) return;
+  float v = x[idx];
+  for (int p = 0; p < count; ++p) v += planes[p * n + idx];
+  x[idx] = v;
+}
+
 template <typename S, typename D>
 __global__ void cast_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
   const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
@@ -60,6 +73,27 @@ LRM_API int lrm_add_inplace(float* x, const void* delta, int delta_dtype, long l
   else
     return LRM_BAD_ARGUMENT;
   LRM_LAUNCH_CHECK();
+  return 0;
+}
+
+__global__ void scale_inplace_kernel(float* __restrict__ x, float factor, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx < n) x[idx] *= factor;
+}
+
+LRM_API int lrm_scale_inplace(float* x, float factor, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (x == nullptr) return LRM_BAD_ARGUMENT;
+  LRM_LAUNCH(scale_inplace_kernel, blocks_for(n), 256, 0, stream, x, factor, static_cast<size_t>(n));
+  return 0;
+}
+
+LRM_API int lrm_add_planes(float* x, const float* planes, int count, long long n, cudaStream_t stream) {
+  if (n <= 0 || count <= 0) return 0;
+  if (x == nullptr || planes == nullptr) return LRM_BAD_ARGUMENT;
+  LRM_LAUNCH(add_planes_kernel, blocks_for(n), 256, 0, stream, x, planes, count, static_cast<size_t>(n));
   return 0;
 }
 

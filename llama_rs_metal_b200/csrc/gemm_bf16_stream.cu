@@ -12,13 +12,16 @@
 // 128-wide chunks (so many loads are in flight per SM), and their partial sums are added in
 // warp order through shared memory (no atomics: the result is deterministic).
 //
-// For the add epilogue blockIdx.y may cut K into slices handled by different CTAs that meet in
-// the float32 output by atomic adds: narrow products (few 16-row tiles) then still keep every
-// SM streaming.
+// For a narrow product (few 16-row tiles) that is to be added to the residual stream,
+// blockIdx.y may cut K into slices handled by different CTAs, so that every SM still streams.
+// Slice s then stores its float32 partial product at out[s] of an [slices, M, N] tensor
+// (epilogue 4); whoever reads the residual stream next adds the slices in slice order (the
+// norm kernel does it in its own pass). No atomics: the result does not depend on which CTA
+// finishes first.
 //
 // Epilogues: 0 store bf16, 1 store f32, 2 add into f32 in place, 3 SiLU gate
 // (rows alternate in blocks of 8 gate / 8 up rows, so a 16-row tile holds 8
-// gated pairs; out is [M, N/2] bf16).
+// gated pairs; out is [M, N/2] bf16), 4 store f32 partials per K slice.
 // (Reference role: the gemv_* family, crates/metal-backend/src/shaders/matrix.metal:10-37.)
 #include "common.cuh"
 
@@ -64,7 +67,8 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
   const int n0 = blockIdx.x * 16;
   const int k_lo = blockIdx.y * k_per_split;              // this CTA's slice of K: [k_lo, K)
   const int K = min(K_total, k_lo + k_per_split);
-  const bool sliced = gridDim.y > 1;
+  // epilogue 4: this slice's partial product goes to its own [M, N] plane of `out`
+  float* plane = mode == 4 ? static_cast<float*>(out) + static_cast<size_t>(blockIdx.y) * M * N : nullptr;
   const int row_a = n0 + g, row_b = n0 + g + 8;
   const bool ok_a = row_a < N, ok_b = row_b < N;
   const __nv_bfloat16* wa = W + static_cast<size_t>(ok_a ? row_a : 0) * K_total;
@@ -101,7 +105,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
   pdl_wait();
   // mode 2 adds into `out`: fetch the old values now so their latency hides behind the stream
   float old[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  if (mode == 2 && !sliced && threadIdx.x < NT * 32) {
+  if (mode == 2 && threadIdx.x < NT * 32) {
     const int j = threadIdx.x >> 5, gg = (threadIdx.x & 31) >> 2, tt = threadIdx.x & 3;
 #pragma unroll
     for (int e = 0; e < 2; ++e)
@@ -174,7 +178,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
         const float v = vals[e][half];
         if (mode == 0) static_cast<__nv_bfloat16*>(out)[o] = __float2bfloat16_rn(v);
         else if (mode == 1) static_cast<float*>(out)[o] = v;
-        else if (sliced) atomicAdd(static_cast<float*>(out) + o, v);
+        else if (mode == 4) plane[o] = v;
         else static_cast<float*>(out)[o] = (item < WARPS * 32 ? old[e][half] : static_cast<float*>(out)[o]) + v;
       }
     }
@@ -218,23 +222,39 @@ LRM_API int lrm_gemm_bf16_stream_supports(int M, int N, int K) {
   return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 ? 1 : 0;
 }
 
-// `warps` (1, 2, 4, 8, 16) and `splits` (K slices, add epilogue only) choose the launch shape;
-// 0 leaves the choice to the rule below.
+static int chunk_of(int M) { return M <= 16 ? 64 : 128; }  // Chunk<NT>::kK for this many rows
+
+// How many K slices a product to be added to the residual stream is cut into: `requested`, or with
+// 0 the kernel's own rule (slices of at least 1024 until about 28 warps per SM stream weights).
+// The answer is the number of [M, N] planes epilogue 4 writes.
+static int pick_splits(int N, int K, int requested) {
+  if (requested > 0) return requested;
+  const int tiles = (N + 15) / 16;
+  int splits = 1;
+  while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 1024) splits *= 2;
+  return splits;
+}
+
+LRM_API int lrm_gemm_bf16_stream_slices(int M, int N, int K, int requested) {
+  if (M <= 0 || N <= 0 || K <= 0) return 1;
+  const int splits = pick_splits(N, K, requested);
+  const int chunk = chunk_of(M);
+  const int k_per_split = ((K + splits - 1) / splits + chunk - 1) / chunk * chunk;
+  return (K + k_per_split - 1) / k_per_split;
+}
+
+// `warps` (1, 2, 4, 8, 16) chooses the launch shape, 0 leaves it to the rule below. `splits`: K
+// slices, epilogue 4 only (out then holds lrm_gemm_bf16_stream_slices(M, N, K, splits) planes).
 LRM_API int lrm_gemm_bf16_stream_shaped(const void* X, const void* W, void* out, int M, int N, int K,
                                         int mode, int warps, int splits, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lrm_gemm_bf16_stream_supports(M, N, K)) return LRM_UNSUPPORTED;
-  if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0)) return LRM_BAD_ARGUMENT;
-  if (warps < 0 || warps > 16 || splits < 0 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
+  if (mode < 0 || mode > 4 || (mode == 3 && N % 16 != 0)) return LRM_BAD_ARGUMENT;
+  if (warps < 0 || warps > 16 || splits < 0 || splits > 64 || (splits > 1 && mode != 4)) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
-  // The add epilogue may cut K across CTAs (slices of at least 1024) until about 28 warps per SM
-  // stream weights; then enough warps per CTA that each has at least one chunk.
+  // then enough warps per CTA that each has at least one chunk
   const int tiles = (N + 15) / 16;
-  if (splits == 0) {
-    splits = 1;
-    if (mode == 2)
-      while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 1024) splits *= 2;
-  }
+  splits = mode == 4 ? pick_splits(N, K, splits) : 1;
   const int chunks = ((K + splits - 1) / splits + 127) / 128;
   if (warps == 0) {
     warps = 4;

@@ -14,12 +14,15 @@
 // (tcgen05.ld, one row per thread) while the next tile's MMAs fill the other
 // accumulator, and apply the epilogue:
 //   0 store bfloat16, 1 store float32, 2 add into float32 in place (residual
-//   stream), 3 SiLU gate over alternating blocks of 8 gate / 8 up columns.
+//   stream), 3 SiLU gate over alternating blocks of 8 gate / 8 up columns,
+//   4 store float32 partials per K slice.
 // Rows and columns beyond M, N, K are zero-filled by TMA and skipped on store,
 // so any M, N and any K that is a multiple of 8 is accepted.
-// With `splits` > 1 (epilogue 2 only) blockIdx.z takes a slice of K and the slices meet in
-// the float32 output through vector atomic adds: this is how a product with few rows and few
-// columns (decode at batch 17-64: O and down projections) still fills the machine.
+// With `splits` > 1 (epilogue 4 only) an item covers a slice of K and stores its partial
+// product in plane `slice` of an [splits, M, N] float32 tensor; whoever next reads the
+// residual stream adds the planes in slice order (the norm kernel does it in its own pass).
+// This is how a product with few rows and few columns (decode at batch 17-64: O and down
+// projections) still fills the machine, with a result that does not depend on timing.
 //
 // Every wait on an mbarrier is bounded: after kSpinLimit polls the thread
 // records where it gave up in `status` and the CTA winds down (waiting, again
@@ -129,7 +132,7 @@ enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain
 
 // The epilogue of one 32-column piece of an accumulator row held in registers.
 __device__ __forceinline__ void store_piece(const uint32_t (&r)[32], void* __restrict__ out, int m, int n,
-                                            int M, int N, int mode, bool atomic) {
+                                            int M, int N, int mode) {
   if (m >= M || n >= N) return;
   const bool whole = n + 32 <= N;
   if (mode == 3) {
@@ -171,8 +174,8 @@ __device__ __forceinline__ void store_piece(const uint32_t (&r)[32], void* __res
         float4 v = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
                                __uint_as_float(r[i + 3]));
         // Adding goes through a vector reduction in L2 (no value comes back, so the thread does
-        // not wait for the old contents). Without K slices each element gets exactly one add,
-        // so the result is as deterministic as a read-modify-write.
+        // not wait for the old contents). Each element gets exactly one add per launch, so the
+        // result is as deterministic as a read-modify-write.
         if (mode == 2) atomicAdd(reinterpret_cast<float4*>(dst + i), v);
         else *reinterpret_cast<float4*>(dst + i) = v;
       }
@@ -214,7 +217,6 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   const int m_tiles = (M + MT * BM - 1) / (MT * BM), n_tiles = (N + BN - 1) / BN;
   const int items = m_tiles * n_tiles * splits;
   const int k_blocks = (K + BK - 1) / BK;
-  const bool atomic = splits > 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -324,13 +326,17 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
         break;
       }
       tc_fence_after();
-      if (num_kb > 0) {  // an empty slice adds nothing
+      // epilogue 4: slice s owns plane s of `out` (the host never makes an empty slice)
+      void* plane = mode == 4 ? static_cast<void*>(static_cast<float*>(out) +
+                                                   static_cast<size_t>(item / (m_tiles * n_tiles)) * M * N)
+                              : out;
+      if (num_kb > 0) {
 #pragma unroll 1
         for (int c = 0; c < MT * BN / 32; ++c) {  // accumulator c / (BN / 32) holds rows 128 (c / (BN / 32)) ...
           const int m = m0 + (c / (BN / 32)) * BM + quarter * 32 + lane;
           uint32_t r[32];
           tmem_load32(tmem_base + acc * SET + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
-          store_piece(r, out, m, n0 + (c % (BN / 32)) * 32, M, N, mode, atomic);
+          store_piece(r, plane, m, n0 + (c % (BN / 32)) * 32, M, N, mode);
         }
       }
       tc_fence_before();
@@ -405,6 +411,14 @@ int launch_umma(const void* X, const void* W, void* out, int M, int x_rows, int 
 
 }  // namespace
 
+// Planes that epilogue 4 writes when K is cut into `splits` slices (no slice is ever empty).
+LRM_API int lrm_gemm_bf16_umma_slices(int K, int splits) {
+  if (K <= 0 || splits <= 1) return 1;
+  const int k_blocks = (K + BK - 1) / BK;
+  const int kb_per_split = (k_blocks + splits - 1) / splits;
+  return (k_blocks + kb_per_split - 1) / kb_per_split;
+}
+
 // Shapes the tensor-core kernel takes: K a multiple of 8 (TMA needs 16-byte row pitches).
 LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
   return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && encode_tiled() != nullptr ? 1 : 0;
@@ -412,7 +426,8 @@ LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
 
 // `status`: one int in device memory, 0 before the launch; a kernel that gave up on a wait
 // writes a nonzero code there (the result is then invalid and the caller must raise).
-// `splits` > 1 cuts K into that many slices that meet by atomic adds (epilogue 2 only).
+// `splits` > 1 cuts K into slices whose partial products go to the planes of an
+// [lrm_gemm_bf16_umma_slices(K, splits), M, N] float32 tensor (epilogue 4 only).
 // `tile`: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256 (rows x columns of the output per item).
 // `x_rows` >= M: rows of X that may be read (the tensor map is built over them; rows from M on only
 // feed accumulator rows that are never stored). TMA was measured slower on maps of fewer than 32
@@ -421,9 +436,9 @@ LRM_API int lrm_gemm_bf16_umma_rows(const void* X, const void* W, void* out, int
                                     int mode, int tile, int splits, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
-  if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
+  if (mode < 0 || mode > 4 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
-  if (splits < 1 || splits > 64 || (splits > 1 && mode != 2)) return LRM_BAD_ARGUMENT;
+  if (splits < 1 || splits > 64 || (splits > 1 && mode != 4)) return LRM_BAD_ARGUMENT;
   if (tile < 0 || tile > 2) return LRM_BAD_ARGUMENT;
   if (x_rows < M) return LRM_BAD_ARGUMENT;
   if (tile == 2) return launch_umma<256, 3, 2>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);

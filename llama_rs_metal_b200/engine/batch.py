@@ -28,11 +28,14 @@ class StepContext:
     """
 
     runtime: Runtime
-    phase: str  # "prefill": every sequence starts at position 0; "decode": one token each
+    # "prefill": every sequence starts at position 0 (attention may read the step's own keys);
+    # "decode": one token onto each started sequence; "extend": anything else (several tokens
+    # onto started sequences, or a mix): keys are stored first, attention reads the cache
+    phase: str
     num_tokens: int
     num_seqs: int
     max_seq_len: int  # most tokens one sequence brings this step
-    max_kv_len: int  # longest sequence after this step
+    max_kv_len: int  # longest sequence after this step, or an upper bound of it (launch geometry only)
     token_ids: torch.Tensor  # int32 [T]
     positions: torch.Tensor  # int32 [T]
     seq_of_token: torch.Tensor  # int32 [T]
@@ -43,6 +46,27 @@ class StepContext:
     dest_rows: List[torch.Tensor] = field(default_factory=list)  # per key/value group: int32 [T]
     entry: Any = None  # the schedule entry being run
     fresh_kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = field(default_factory=dict)
+    # Partial sums [n, T, h] (float32) that belong to the residual stream but are not added to it
+    # yet: the K slices of a narrow product, which the next norm adds in its own pass instead of
+    # atomics meeting in memory. A part may leave them only while `may_defer` is set, which a
+    # block does right before it passes the part's output through a norm with `folds_pending`;
+    # `next_folds_pending` tells a block whether whatever reads the stream after it does so.
+    pending: Any = None
+    may_defer: bool = False
+    next_folds_pending: bool = False
+
+    def take_pending(self):
+        """The pending partial sums (the caller adds them); none are pending afterwards."""
+        pending, self.pending = self.pending, None
+        return pending
+
+    def settle(self, residual: torch.Tensor) -> torch.Tensor:
+        """Add pending partial sums into `residual` now (for a reader that cannot fold them)."""
+        pending = self.take_pending()
+        if pending is not None:
+            from ..kernels import ops
+            ops.add_planes_(residual, pending)
+        return residual
 
 
 def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_rows=()):

@@ -187,10 +187,14 @@ def _decode_ahead(stepper, sampler, active: List[_Live], options, stop, context,
     tokens: it takes them from the device. What the host can foresee (the token budget, the
     context) decides whether that next step may be enqueued at all; a stop token it cannot
     foresee, so when one ends a sequence the step already in flight has carried that sequence
-    one token too far. That row is dropped (rows do not depend on one another, and the slot is
-    closed anyway), the other rows of that step count as usual, and the caller goes on with
-    the smaller set. The decisions per sequence are those of the plain loop, in its order.
-    Returns the sequences that go on, each with its pending token.
+    one token too far, in a batch that the plain loop would not have formed. Where the stepper
+    can take a step back (`can_rewind`: keys and values are just written again) the step in
+    flight is dropped whole and the caller runs it again for the smaller set, so every token
+    comes from exactly the batches the plain loop runs and the results are the same bit for
+    bit. Otherwise (sequences with fixed-size state) only the ended sequence's row is dropped
+    (rows do not depend on one another beyond rounding, and the slot is closed anyway) and the
+    other rows of that step count as usual. The decisions per sequence are those of the plain
+    loop, in its order. Returns the sequences that go on, each with its pending token.
     """
     check = getattr(stepper, "check_device_status", None)
     slots = [seq.slot for seq in active]
@@ -220,6 +224,10 @@ def _decode_ahead(stepper, sampler, active: List[_Live], options, stop, context,
             current = following
             continue
         # a stop token ended some: the step in flight still carried them
+        if getattr(stepper, "can_rewind", False):
+            if still:
+                stepper.rewind([seq.slot for seq in still], 1)  # that step never happened
+            return still  # each with the token it just emitted pending, to be fed again
         picked = following.ids()
         if check is not None:
             check()

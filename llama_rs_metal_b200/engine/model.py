@@ -10,6 +10,8 @@ from ..kernels import ops
 from ..parts.base import Block, ModelPlan, PartSpec
 from ..parts.linear import LinearWeight
 from ..registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part
+
+FAMILIES = {"mixer": (MIXERS, "mixer"), "feed_forward": (FEED_FORWARDS, "feed-forward"), "norm": (NORMS, "norm")}
 from ..runtime import Runtime
 from ..weights.loader import TensorSpec
 
@@ -33,19 +35,26 @@ class DecoderModel:
         for layer in plan.layers:
             if layer.block not in BLOCKS:
                 raise InvalidError(f"block kind {layer.block!r} is not registered")
-            parts = {
-                "mixer": build_part(MIXERS, layer.mixer, "mixer"),
-                "feed_forward": build_part(FEED_FORWARDS, layer.feed_forward, "feed-forward"),
-                "mixer_norm": build_part(NORMS, layer.mixer_norm, "norm"),
-                "feed_forward_norm": build_part(NORMS, layer.feed_forward_norm, "norm"),
-            }
-            self.blocks.append(BLOCKS[layer.block](**parts))
-            self._names.append({role: _full_names(getattr(layer, role), part)
-                                for role, part in parts.items()})
+            block_class = BLOCKS[layer.block]
+            # the block says which roles a layer of its kind has, and of which family each is
+            parts = {}
+            for role, family in block_class.roles.items():
+                if role not in layer.parts:
+                    raise InvalidError(f"a {layer.block!r} layer needs a part for the role {role!r}")
+                if family not in FAMILIES:
+                    raise InvalidError(f"block {layer.block!r}: role {role!r} has unknown family {family!r}")
+                table, label = FAMILIES[family]
+                parts[role] = build_part(table, layer.parts[role], label)
+            unknown = sorted(set(layer.parts) - set(parts))
+            if unknown:
+                raise InvalidError(f"a {layer.block!r} layer has no role {', '.join(unknown)}")
+            self.blocks.append(block_class(**parts))
+            self._names.append({role: _full_names(layer.parts[role], part) for role, part in parts.items()})
         self.final_norm = build_part(NORMS, plan.final_norm, "norm")
         self._final_names = _full_names(plan.final_norm, self.final_norm)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[LinearWeight] = None
+        self.unexpected_tensors: tuple = ()  # stored names the loader skipped (set by the loader's caller)
         self._check_schedule()
 
     # -- schedule and cache --------------------------------------------------------
@@ -68,7 +77,7 @@ class DecoderModel:
         out = {}
         for entry in self.plan.schedule:
             if entry.writes_cache:
-                out[entry.cache] = self.blocks[entry.layer].mixer.cache_request()
+                out[entry.cache] = self.blocks[entry.layer].cache_request()
         return [out[i] for i in range(len(out))]
 
     @property
@@ -76,7 +85,7 @@ class DecoderModel:
         """True when every part only enqueues device work, so a decode step can be a CUDA graph."""
         parts = [self.final_norm]
         for block in self.blocks:
-            parts += [block, block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm]
+            parts += [block, *block.parts.values()]
         return all(p.graph_safe for p in parts)
 
     # -- weights ---------------------------------------------------------------------
@@ -108,15 +117,30 @@ class DecoderModel:
     # -- forward ---------------------------------------------------------------------
     def forward(self, ctx, cache) -> torch.Tensor:
         """float32 logits [len(ctx.wanted_rows), vocab] for one step."""
-        hidden = ops.embed_rows(self.embedding, ctx.token_ids)
-        for entry in self.plan.schedule:
+        plan = self.plan
+        hidden = ops.embed_rows(self.embedding, ctx.token_ids, plan.embedding_scale)
+        wanted = ctx.wanted_rows.numel() > 0
+        schedule = plan.schedule
+        for i, entry in enumerate(schedule):
             ctx.entry = entry
             view = cache.view(entry.cache) if cache is not None else None
+            # may this block's last product leave its K slices for the next reader of the stream?
+            if i + 1 < len(schedule):
+                ctx.next_folds_pending = self.blocks[schedule[i + 1].layer].folds_pending_on_entry
+            else:
+                ctx.next_folds_pending = wanted and self.final_norm.folds_pending
             hidden = self.blocks[entry.layer].forward(hidden, ctx, view)
+            if ctx.pending is not None and not ctx.next_folds_pending:
+                ctx.settle(hidden)  # a block left sums its successor cannot add itself
         ctx.entry = None
-        if ctx.wanted_rows.numel() == 0:
-            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=hidden.device)
+        ctx.next_folds_pending = False
+        if not wanted:
+            ctx.take_pending()
+            return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=hidden.device)
         # the head runs only on the rows whose logits are wanted
         # (crates/model-runtime/src/execute.rs:238-247 does it for the last row)
         x = self.final_norm.forward(hidden, ctx, rows=ctx.wanted_rows)
-        return self.head(x, out_dtype=torch.float32)
+        logits = self.head(x, out_dtype=torch.float32)
+        if plan.logit_scale is not None:
+            ops.scale_(logits, plan.logit_scale)
+        return logits

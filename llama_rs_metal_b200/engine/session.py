@@ -65,7 +65,8 @@ class Engine:
 
 
 def build_model(model_dir: str, runtime: Runtime):
-    """(config, plan, model with weights bound, bytes of weights) for a model folder."""
+    """(config, plan, model with weights bound, bytes of weights) for a model folder. Stored
+    tensors the model has no use for are skipped; their names are in `model.unexpected_tensors`."""
     root = read_config_json(model_dir)
     arch = find_architecture(root)
     config = arch.config_class.from_dict(root)
@@ -74,6 +75,7 @@ def build_model(model_dir: str, runtime: Runtime):
     tensors = load_tensors(model_dir, model.tensor_specs(), ignored=plan.ignored_names,
                            float32=runtime.float32, device=runtime.device)
     model.bind(tensors)
+    model.unexpected_tensors = tuple(tensors.unexpected)
     weight_bytes = sum(t.numel() * t.element_size() for t in tensors.values())
     return config, plan, model, weight_bytes
 
@@ -84,6 +86,9 @@ class Model:
         self.model_dir = model_dir
         self.runtime = Runtime(engine.device, dtype)
         self.config, self.plan, self.decoder, self.weight_bytes = build_model(model_dir, self.runtime)
+        # stored tensors no part asked for: skipped, as the reference skips unknown names
+        # (crates/model-format/src/mlx/mod.rs:41-43)
+        self.unexpected_tensors = self.decoder.unexpected_tensors
         stops = set(self.plan.stop_token_ids) | set(read_generation_eos(model_dir))
         self.stop_token_ids = tuple(sorted(stops))
 
@@ -150,6 +155,13 @@ class Session:
     def decode_ahead(self, slots, tokens, previous, picker):
         return self.runner.decode_ahead(slots, tokens, previous, picker)
 
+    @property
+    def can_rewind(self) -> bool:
+        return self.runner.can_rewind
+
+    def rewind(self, slots, tokens: int = 1) -> None:
+        self.runner.rewind(slots, tokens)
+
     # -- many sequences -------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], options: Optional[GenerationOptions] = None,
                  stop_token_ids: Optional[Iterable[int]] = None,
@@ -181,26 +193,47 @@ class Session:
     def prefill(self, tokens: Sequence[int]) -> torch.Tensor:
         """Feed tokens to the session's own sequence; logits of the last one.
 
-        On an empty sequence the tokens run as one step. Afterwards a step holds
-        one token per sequence, so further tokens are fed one by one.
+        The tokens run as one step whatever the sequence already holds: on an empty
+        sequence as a prompt, on a started one as a portion that attends to the cache
+        (crates/model-runtime/src/session.rs:105-164 appends to a session's history the
+        same way, in chunks of 32). A kernel that gave up on a bounded wait poisons the
+        session here, before any logits are handed out.
         """
         tokens = [int(t) for t in tokens]
         if not tokens:
             raise OptionsError("prompt must contain at least one token")
         if len(self._own_tokens) + len(tokens) > self.context:
             raise ContextError(self.context, len(self._own_tokens) + len(tokens))
+        if self._cancel:
+            raise CancelledError("cancelled")
         if self._own_slot is None:
             self._own_slot = self.cache.open_slot()
-        if not self._own_tokens:
-            chunks = [tokens]
-        else:
-            chunks = [[t] for t in tokens]
-        for chunk in chunks:
-            if self._cancel:
-                raise CancelledError("cancelled")
-            out = self.runner.step([StepEntry(self._own_slot, chunk, [len(chunk) - 1])])
-            self._own_tokens.extend(chunk)
-            self._last_logits = out[0]
+        out = self.runner.step([StepEntry(self._own_slot, tokens, [len(tokens) - 1])])
+        self._own_tokens.extend(tokens)
+        self.runner.check_device_status()  # reads 4 bytes back when a kernel with bounded waits ran
+        self._last_logits = out[0]
+        return self._last_logits
+
+    def synchronize_prompt(self, tokens: Sequence[int]) -> torch.Tensor:
+        """Make the session's own sequence equal `tokens` with as little work as possible: if
+        they go on from what the sequence holds only the new tokens are fed, otherwise the
+        sequence starts over (crates/llama-rs/src/session.rs:47-77). Logits of the last token."""
+        tokens = [int(t) for t in tokens]
+        if not tokens:
+            raise OptionsError("prompt must contain at least one token")
+        if len(tokens) > self.context:
+            raise ContextError(self.context, len(tokens))
+        if any(not 0 <= t < self.model.plan.vocab_size for t in tokens):
+            raise OptionsError("token outside vocabulary")
+        held = self._own_tokens
+        if tokens[:len(held)] != held:
+            self.reset()
+            held = self._own_tokens
+        suffix = tokens[len(held):]
+        if suffix:
+            return self.prefill(suffix)
+        if self._last_logits is None:
+            raise OptionsError("prompt must contain at least one token")
         return self._last_logits
 
     def decode(self, token: int) -> torch.Tensor:

@@ -1,20 +1,28 @@
 """The step function: run the tokens a step brings, as one batch, from the cache.
 
-A step is a list of entries, one per sequence. Either every sequence is at its
-first token (a *prefill* step: whole prompts of unequal lengths) or every
-sequence goes on by exactly one token (a *decode* step). Everything is checked
-before anything is launched or changed, so a rejected step leaves the cache as
-it was (the reference validates before submitting for the same reason,
-crates/model-runtime/src/session.rs:114-130). Sequences' lengths advance only
-after the step's kernels are enqueued.
+A step is a list of entries, one per sequence, each bringing one or more tokens
+that go on from where its sequence stands. Three phases share one forward pass:
+every sequence at its first token is a *prefill* step (whole prompts of unequal
+lengths; attention reads the step's own keys); every sequence going on by
+exactly one token is a *decode* step; anything else (several tokens onto a
+started sequence, as the reference's prefill on a session with history does,
+crates/model-runtime/src/session.rs:105-164, or a mix of the above) is an
+*extend* step: keys and values are stored first and attention reads the cache.
+Everything is checked before anything is launched or changed, so a rejected
+step leaves the cache as it was (the reference validates before submitting for
+the same reason, session.rs:114-130). Sequences' lengths advance only after
+the step's kernels are enqueued.
 
 A decode step's launches are captured once per (batch size, length bucket) in
 a CUDA graph and replayed: its int32 inputs live in a static device buffer
-that each step overwrites with one host-to-device copy.
+that each step overwrites with one host-to-device copy. Launch geometry
+depends on the lengths only through the bucket, with or without graphs, so
+both ways compute the same bits.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from collections import OrderedDict
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -28,7 +36,7 @@ from .model import DecoderModel
 
 
 def classify_step(entries: Sequence[StepEntry], lengths_before: Sequence[int]) -> str:
-    """ "prefill" or "decode"; raises for an empty, mixed or malformed step."""
+    """ "prefill", "decode" or "extend"; raises for an empty or malformed step."""
     if not entries:
         raise InvalidError("a step needs at least one entry")
     if any(len(e.tokens) == 0 for e in entries):
@@ -37,8 +45,7 @@ def classify_step(entries: Sequence[StepEntry], lengths_before: Sequence[int]) -
         return "prefill"
     if all(n > 0 for n in lengths_before) and all(len(e.tokens) == 1 for e in entries):
         return "decode"
-    raise UnsupportedError(
-        "the sequences of a step either all start at their first token or all go on by one token")
+    return "extend"
 
 
 def validate_entries(entries: Sequence[StepEntry], vocab_size: int) -> None:
@@ -82,6 +89,7 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.greedy: Optional[torch.Tensor] = None  # int32 [B]: argmax of every row, part of the graph
         self.launches = 0
+        self.reports_status = False  # the graph holds kernels that write the device status word
 
     def upload(self, host: np.ndarray) -> None:
         i = self.turn % self.RING
@@ -120,7 +128,10 @@ class StepRunner:
         self.poisoned = False
         self.steps_run = 0
         self.use_graphs = use_graphs and runtime.device.type == "cuda" and model.graph_safe
-        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        # captured decode steps by (batch size, length bucket), least recently used first; each
+        # holds its own [batch, vocab] logits, so only the newest `max_graphs` are kept
+        self._graphs: "OrderedDict[Tuple[int, int], _DecodeGraph]" = OrderedDict()
+        self.max_graphs = 24
         self._pool = None
         self.last_launches = 0  # kernels of this library launched by the last step
         # pinned buffers for the ids of steps that do not wait (two are in flight at most)
@@ -147,7 +158,10 @@ class StepRunner:
         validate_entries(entries, self.model.plan.vocab_size)
         before = [cache.length(e.slot) for e in entries]
         phase = classify_step(entries, before)
-        growth = [(e.slot, n + len(e.tokens)) for e, n in zip(entries, before)]
+        if phase == "prefill":  # attention reads the step's own keys: the cache keeps what later steps see
+            growth = [(e.slot, n + len(e.tokens)) for e, n in zip(entries, before)]
+        else:                   # attention reads the cache from each portion's first query on
+            growth = [(e.slot, n + len(e.tokens), n) for e, n in zip(entries, before)]
         cache.check_growth(growth)  # raises before anything changes
         cache.grow(growth)
         cache.sync()
@@ -157,6 +171,8 @@ class StepRunner:
                 logits = self._decode_with_graph(entries, before, borrow, dest_rows)
             else:
                 ctx = pack_step(entries, before, self.runtime, phase, dest_rows)
+                if phase == "decode":  # the geometry a captured step would have
+                    ctx.max_kv_len = length_bucket(ctx.max_kv_len)
                 start = ops.launch_count()
                 logits = self.model.forward(ctx, cache)
                 self.last_launches = ops.launch_count() - start
@@ -240,9 +256,21 @@ class StepRunner:
     # -- decode that does not wait for its own result -------------------------------------
     @property
     def can_decode_ahead(self) -> bool:
-        """True when decode steps can take their tokens from the device (CUDA graphs on, no
-        windowed cache group)."""
-        return self.use_graphs and all(g.request.window is None for g in self.cache.kv_groups)
+        """True when decode steps can take their tokens from the device (CUDA graphs on)."""
+        return self.use_graphs
+
+    @property
+    def can_rewind(self) -> bool:
+        """True when the last decode step of some sequences can be taken back: keys and values
+        are simply written again, fixed-size state cannot be un-updated."""
+        return not self.cache.state_groups
+
+    def rewind(self, slots: Sequence[int], tokens: int = 1) -> None:
+        """Forget the last `tokens` tokens of started sequences (their cache rows stay where
+        they are and are overwritten when the positions are fed again)."""
+        if not self.can_rewind:
+            raise UnsupportedError("sequences with fixed-size state cannot be rewound")
+        self.cache.shorten(slots, tokens)
 
     def decode_ahead(self, slots: Sequence[int], tokens: Optional[Sequence[int]], previous,
                      picker) -> "PendingPicks":
@@ -261,20 +289,14 @@ class StepRunner:
         token_array = np.zeros(batch, dtype=np.int64) if tokens is None else np.asarray(tokens, dtype=np.int64)
         prepared = self._prepare_decode(slot_array, token_array)
         if prepared is None:
-            raise UnsupportedError("decode_ahead needs open, started sequences and no windowed cache group")
+            raise UnsupportedError("decode_ahead needs open, started sequences")
         host, before = prepared
         try:
-            key = (batch, length_bucket(int(before.max()) + 1))
-            graph = self._graphs.get(key)
-            if graph is None:
-                graph = self._graphs[key] = _DecodeGraph(self, *key)
+            graph = self._graph_for(batch, int(before.max()) + 1)
             graph.upload(host)
             if tokens is None:
                 graph.static[:batch].copy_(previous.device_ids)  # the ids chosen by the step before
-            if graph.graph is None:
-                self._capture(graph)
-            graph.graph.replay()
-            self.last_launches = graph.launches
+            self._launch(graph)
             device_ids = picker(graph.logits)
             pending = self._pending_slot()
             pending.launch(device_ids, batch)
@@ -303,20 +325,36 @@ class StepRunner:
 
     def _replay(self, host: np.ndarray, batch: int, max_kv_len: int, wanted: List[int],
                 borrow: bool) -> torch.Tensor:
-        key = (batch, length_bucket(max_kv_len))
-        graph = self._graphs.get(key)
-        if graph is None:
-            graph = self._graphs[key] = _DecodeGraph(self, *key)
+        graph = self._graph_for(batch, max_kv_len)
         graph.upload(host)
-        if graph.graph is None:
-            self._capture(graph)
-        graph.graph.replay()
-        self.last_launches = graph.launches
+        self._launch(graph)
         logits = graph.logits
         if wanted != list(range(batch)):
             index = torch.tensor(wanted, dtype=torch.long, device=logits.device)
             return logits.index_select(0, index)
         return logits if borrow else logits.clone()
+
+    def _graph_for(self, batch: int, max_kv_len: int) -> _DecodeGraph:
+        key = (batch, length_bucket(max_kv_len))
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._graphs[key] = _DecodeGraph(self, *key)
+            while len(self._graphs) > self.max_graphs:
+                self._graphs.popitem(last=False)  # the least recently used one and its buffers
+        else:
+            self._graphs.move_to_end(key)
+        return graph
+
+    def _launch(self, graph: _DecodeGraph) -> None:
+        from ..kernels import gemm_dispatch
+        if graph.graph is None:
+            self._capture(graph)
+        graph.graph.replay()
+        self.last_launches = graph.launches
+        if graph.reports_status:
+            # a replay launches kernels with bounded waits without passing through their Python
+            # wrappers: say here that the status word has to be read at the next check
+            gemm_dispatch.mark_status_dirty()
 
     def _capture(self, graph: _DecodeGraph) -> None:
         # One eager run first: it loads every kernel the step needs and writes
@@ -325,8 +363,10 @@ class StepRunner:
         torch.cuda.current_stream().synchronize()
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
+        from ..kernels import gemm_dispatch
         captured = torch.cuda.CUDAGraph()
         start = ops.launch_count()
+        status_launches = gemm_dispatch.status_launch_count()
         with torch.cuda.graph(captured, pool=self._pool):
             graph.logits = self.model.forward(graph.ctx, self.cache)
             # the greedy pick rides along (two small kernels): a sampler that wants it finds it
@@ -334,4 +374,5 @@ class StepRunner:
             graph.greedy = ops.argmax_rows(graph.logits)
             graph.logits.greedy_ids = graph.greedy
         graph.launches = ops.launch_count() - start  # the pick's two kernels included
+        graph.reports_status = gemm_dispatch.status_launch_count() > status_launches
         graph.graph = captured

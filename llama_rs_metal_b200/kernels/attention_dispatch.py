@@ -7,7 +7,12 @@ prompts with head size 64 or 128 run the TMA + tcgen05 kernel
 64-token pages otherwise runs the warp-level tiled kernels (csrc/attention_tiled.cu).
 A bfloat16 decode step of a layer that writes its own unwindowed cache runs rotation,
 cache write, attention and the merge of the splits as one cluster kernel
-(csrc/attention_decode_cluster.cu).
+(csrc/attention_decode_cluster.cu). A step that appends several tokens to started
+sequences stores its keys first and attends over the cache (row-wise, or the tiled
+extend kernel in bfloat16).
+
+`attend` is the one call a mixer makes: it takes the step's projection and picks
+rotation, cache write and attention kernels for the step's phase and geometry.
 """
 from __future__ import annotations
 
@@ -37,7 +42,7 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
     if (not force_rowwise and not force_warp_level and q.dtype == torch.bfloat16 and aligned
             and lib.lrm_attention_prefill_umma_supports(d)):
         from . import gemm_dispatch
-        gemm_dispatch._status_dirty = True
+        gemm_dispatch.mark_status_dirty()
         _done(lib.lrm_attention_prefill_umma(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), T,
                                              cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
                                              ctypes.c_float(scale), window,
@@ -81,9 +86,30 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
         return
     _done(lib.lrm_attention_paged_rowwise(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _code(q.dtype),
                                           _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
-                                          _ptr(kv_lens), B, Hq, kv.kv_heads, d, kv.page_size,
+                                          _ptr(kv_lens), None, None, B, Hq, kv.kv_heads, d, kv.page_size,
                                           ctypes.c_float(scale), window, _stream()),
           "attention_paged_rowwise")
+
+
+def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_seq_len: int, scale: float,
+           window: int) -> None:
+    """Packed queries, several per sequence, over the cache that already holds the step's keys."""
+    T, Hq, d = q.shape
+    lib = library.load()
+    if _tiled(q, kv.page_size):
+        _done(lib.lrm_attention_extend_tiled(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _ptr(cu_seqlens),
+                                             _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
+                                             _ptr(kv_lens), cu_seqlens.numel() - 1, max_seq_len, Hq,
+                                             kv.kv_heads, d, kv.page_size, ctypes.c_float(scale), window,
+                                             _stream()), "attention_extend_tiled")
+        return
+    # the same arithmetic, key by key in ascending order, as the packed row-wise kernel: in
+    # float32 a prompt cut into portions gives the bits of the whole prompt
+    _done(lib.lrm_attention_paged_rowwise(_ptr(q), _ptr(kv.k), _ptr(kv.v), _ptr(out), _code(q.dtype),
+                                          _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
+                                          _ptr(kv_lens), _ptr(seq_of_token), _ptr(positions), T, Hq,
+                                          kv.kv_heads, d, kv.page_size, ctypes.c_float(scale), window,
+                                          _stream()), "attention_paged_rowwise")
 
 
 _cluster_ok = {}
@@ -154,3 +180,48 @@ def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slot
         _ptr(qkv), _ptr(positions), _ptr(inv_freq), rotary, _ptr(kv.k), _ptr(kv.v), _ptr(dest_rows), _ptr(out),
         _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots), _ptr(kv_lens), B, q_heads, kv.kv_heads, d,
         kv.page_size, ctypes.c_float(scale), cluster, _stream()), "attention_decode_cluster")
+
+
+# --------------------------------------------------------------------------- one call for a mixer
+def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx, cache, writes_cache: bool,
+           cache_entry: int, scale: float, window):
+    """A layer's attention for one step: position rotation, cache write and attention, with the
+    kernels chosen here for the step's phase, dtype and geometry. -> mixed heads [T, q_heads * d].
+
+    projected: the step's fused [T, (q_heads + 2 kv_heads) * d] q|k|v projection when the layer
+        writes its cache entry, else its [T, q_heads * d] queries (the entry was filled, in this
+        step, by the layer that owns it).
+    rotary: (inverse frequencies float32 [R/2], R) for a split-half rotation applied here, or None
+        (no rotation: another scheme already transformed q and k, or there is none).
+    ctx: the StepContext; cache: the KeyValueView of `cache_entry`; window: keys a query sees, or None.
+    """
+    from . import ops
+    inv_freq, width = rotary if rotary is not None else (None, 0)
+    phase = ctx.phase
+    if writes_cache:
+        if (phase == "decode" and cache is not None and projected.dtype == torch.bfloat16
+                and decode_fused_supported(projected.dtype, head_dim, cache.page_size, width,
+                                           window or cache.window)
+                and decode_prefers_fused(projected.shape[0], kv_heads, q_heads // kv_heads, head_dim,
+                                         ctx.max_kv_len)):
+            # rotation, cache write, attention and the merge of the splits in one launch
+            return ops.attention_decode_fused(projected, q_heads, inv_freq, width, ctx.positions, cache,
+                                              ctx.dest_rows[cache.group], ctx.slots, ctx.kv_lens,
+                                              ctx.max_kv_len, scale)
+        prefill = phase == "prefill"
+        q, k, v = ops.rope_store(projected, q_heads, kv_heads, head_dim, inv_freq, width, ctx.positions,
+                                 kv=cache, dest_rows=ctx.dest_rows[cache.group] if cache is not None else None,
+                                 keep_packed=prefill)
+        if prefill:
+            ctx.fresh_kv[cache_entry] = (k, v)
+    else:
+        q, _, _ = ops.rope_store(projected, q_heads, 0, head_dim, inv_freq, width, ctx.positions,
+                                 keep_packed=False)
+        if phase == "prefill":
+            k, v = ctx.fresh_kv[cache_entry]
+    if phase == "prefill":
+        return ops.attention_prefill(q, k, v, ctx.cu_seqlens, ctx.seq_of_token, ctx.max_seq_len, scale, window)
+    if phase == "decode":
+        return ops.attention_decode(q, cache, ctx.slots, ctx.kv_lens, ctx.max_kv_len, scale, window)
+    return ops.attention_extend(q, cache, ctx.cu_seqlens, ctx.seq_of_token, ctx.positions, ctx.slots,
+                                ctx.kv_lens, ctx.max_seq_len, scale, window)

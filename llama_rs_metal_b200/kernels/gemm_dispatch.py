@@ -5,8 +5,11 @@
   leave most SMs idle and cannot split K (few output columns, epilogue other than "add");
 * more rows (prompts, larger decode batches): the TMA + tcgen05 kernel
   (csrc/gemm_bf16_umma.cu), with 128 x 128, 128 x 256 or 256 x 256 tiles, whichever needs less
-  time by a count of rounds over the SMs and the measured cost of a tile; with at most 64 rows and few
-  columns it cuts K into slices that meet by atomic adds in the float32 residual stream;
+  time by a count of rounds over the SMs and the measured cost of a tile;
+* a narrow product that is to be added to the residual stream may be cut into K slices so that
+  every SM works: the slices are stored as planes of an [slices, M, N] tensor, which the next
+  norm adds in slice order (gemm_bf16_slices); nothing meets by atomics, so the same step gives
+  the same bits every time;
 * every shape the others refuse (K not a multiple of 8, unaligned views): the
   warp-level tiled kernel (csrc/gemm_bf16_mma.cu), which takes any M, N, K.
 """
@@ -26,6 +29,19 @@ umma_width: Optional[int] = None  # tests pin the tile: 128 (128 x 128), 256 (12
 
 _status: Dict[int, torch.Tensor] = {}
 _status_dirty = False
+_status_launches = 0  # launches (or captures) so far of kernels that write the status word
+
+
+def mark_status_dirty() -> None:
+    """A kernel with bounded waits was launched (directly, or by replaying a CUDA graph that holds
+    one): the next check_status() reads the status word."""
+    global _status_dirty, _status_launches
+    _status_dirty = True
+    _status_launches += 1
+
+
+def status_launch_count() -> int:
+    return _status_launches
 
 
 def _status_word(device: torch.device) -> torch.Tensor:
@@ -87,13 +103,14 @@ stream_shape = None  # tests and tuning: (warps per CTA, K slices) of the stream
 
 def _few_rows_plan(M: int, N: int, K: int, mode: int):
     """For 9-64 rows: (use the tensor-core kernel?, K slices). Measured at the 1B layer sizes:
-    many column tiles run as they are from 13 rows on; a product that adds into the residual is cut
-    into as many K slices as keep every item in one round over the SMs, except a small one (8 MB of
-    weights, up to 32 rows), which the streaming kernel does faster; the rest streams."""
+    many column tiles run as they are from 13 rows on; a product whose slices the next norm adds
+    (mode 4) is cut into as many K slices as keep every item in one round over the SMs, except a
+    small one (8 MB of weights, up to 32 rows), which the streaming kernel does faster; the rest
+    streams."""
     tiles = -(-N // 128)
     if tiles >= SM_COUNT // 2:
         return M > 12, 1
-    if mode == 2:
+    if mode == 4:
         if M <= 32 and N * K <= 4 * 1024 * 1024:
             return False, 1
         k_blocks = -(-K // 64)
@@ -101,28 +118,67 @@ def _few_rows_plan(M: int, N: int, K: int, mode: int):
     return False, 1
 
 
-def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int) -> None:
-    """out (mode 0 bf16 store, 1 f32 store, 2 f32 add in place, 3 silu gate) = x . weight^T."""
-    global _status_dirty
+def _fast_kernels(x: torch.Tensor, weight: torch.Tensor, lib):
+    M, K = x.shape
+    N = weight.shape[0]
+    aligned = x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+    fast = not force_tiled and aligned
+    return (fast and bool(lib.lrm_gemm_bf16_stream_supports(M, N, K)),
+            fast and bool(lib.lrm_gemm_bf16_umma_supports(M, N, K)))
+
+
+def gemm_bf16_slices(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
+    """x . weight^T as float32 partial products over K slices, [slices, M, N], whose sum in plane
+    order is the product; None when this shape is not worth cutting (the caller then adds the
+    whole product in place). For products that go into the residual stream."""
     M, K = x.shape
     N = weight.shape[0]
     lib = library.load()
-    aligned = x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
-    fast = not force_tiled and aligned
-    stream_ok = fast and lib.lrm_gemm_bf16_stream_supports(M, N, K)
-    umma_ok = fast and lib.lrm_gemm_bf16_umma_supports(M, N, K)
+    stream_ok, umma_ok = _fast_kernels(x, weight, lib)
+    if not stream_ok:
+        return None
+    use_umma, splits = False, 1
+    if umma_ok and M > STREAM_ROWS and not force_stream:
+        use_umma, splits = _few_rows_plan(M, N, K, 4)
+    if use_umma:
+        planes = lib.lrm_gemm_bf16_umma_slices(K, splits)
+        if planes <= 1:
+            return None
+        out = torch.empty((planes, M, N), dtype=torch.float32, device=x.device)
+        mark_status_dirty()
+        held = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // K
+        _done(lib.lrm_gemm_bf16_umma_rows(_ptr(x), _ptr(weight), _ptr(out), M, min(max(M, 32), max(M, held)), N, K,
+                                          4, 0 if umma_width is None else tile_choice(M, N, K, 4), splits,
+                                          _ptr(_status_word(x.device)), _stream()), "gemm_bf16_umma")
+        return out
+    warps, wanted = stream_shape if stream_shape is not None else (0, 0)
+    planes = lib.lrm_gemm_bf16_stream_slices(M, N, K, wanted)
+    if planes <= 1:
+        return None
+    out = torch.empty((planes, M, N), dtype=torch.float32, device=x.device)
+    _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, 4, warps, wanted, _stream()),
+          "gemm_bf16_stream")
+    return out
+
+
+def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int) -> None:
+    """out (mode 0 bf16 store, 1 f32 store, 2 f32 add in place, 3 silu gate) = x . weight^T."""
+    M, K = x.shape
+    N = weight.shape[0]
+    lib = library.load()
+    stream_ok, umma_ok = _fast_kernels(x, weight, lib)
     tile, splits = tile_choice(M, N, K, mode), 1
     if stream_ok and umma_ok and M > STREAM_ROWS and not force_stream:
         use_umma, splits = _few_rows_plan(M, N, K, mode)
         stream_ok = not use_umma
         tile = 0 if umma_width is None else tile
     if stream_ok:
-        warps, slices = stream_shape if stream_shape is not None else (0, 0)
-        _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, warps,
-                                              slices if mode == 2 else 0, _stream()), "gemm_bf16_stream")
+        warps = stream_shape[0] if stream_shape is not None else 0
+        _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, warps, 0,
+                                              _stream()), "gemm_bf16_stream")
         return
     if umma_ok:
-        _status_dirty = True
+        mark_status_dirty()
         # rows of x that its storage holds beyond M may be named in the tensor map (see the kernel)
         held = (x.untyped_storage().nbytes() // x.element_size() - x.storage_offset()) // K
         _done(lib.lrm_gemm_bf16_umma_rows(_ptr(x), _ptr(weight), _ptr(out), M, min(max(M, 32), max(M, held)), N, K,

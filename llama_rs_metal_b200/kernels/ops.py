@@ -83,13 +83,15 @@ def _activation(rows: int, width: int, dtype: torch.dtype, device) -> torch.Tens
 
 
 # --------------------------------------------------------------------------- embedding
-def embed_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-    """float32 [T, h] rows of `table` ([vocab, h], float32 or bfloat16) at int32 ids [T]."""
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, scale: Optional[float] = None) -> torch.Tensor:
+    """float32 [T, h] rows of `table` ([vocab, h], float32 or bfloat16) at int32 ids [T],
+    multiplied by `scale` when one is given."""
     _check(table, "table", dims=2)
     _check(ids, "ids", torch.int32, 1)
     out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=table.device)
     _done(_lib().lrm_embed_rows(_ptr(table), _code(table.dtype), _ptr(ids), _ptr(out),
-                                ids.numel(), table.shape[1], table.shape[0], _stream()), "embed_rows")
+                                ids.numel(), table.shape[1], table.shape[0],
+                                ctypes.c_float(1.0 if scale is None else scale), _stream()), "embed_rows")
     return out
 
 
@@ -178,6 +180,39 @@ def linear(x: torch.Tensor, weight: torch.Tensor, epilogue: str = STORE,
     from . import gemm_dispatch
     gemm_dispatch.gemm_bf16(x, weight, out, mode)
     return out
+
+
+def linear_slices(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
+    """x . weight^T as float32 partial products over K slices [slices, M, N] (their sum in plane
+    order is the product), or None when this product is not cut. Only narrow bfloat16 products
+    are cut; rms_norm(partials=...) or add_planes_ adds the planes to the residual stream."""
+    _check(x, "x", dims=2)
+    _check(weight, "weight", dims=2)
+    if weight.shape[1] != x.shape[1]:
+        raise InvalidError(f"linear: x has {x.shape[1]} columns, weight has {weight.shape[1]}")
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return None
+    from . import gemm_dispatch
+    return gemm_dispatch.gemm_bf16_slices(x, weight)
+
+
+def add_planes_(x: torch.Tensor, planes: torch.Tensor) -> torch.Tensor:
+    """x += planes[0] + planes[1] + ... (in that order); x float32, planes [n, *x.shape] float32."""
+    _check(x, "x", torch.float32)
+    _check(planes, "planes", torch.float32)
+    if tuple(planes.shape[1:]) != tuple(x.shape):
+        raise InvalidError(f"add_planes_: planes {tuple(planes.shape)} do not match {tuple(x.shape)}")
+    _done(_lib().lrm_add_planes(_ptr(x), _ptr(planes), planes.shape[0], ctypes.c_longlong(x.numel()),
+                                _stream()), "add_planes_")
+    return x
+
+
+def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (float32)."""
+    _check(x, "x", torch.float32)
+    _done(_lib().lrm_scale_inplace(_ptr(x), ctypes.c_float(factor), ctypes.c_longlong(x.numel()), _stream()),
+          "scale_")
+    return x
 
 
 def silu_mul(gate_up: torch.Tensor, block: int) -> torch.Tensor:
@@ -295,6 +330,31 @@ def attention_decode(q: torch.Tensor, kv, slots: torch.Tensor, kv_lens: torch.Te
     return out
 
 
+def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor,
+                     positions: torch.Tensor, slots: torch.Tensor, kv_lens: torch.Tensor, max_seq_len: int,
+                     scale: float, window: Optional[int] = None) -> torch.Tensor:
+    """Several queries per sequence over the cache, which already holds the step's own keys:
+    query t (packed, of sequence seq_of_token[t]) sees the keys up to positions[t]. -> [T, Hq*d]"""
+    _check(q, "q", dims=3)
+    _check(kv.k, "k pages", q.dtype, 4)
+    _check(kv.v, "v pages", q.dtype, 4)
+    _check(kv.page_table, "page table", torch.int32, 2)
+    T, Hq, d = q.shape
+    for name, t, n in (("cu_seqlens", cu_seqlens, None), ("seq_of_token", seq_of_token, T),
+                       ("positions", positions, T), ("slots", slots, cu_seqlens.numel() - 1),
+                       ("kv_lens", kv_lens, cu_seqlens.numel() - 1)):
+        _check(t, name, torch.int32, 1)
+        if n is not None and t.numel() != n:
+            raise InvalidError(f"attention_extend: {name} must have {n} entries")
+    if tuple(kv.k.shape[1:]) != (kv.kv_heads, kv.page_size, d) or Hq % kv.kv_heads:
+        raise InvalidError("attention_extend: cache pages do not match the query geometry")
+    out = _activation(T, Hq * d, q.dtype, q.device)
+    from . import attention_dispatch
+    attention_dispatch.extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_seq_len,
+                              scale, window or 0)
+    return out
+
+
 def attention_decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, window) -> bool:
     from . import attention_dispatch
     return attention_dispatch.decode_fused_supported(dtype, head_dim, page_size, rotary, window)
@@ -339,6 +399,12 @@ def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[t
     attention_dispatch.decode_fused(qkv, positions, inv_freq, rotary, kv, dest_rows, out, slots, kv_lens,
                                     max_kv_len, q_heads, scale)
     return out
+
+
+def attend(projected: torch.Tensor, **geometry) -> torch.Tensor:
+    """A layer's attention for one step from its projection (see attention_dispatch.attend)."""
+    from . import attention_dispatch
+    return attention_dispatch.attend(projected, **geometry)
 
 
 # --------------------------------------------------------------------------- sampling

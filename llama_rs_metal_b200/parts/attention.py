@@ -20,8 +20,11 @@ class Attention(Mixer):
     causal attention with scale head_dim^-1/2 -> output projection, added to
     the residual stream (crates/model-runtime/src/execute.rs:45-112,196).
 
-    A prompt attends to its own freshly projected keys; a decoded token
-    attends to the cache. `window` limits a query to the last `window` keys.
+    A prompt attends to its own freshly projected keys; a decoded token, or a
+    portion of several tokens appended to a started sequence, attends to the
+    cache. `window` limits a query to the last `window` keys. Which kernels run
+    is decided in kernels/attention_dispatch.py (`attend`); a variant mixer
+    overrides `before_rotation` to transform q and k per head.
     """
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -74,50 +77,28 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache, residual):
         entry = ctx.entry
-        table = self.position.rotary_table() if self.position is not None else None
-        inv_freq, rotary = table if table is not None else (None, 0)
-        prefill = ctx.phase == "prefill"
-        if entry.writes_cache:
-            qkv = self.qkv(x)
-            if self.position is not None and table is None:
-                qkv = self._apply_other_position(qkv, ctx)
-            if (not prefill and cache is not None and qkv.dtype == torch.bfloat16
-                    and ops.attention_decode_fused_supported(qkv.dtype, self.head_dim, cache.page_size,
-                                                             rotary if inv_freq is not None else 0,
-                                                             self.window or cache.window)
-                    and ops.attention_decode_prefers_fused(qkv.shape[0], self.num_kv_heads,
-                                                           self.num_heads // self.num_kv_heads, self.head_dim,
-                                                           ctx.max_kv_len)):
-                # rotation, cache write, attention and the merge of the splits in one launch
-                mixed = ops.attention_decode_fused(qkv, self.num_heads, inv_freq, rotary, ctx.positions, cache,
-                                                   ctx.dest_rows[cache.group], ctx.slots, ctx.kv_lens,
-                                                   ctx.max_kv_len, self.scale)
-                return self.out(mixed, epilogue=ops.ADD, out=residual)
-            q, k, v = ops.rope_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim, inv_freq,
-                                     rotary, ctx.positions, kv=cache,
-                                     dest_rows=ctx.dest_rows[cache.group] if cache is not None else None,
-                                     keep_packed=prefill)
-            if prefill:
-                ctx.fresh_kv[entry.cache] = (k, v)
-        else:
-            # this layer reads keys and values another layer stored
-            q_proj = self.q_only(x)
-            q, _, _ = ops.rope_store(q_proj, self.num_heads, 0, self.head_dim, inv_freq, rotary,
-                                     ctx.positions, keep_packed=False)
-            if prefill:
-                k, v = ctx.fresh_kv[entry.cache]
-        if prefill:
-            mixed = ops.attention_prefill(q, k, v, ctx.cu_seqlens, ctx.seq_of_token, ctx.max_seq_len,
-                                          self.scale, self.window)
-        else:
-            mixed = ops.attention_decode(q, cache, ctx.slots, ctx.kv_lens, ctx.max_kv_len,
-                                         self.scale, self.window)
-        return self.out(mixed, epilogue=ops.ADD, out=residual)
+        projected = (self.qkv if entry.writes_cache else self.q_only)(x)
+        projected = self.before_rotation(projected, ctx, entry.writes_cache)
+        rotary = self.position.rotary_table() if self.position is not None else None
+        mixed = ops.attend(projected, q_heads=self.num_heads, kv_heads=self.num_kv_heads,
+                           head_dim=self.head_dim, rotary=rotary, ctx=ctx, cache=cache,
+                           writes_cache=entry.writes_cache, cache_entry=entry.cache, scale=self.scale,
+                           window=self.window)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
 
-    def _apply_other_position(self, qkv, ctx):
-        T = qkv.shape[0]
+    def before_rotation(self, projected, ctx, has_keys: bool):
+        """Hook between the projection and the kernels: [T, (Hq + 2 Hk) d] when `has_keys`, else
+        [T, Hq d] queries. A variant mixer transforms q and k per head here (a norm of each
+        head, a bias) and returns the same layout. As built: a position scheme that is not a
+        rotary table transforms q and k here."""
+        if self.position is None or self.position.rotary_table() is not None:
+            return projected
+        T = projected.shape[0]
         nq, nk = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
-        q = qkv[:, :nq].reshape(T, self.num_heads, self.head_dim)
-        k = qkv[:, nq:nq + nk].reshape(T, self.num_kv_heads, self.head_dim)
+        q = projected[:, :nq].reshape(T, self.num_heads, self.head_dim)
+        if not has_keys:
+            q, _ = self.position.apply(q, q[:, :0], ctx)
+            return q.reshape(T, nq).contiguous()
+        k = projected[:, nq:nq + nk].reshape(T, self.num_kv_heads, self.head_dim)
         q, k = self.position.apply(q, k, ctx)
-        return torch.cat([q.reshape(T, nq), k.reshape(T, nk), qkv[:, nq + nk:]], dim=1).contiguous()
+        return torch.cat([q.reshape(T, nq), k.reshape(T, nk), projected[:, nq + nk:]], dim=1).contiguous()

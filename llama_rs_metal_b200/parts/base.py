@@ -31,15 +31,43 @@ class PartSpec:
     names: Mapping[str, str] = field(default_factory=dict)  # own name -> full checkpoint name
 
 
-@dataclass(frozen=True)
 class LayerSpec:
-    """One layer's parts. `block` says how they are arranged (e.g. "pre_norm")."""
+    """One layer: the kind of block that arranges it, and its parts by role.
 
-    block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    Which roles a layer has is the block's business: the registered block class names them
+    and the family each belongs to (`Block.roles`), the engine builds one part per role and
+    hands them to the block. The usual four (a mixer and a feed-forward, each behind a norm)
+    can be given by name; any other set goes in `parts`.
+    """
+
+    __slots__ = ("block", "parts")
+
+    def __init__(self, block: str, mixer: Optional[PartSpec] = None, feed_forward: Optional[PartSpec] = None,
+                 mixer_norm: Optional[PartSpec] = None, feed_forward_norm: Optional[PartSpec] = None,
+                 parts: Optional[Mapping[str, PartSpec]] = None):
+        named = {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
+                 "feed_forward_norm": feed_forward_norm}
+        merged = {role: spec for role, spec in named.items() if spec is not None}
+        merged.update(parts or {})
+        object.__setattr__(self, "block", block)
+        object.__setattr__(self, "parts", merged)
+
+    def __setattr__(self, name, value):
+        raise AttributeError("LayerSpec is immutable; use with_parts()")
+
+    def __getattr__(self, role):
+        # layer.mixer, layer.feed_forward_norm, ... read the part of that role
+        try:
+            return object.__getattribute__(self, "parts")[role]
+        except KeyError:
+            raise AttributeError(role) from None
+
+    def with_parts(self, **changes: PartSpec) -> "LayerSpec":
+        """A copy with some roles' parts replaced or added."""
+        return LayerSpec(self.block, parts={**self.parts, **changes})
+
+    def __repr__(self):
+        return f"LayerSpec({self.block!r}, {dict(self.parts)!r})"
 
 
 @dataclass(frozen=True)
@@ -68,6 +96,8 @@ class ModelPlan:
     head_name: Optional[str]  # None: the head is the embedding table (tied)
     ignored_names: Tuple[str, ...] = ()
     stop_token_ids: Tuple[int, ...] = ()
+    embedding_scale: Optional[float] = None  # embedded rows are multiplied by this (None: 1)
+    logit_scale: Optional[float] = None      # logits are multiplied by this (None: 1)
 
 
 # --------------------------------------------------------------------------- cache requests
@@ -110,6 +140,11 @@ class Part:
 
 
 class Norm(Part):
+    # True when forward() adds `ctx.pending` (partial sums that belong to the residual stream,
+    # see StepContext.pending) to `hidden` itself before it normalizes. A block that is about to
+    # pass a part's output through such a norm may let the part leave its sums there.
+    folds_pending = False
+
     def forward(self, hidden: torch.Tensor, ctx, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """float32 residual [T,h] -> normalized activations [T,h] (or [len(rows),h])."""
         raise NotImplementedError
@@ -155,14 +190,32 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    """Arrangement of one layer's parts; owns them and forwards tensors()/bind() to them."""
+    """Arrangement of one layer's parts. The class says which roles a layer of this kind has
+    and to which family each belongs ("mixer", "feed_forward", "norm"); the engine builds
+    one part per role from the layer's LayerSpec and passes them by role name. A block with
+    other roles (a norm after the mixer, a second feed-forward) overrides `roles`."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm):
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+    roles: Mapping[str, str] = {"mixer": "mixer", "feed_forward": "feed_forward",
+                                "mixer_norm": "norm", "feed_forward_norm": "norm"}
+
+    def __init__(self, **parts: Part):
+        missing = [role for role in self.roles if role not in parts]
+        if missing:
+            raise TypeError(f"{type(self).__name__} needs parts for {', '.join(missing)}")
+        self.parts: Dict[str, Part] = dict(parts)
+        for role, part in parts.items():
+            setattr(self, role, part)
+
+    def cache_request(self):
+        """What this layer asks of the cache (one request per layer): its mixer's."""
+        mixer = self.parts.get("mixer")
+        return mixer.cache_request() if mixer is not None else None
+
+    @property
+    def folds_pending_on_entry(self) -> bool:
+        """True when the first thing forward() does with `hidden` is to pass it through a norm
+        that folds ctx.pending (the layer before may then leave partial sums there)."""
+        return False
 
     def forward(self, hidden: torch.Tensor, ctx, cache) -> torch.Tensor:
         raise NotImplementedError

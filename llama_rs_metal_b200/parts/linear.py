@@ -27,9 +27,18 @@ class LinearWeight:
         return self.weight.dtype == torch.bfloat16 and x_dtype == torch.bfloat16
 
     def __call__(self, x: torch.Tensor, epilogue: str = ops.STORE, out: Optional[torch.Tensor] = None,
-                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                 out_dtype: Optional[torch.dtype] = None, ctx=None) -> torch.Tensor:
+        """`ctx` (a StepContext) may be given with epilogue "add" for a part's last addition into
+        the residual stream: while ctx.may_defer is set, a product that is cut into K slices
+        leaves them in ctx.pending for the next norm to add instead of adding them here."""
         w = self.weight
         if x.dtype == w.dtype:
+            if epilogue == ops.ADD and ctx is not None and ctx.may_defer:
+                planes = ops.linear_slices(x, w)
+                if planes is not None:
+                    ctx.settle(out)  # at most one set of partial sums is pending at a time
+                    ctx.pending = planes
+                    return out
             return ops.linear(x, w, epilogue, out, out_dtype)
         if w.dtype == torch.float32 and x.dtype == torch.bfloat16:
             x32 = ops.cast(x, torch.float32)

@@ -50,4 +50,4 @@ class GatedMLP(FeedForward):
             gated = self.gate_up(x, epilogue=ops.SILU_GATE)
         else:
             gated = ops.silu_mul(self.gate_up(x), self.block)
-        return self.down(gated, epilogue=ops.ADD, out=residual)
+        return self.down(gated, epilogue=ops.ADD, out=residual, ctx=ctx)

@@ -17,6 +17,7 @@ class RMSNorm(Norm):
     (crates/metal-backend/src/shaders/elementwise.metal:31-46; no +1 offset for Llama)."""
 
     graph_safe = True
+    folds_pending = True
 
     def __init__(self, size: int, eps: float):
         self.size = size
@@ -30,4 +31,6 @@ class RMSNorm(Norm):
         self.weight = weights["weight"].contiguous()
 
     def forward(self, hidden, ctx, rows=None):
-        return ops.rms_norm(hidden, self.weight, self.eps, ctx.runtime.dtype, rows=rows)
+        # partial sums a product left for the residual stream are added in the same pass
+        pending = ctx.take_pending()
+        return ops.rms_norm(hidden, self.weight, self.eps, ctx.runtime.dtype, rows=rows, partials=pending)

@@ -42,10 +42,31 @@ def read_model(model_dir):
     return config, tensors
 
 
+class LazyTensors:
+    """Tensors of a model folder read one at a time when asked for, in their stored precision
+    (the functions below widen what they use): for models too large to hold in float64 at once."""
+
+    def __init__(self, model_dir):
+        from safetensors import safe_open
+        self._handle = safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt")
+        self._names = set(self._handle.keys())
+
+    def __getitem__(self, name):
+        return self._handle.get_tensor(name)
+
+    def __contains__(self, name):
+        return name in self._names
+
+
+def read_model_lazily(model_dir):
+    with open(os.path.join(model_dir, "config.json"), "r", encoding="utf-8") as handle:
+        return json.load(handle), LazyTensors(model_dir)
+
+
 # --------------------------------------------------------------------------- parts
 def embedding(table, ids):
     """hidden[t,:] = E[ids[t],:]  (crates/metal-backend/src/shaders/matrix.metal:94-103)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long)].to(F64)
 
 
 def rms_norm(x, weight, eps):
@@ -53,13 +74,13 @@ def rms_norm(x, weight, eps):
     (crates/metal-backend/src/shaders/elementwise.metal:31-46;
     crates/tensor-core/src/lib.rs:64-70)."""
     inv = 1.0 / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
-    return x * inv * weight
+    return x * inv * weight.to(F64)
 
 
 def linear(x, weight):
     """y[t,o] = sum_k W[o,k] x[t,k], no bias
     (crates/metal-backend/src/shaders/matrix.metal:10-37)."""
-    return x @ weight.T
+    return x @ weight.to(F64).T
 
 
 def rope_scaling_fields(config):
@@ -174,8 +195,9 @@ def gated_mlp(x, gate, up, down):
 
 
 # --------------------------------------------------------------------------- the model
-def forward(config, tensors, tokens, window=None):
-    """Logits [T, vocab] (float64) at every position of one whole sequence.
+def forward(config, tensors, tokens, window=None, rows=None):
+    """Logits [T, vocab] (float64) at every position of one whole sequence, or with `rows` at
+    those positions only (the head is the one part whose cost the positions asked for decide).
 
     Order of operations of crates/model-runtime/src/execute.rs:3-249 (Llama
     branch): embedding; per layer norm -> q,k,v -> rope(q), rope(k) ->
@@ -210,6 +232,8 @@ def forward(config, tensors, tokens, window=None):
         hidden = hidden + gated_mlp(x, tensors[p + "mlp.gate_proj.weight"],
                                     tensors[p + "mlp.up_proj.weight"],
                                     tensors[p + "mlp.down_proj.weight"])
+    if rows is not None:
+        hidden = hidden[torch.as_tensor(list(rows), dtype=torch.long)]
     x = rms_norm(hidden, tensors["model.norm.weight"], eps)
     tied = cfg.get("tie_word_embeddings", False)
     head = tensors["model.embed_tokens.weight"] if tied else tensors["lm_head.weight"]

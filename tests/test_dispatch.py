@@ -70,5 +70,7 @@ def test_few_rows_plan():
     plan = gemm_dispatch._few_rows_plan
     assert plan(64, 16384, 2048, 3) == (True, 1)   # many column tiles: the tensor-core kernel as it is
     assert plan(64, 3072, 2048, 0) == (False, 1)   # few tiles and nothing to split: the streaming kernel
-    use, slices = plan(64, 2048, 8192, 2)          # adds into the residual: K in slices
+    use, slices = plan(64, 2048, 8192, 4)          # K slices as planes for the next norm to add
     assert use and 2 <= slices <= 64
+    assert plan(64, 2048, 8192, 2) == (False, 1)   # added in place: never cut (nothing meets by atomics)
+    assert plan(24, 2048, 2048, 4) == (False, 1)   # a small one streams

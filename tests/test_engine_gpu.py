@@ -34,7 +34,7 @@ def entry(slot, tokens, want=None):
 
 
 # --------------------------------------------------------------------------- cutting invariance
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D", "E"])
 def test_float32_logits_are_identical_however_the_tokens_are_cut(engine, model_dirs, name):
     vocab = helpers.TINY[name]["config"]["vocab_size"]
     seqs = [helpers.random_tokens(40 + i, n, vocab) for i, n in enumerate([70, 9, 33])]
@@ -57,6 +57,25 @@ def test_float32_logits_are_identical_however_the_tokens_are_cut(engine, model_d
             got[b].append(out[row:row + 1])
     for b in range(3):
         assert torch.equal(torch.cat(got[b]), whole[b]), f"sequence {b} differs between whole and batched decoding"
+        cache.close_slot(slots[b])
+    # portions onto started sequences: chunks of 17 (tools/benchmarks/verify.py:222-225), 4 + 5
+    # (crates/llama-rs/tests/sessions.rs:10-37), and cuts at 1, 2, 63, 64, 65
+    for sizes in ([17], [4, 5], [1, 1, 61, 1, 1]):
+        slots = [cache.open_slot() for _ in seqs]
+        got, at, i = [[] for _ in seqs], [0] * 3, 0
+        while any(at[b] < len(seqs[b]) for b in range(3)):
+            n = sizes[min(i, len(sizes) - 1)]
+            live = [b for b in range(3) if at[b] < len(seqs[b])]
+            out = runner.step([entry(slots[b], seqs[b][at[b]:at[b] + n]) for b in live])
+            row = 0
+            for b in live:
+                m = min(n, len(seqs[b]) - at[b])
+                got[b].append(out[row:row + m])
+                row, at[b] = row + m, at[b] + m
+            i += 1
+        for b in range(3):
+            assert torch.equal(torch.cat(got[b]), whole[b]), f"sequence {b} differs when cut into portions {sizes}"
+            cache.close_slot(slots[b])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -106,16 +125,14 @@ def test_a_used_slot_does_not_leak_into_its_next_sequence(engine, model_dirs, pl
 
 
 def test_rejected_steps_change_nothing(engine, model_dirs):
-    from llama_rs_metal_b200.errors import CacheMemoryError, ContextError, InvalidError, UnsupportedError
+    from llama_rs_metal_b200.errors import CacheMemoryError, InvalidError
     runner, cache, _ = open_runner(engine, model_dirs["A"], "float32", max_tokens=128, max_slots=2)
     a, b = cache.open_slot(), cache.open_slot()
     good = runner.step([entry(a, [1, 2, 3])]).clone()
     with pytest.raises(InvalidError, match="outside vocabulary"):
         runner.step([entry(a, [256])])
-    with pytest.raises(UnsupportedError):
-        runner.step([entry(a, [4]), entry(b, [5, 6])])         # one goes on, one starts
-    with pytest.raises(UnsupportedError):
-        runner.step([entry(a, [4, 5])])                        # two tokens onto a started sequence
+    with pytest.raises(InvalidError):
+        runner.step([entry(a, [4]), entry(b, [])])             # an entry without a token
     with pytest.raises(InvalidError):
         runner.step([entry(a, [4]), entry(a, [5])])
     with pytest.raises(InvalidError):
@@ -198,9 +215,15 @@ def test_parts_alone(engine, dtype):
         at += n
     helpers.assert_logits_close(out.cpu(), hidden.double() + torch.cat(want), dtype, "attention part")
 
-    block = PreNormBlock(attn, mlp, norm, norm)
+    block = PreNormBlock(mixer=attn, feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm)
     out = block.forward(hidden.to(DEV).clone(), ctx, cache.view(0))
-    assert out.shape == (T, h) and torch.isfinite(out).all()
+    ctx.settle(out)
+    # the block is the two parts behind the norm: hidden += attention(norm(hidden)); += mlp(norm(hidden))
+    after_mixer = hidden.double() + torch.cat(want)
+    x2 = P.rms_norm(after_mixer, nw.double(), 1e-3)
+    want_block = after_mixer + P.gated_mlp(x2, *(mw[k].double() for k in
+                                           ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
+    helpers.assert_logits_close(out.cpu(), want_block, dtype, "pre-norm block")
 
 
 # --------------------------------------------------------------------------- generation
@@ -671,3 +694,330 @@ def test_toy_feed_forward_position_norm_and_block_are_registered_from_outside(en
         for b in range(3):
             if prompts[b] + step + 1 == len(seqs[b]):
                 cache.close_slot(slots[b])
+
+
+# --------------------------------------------------------------------------- portions and mixed steps
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "D", "E"])
+def test_portions_and_mixed_steps_match_the_plain_implementation(engine, model_dirs, plain_models, name, dtype):
+    """One step may bring several tokens onto a started sequence, and sequences that start may
+    share a step with sequences that go on: cuts at 1, 2, 63, 64 and 65 tokens, a request that
+    joins late, all compared with the plain implementation's whole sequences."""
+    vocab = helpers.TINY[name]["config"]["vocab_size"]
+    seqs = [helpers.random_tokens(300 + i, n, vocab) for i, n in enumerate([200, 131, 66])]
+    refs = [P.forward(*plain_models[name], s).numpy() for s in seqs]
+    runner, cache, _ = open_runner(engine, model_dirs[name], dtype)
+    slots = [cache.open_slot() for _ in seqs]
+    at = [0, 0, 0]
+    plan = [  # tokens each sequence brings, step by step (0: it sits this step out)
+        (1, 0, 0), (2, 63, 0), (63, 1, 0), (64, 2, 5), (65, 64, 1), (5, 1, 60),
+    ]
+    for step in plan:
+        entries, rows = [], []
+        for b, n in enumerate(step):
+            n = min(n, len(seqs[b]) - at[b])
+            if n > 0:
+                entries.append(entry(slots[b], seqs[b][at[b]:at[b] + n]))
+                rows.append((b, at[b], n))
+                at[b] += n
+        out = runner.step(entries).cpu()
+        row = 0
+        for b, first, n in rows:
+            helpers.assert_logits_close(out[row:row + n], refs[b][first:first + n], dtype,
+                                        f"sequence {b}, positions {first}..{first + n - 1}")
+            row += n
+    assert [cache.length(s) for s in slots] == at
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_windowed_portions_keep_the_pages_their_first_query_sees(engine, tmp_path, dtype):
+    """A window of 40 keys and portions of 70 tokens: a portion's first query still sees keys
+    that the sequence's new length would let go, so those pages stay until the step is over."""
+    from llama_rs_metal_b200.config import LlamaConfig
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.registry import register_architecture
+
+    register_architecture("WindowedLlamaForTest", LlamaConfig, lambda c: _llama_like_plan(c, window=40))
+    cfg = dict(helpers.TINY["B"]["config"], architectures=["WindowedLlamaForTest"], model_type="windowed_test")
+    folder = write_random_model(str(tmp_path), cfg, seed=5, std=0.05, norm_std=0.1)
+    plain_cfg, tensors = P.read_model(folder)
+    runner, cache, _ = open_runner(engine, folder, dtype, max_tokens=1024, max_slots=2)
+    tokens = helpers.random_tokens(61, 250, 512)
+    ref = P.forward(plain_cfg, tensors, tokens, window=40).numpy()
+    slot = cache.open_slot()
+    at = 0
+    for n in (30, 70, 70, 1, 1, 70, 8):
+        out = runner.step([entry(slot, tokens[at:at + n])]).cpu()
+        helpers.assert_logits_close(out, ref[at:at + n], dtype, f"windowed portion at {at}")
+        at += n
+    assert at == 250
+    kept = (cache.kv_groups[0].table_host[slot] >= 0).nonzero()[0].tolist()
+    assert kept == [3]  # the last portion's first query (position 242) sees keys from 203: page 3 on
+
+
+# --------------------------------------------------------------------------- failures and memory
+def test_a_device_status_poisons_the_session_until_reset(engine, model_dirs, plain_models):
+    """What a kernel that gave up on a bounded wait leaves behind is a code in the status word.
+    Written there from the host (no kernel is made to fail), it must stop the session before any
+    logits are handed out, keep it stopped until reset, and leave a reset session exact again
+    (crates/model-runtime/src/session.rs:156-159, 101)."""
+    from llama_rs_metal_b200.errors import LlamaError, PoisonedError
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    model = engine.load(model_dirs["D"], dtype="bfloat16")
+    session = model.session(context=256)
+    tokens = helpers.random_tokens(4, 90, 2048)
+    ref = P.forward(*plain_models["D"], tokens).numpy()
+    good = session.prefill(tokens[:70]).clone()
+    helpers.assert_logits_close(good.cpu().numpy()[None], ref[69:70], "bfloat16")
+    session.reset()
+    session.prefill(tokens[:20])
+    gemm_dispatch.check_status()
+    word = gemm_dispatch._status_word(engine.device)
+    word.fill_(2)                                   # "gave up waiting for operand tiles"
+    with pytest.raises(LlamaError, match="gave up waiting for operand tiles"):
+        session.prefill(tokens[20:90])              # 70 rows: a portion through the tensor-core kernels
+    assert int(word.item()) == 0                    # read and cleared
+    with pytest.raises(PoisonedError):
+        session.decode(5)
+    with pytest.raises(PoisonedError):
+        session.prefill([1, 2, 3])
+    session.reset()
+    assert session.tokens() == []
+    assert torch.equal(session.prefill(tokens[:70]), good)
+    # the same through the generation loop, where the captured decode step runs the kernels
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    session.reset()
+    batch = model.session(context=128, max_batch=40)
+    prompts = [helpers.random_tokens(50 + i, 5 + i % 9, 2048) for i in range(40)]
+    options = GenerationOptions(max_tokens=4, sampling=Sampling(temperature=0.0))
+    want = [r.tokens for r in batch.generate(prompts, options, stop_token_ids=())]
+    word.fill_(3)
+    with pytest.raises(LlamaError, match="gave up waiting"):
+        batch.generate(prompts, options, stop_token_ids=())
+    assert batch.runner.poisoned and batch.cache.slots.held == 0
+    with pytest.raises(PoisonedError):
+        batch.generate(prompts, options, stop_token_ids=())
+    batch.reset()
+    assert [r.tokens for r in batch.generate(prompts, options, stop_token_ids=())] == want
+
+
+def test_a_replayed_graph_marks_the_status_word_for_reading(engine, model_dirs):
+    """Kernels inside a replayed CUDA graph do not pass through their Python wrappers; the replay
+    itself has to say that the status word must be read."""
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    runner, cache, _ = open_runner(engine, model_dirs["D"], "bfloat16", max_tokens=4096, max_slots=48)
+    slots = [cache.open_slot() for _ in range(40)]
+    runner.step([entry(s, helpers.random_tokens(s, 4 + s % 11, 2048), []) for s in slots])
+    runner.step([entry(s, [7]) for s in slots])     # captures the decode step of 40 rows
+    graph = next(iter(runner._graphs.values()))
+    assert graph.reports_status                     # 40 rows: the O and down products run on tcgen05 in K slices
+    gemm_dispatch.check_status()
+    assert not gemm_dispatch._status_dirty
+    runner.step([entry(s, [8]) for s in slots])     # a replay only
+    assert gemm_dispatch._status_dirty
+    gemm_dispatch.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_device_memory_is_constant_over_many_decode_steps(engine, model_dirs, dtype):
+    """After warm-up, decoding allocates nothing more: three rounds of 64 steps leave the bytes
+    in use where they were (crates/llama-rs/tests/sessions.rs:65-83)."""
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    model = engine.load(model_dirs["A"], dtype=dtype)
+    session = model.session(context=128, max_batch=3)
+    prompts = [helpers.random_tokens(i, 3 + i, 256) for i in range(3)]
+    options = GenerationOptions(max_tokens=65, sampling=Sampling(temperature=0.0))
+    session.generate(prompts, options, stop_token_ids=())          # warm-up: graphs, staging buffers
+    torch.cuda.synchronize()
+    in_use, reserved = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        results = session.generate(prompts, options, stop_token_ids=())
+        assert all(len(r.tokens) == 65 for r in results)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == in_use and torch.cuda.memory_reserved() == reserved
+    assert torch.cuda.mem_get_info()[0] >= free_before             # nothing was taken from the driver either
+    # and the runner keeps a bounded number of captured steps
+    assert len(session.runner._graphs) <= session.runner.max_graphs
+
+
+# --------------------------------------------------------------------------- reproducibility
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_forty_random_generations_one_step_ahead_equal_step_by_step(engine, model_dirs, dtype):
+    """Random prompts, budgets, contexts, stop ids and sampling, forty times over: generation
+    that keeps a step in flight (CUDA graphs, tokens fed on the device) and generation that waits
+    for every token give the same tokens and reasons, in bfloat16 too. That needs results that do
+    not depend on timing (no sums meeting by atomics), the same launch geometry with and without
+    graphs, and a step in flight that is dropped when a stop token shrinks the batch."""
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    name = "D"
+    vocab = helpers.TINY[name]["config"]["vocab_size"]
+    model = engine.load(model_dirs[name], dtype=dtype)
+    rng = np.random.default_rng(2024)
+    sessions = {}
+    for trial in range(40):
+        max_batch = int(rng.choice([1, 3, 12]))
+        context = int(rng.choice([48, 80, 200]))
+        if (max_batch, context) not in sessions:
+            ahead, plain = model.session(context=context, max_batch=max_batch), model.session(context=context, max_batch=max_batch)
+            plain.runner.use_graphs = False
+            sessions[(max_batch, context)] = (ahead, plain)
+        ahead, plain = sessions[(max_batch, context)]
+        count = int(rng.integers(1, 2 * max_batch + 2))
+        prompts = [[int(t) for t in rng.integers(0, vocab, size=int(rng.integers(1, 40)))] for _ in range(count)]
+        sampling = Sampling(temperature=0.0) if trial % 2 == 0 else \
+            Sampling(temperature=float(rng.choice([0.7, 1.0])), top_k=0, top_p=1.0, seed=int(rng.integers(0, 1000)))
+        options = GenerationOptions(max_tokens=int(rng.integers(1, 30)), sampling=sampling)
+        free = plain.generate(prompts, options, stop_token_ids=())
+        emitted = [t for r in free for t in r.tokens]
+        stops = sorted({emitted[int(i)] for i in rng.integers(0, len(emitted), size=int(rng.integers(0, 4)))}) if emitted else []
+        want = plain.generate(prompts, options, stop_token_ids=stops)
+        got = ahead.generate(prompts, options, stop_token_ids=stops)
+        assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want], \
+            f"trial {trial}: batch {max_batch}, context {context}, {count} prompts, stops {stops}"
+        assert ahead.cache.slots.held == 0 and plain.cache.slots.held == 0
+
+
+# --------------------------------------------------------------------------- the stated workloads
+def test_tiny_b_workload_as_stated_with_temperature_sampling(engine, model_dirs, plain_models):
+    """Five prompts of 1, 9, 33, 64 and 130 tokens (ids from seed 8), then 12 steps at temperature
+    0.8 with sampling seed 9, in float32: every sampled token is the plain implementation's logits
+    through the sampler's CPU twin (a different token only where two perturbed scores tie within
+    rounding)."""
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    rng = np.random.default_rng(8)
+    prompts = [[int(t) for t in rng.integers(0, 512, size=n)] for n in (1, 9, 33, 64, 130)]
+    model = engine.load(model_dirs["B"], dtype="float32")
+    session = model.session(context=256, max_batch=5)
+    options = GenerationOptions(max_tokens=12, sampling=Sampling(temperature=0.8, top_k=0, top_p=1.0, seed=9))
+    results = session.generate(prompts, options, stop_token_ids=())
+    cfg, tensors = plain_models["B"]
+    for request, (prompt, result) in enumerate(zip(prompts, results)):
+        assert result.finish_reason == "length" and len(result.tokens) == 12
+        seq = list(prompt)
+        for step, token in enumerate(result.tokens):
+            logits = P.forward(cfg, tensors, seq)[-1].numpy()
+            scores = helpers.gumbel_twin(logits.tolist(), 0.8, 9, (request << 32) | step)
+            assert scores[token] >= max(scores) - 1e-3, \
+                f"request {request}, step {step}: sampled {token}, the twin draws {int(np.argmax(scores))}"
+            seq.append(token)
+    # the decoding positions go past original_max_position_embeddings = 64: all three branches of
+    # the llama3 rule are in use (low, high and the smooth band between)
+    from llama_rs_metal_b200.parts.rope import RotaryEmbedding
+    spec = model.plan.layers[0].mixer.params["position"].params
+    factors = [f0 / f for f0, f in zip(RotaryEmbedding(**dict(spec, scaling="default")).inverse_frequencies(),
+                                       RotaryEmbedding(**spec).inverse_frequencies())]
+    assert min(factors) == 1.0 and abs(max(factors) - 8.0) < 1e-9 and any(1.0 < f < 8.0 - 1e-9 for f in factors)
+
+
+# --------------------------------------------------------------------------- another block, model-level scales
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_block_with_roles_of_its_own_and_scaled_embedding_and_logits(engine, tmp_path, dtype):
+    """A block that norms each part's output before it joins the stream (two more norms per layer
+    than the library's block has roles for), a scale on the embedding and one on the logits:
+    registered here, built from a plan, stepped whole and in portions, compared with a plain
+    restatement. The library's attention, feed-forward, norm, cache and step function run it as
+    they are."""
+    import dataclasses
+    from llama_rs_metal_b200.config import LlamaConfig
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.kernels import ops
+    from llama_rs_metal_b200.models.llama import llama_plan
+    from llama_rs_metal_b200.parts import Block, LayerSpec, PartSpec
+    from llama_rs_metal_b200.registry import register_architecture, register_block
+
+    @register_block("toy_sandwich")
+    class Sandwich(Block):
+        roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm",
+                 "feed_forward_norm": "norm", "after_mixer_norm": "norm", "after_feed_forward_norm": "norm"}
+        graph_safe = True
+
+        def forward(self, hidden, ctx, cache):
+            x = self.mixer_norm.forward(hidden, ctx)
+            mixed = self.mixer.forward(x, ctx, cache, residual=torch.zeros_like(hidden))
+            ops.add_(hidden, self.after_mixer_norm.forward(mixed, ctx))
+            x = self.feed_forward_norm.forward(hidden, ctx)
+            fed = self.feed_forward.forward(x, ctx, residual=torch.zeros_like(hidden))
+            return ops.add_(hidden, self.after_feed_forward_norm.forward(fed, ctx))
+
+    EMBED, LOGIT = 8.0, 0.25
+
+    def plan(config):
+        base = llama_plan(config)
+        layers = []
+        for i, layer in enumerate(base.layers):
+            norm = layer.mixer_norm
+            p = f"model.layers.{i}."
+            layers.append(LayerSpec("toy_sandwich", parts=dict(
+                layer.parts,
+                after_mixer_norm=PartSpec(norm.kind, norm.params, prefix=p + "after_attention_norm."),
+                after_feed_forward_norm=PartSpec(norm.kind, norm.params, prefix=p + "after_mlp_norm."))))
+        return dataclasses.replace(base, layers=tuple(layers), embedding_scale=EMBED, logit_scale=LOGIT)
+
+    register_architecture("SandwichLlamaForTest", LlamaConfig, plan)
+    cfg = dict(helpers.TINY["B"]["config"], architectures=["SandwichLlamaForTest"], model_type="sandwich_test")
+    folder = write_random_model(str(tmp_path), cfg, seed=21, std=0.05, norm_std=0.1)
+    c, w = P.read_model(folder)
+    Hq, Hk, d, eps = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], c["rms_norm_eps"]
+    inv = P.rope_inverse_frequencies(c, d)
+
+    def oracle(tokens):
+        n = len(tokens)
+        hidden = P.embedding(w["model.embed_tokens.weight"], tokens) * EMBED
+        for i in range(c["num_hidden_layers"]):
+            p = f"model.layers.{i}."
+            x = P.rms_norm(hidden, w[p + "input_layernorm.weight"], eps)
+            q = P.rope(P.linear(x, w[p + "self_attn.q_proj.weight"]).view(n, Hq, d), range(n), inv, d)
+            k = P.rope(P.linear(x, w[p + "self_attn.k_proj.weight"]).view(n, Hk, d), range(n), inv, d)
+            v = P.linear(x, w[p + "self_attn.v_proj.weight"]).view(n, Hk, d)
+            mixed = P.linear(P.attention(q, k, v).reshape(n, Hq * d), w[p + "self_attn.o_proj.weight"])
+            hidden = hidden + P.rms_norm(mixed, w[p + "after_attention_norm.weight"], eps)
+            x = P.rms_norm(hidden, w[p + "post_attention_layernorm.weight"], eps)
+            fed = P.gated_mlp(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+            hidden = hidden + P.rms_norm(fed, w[p + "after_mlp_norm.weight"], eps)
+        return P.linear(P.rms_norm(hidden, w["model.norm.weight"], eps), w["lm_head.weight"]) * LOGIT
+
+    runner, cache, model = open_runner(engine, folder, dtype, max_tokens=512, max_slots=2)
+    assert len(model.blocks[0].parts) == 6
+    tokens = helpers.random_tokens(33, 90, 512)
+    ref = oracle(tokens).numpy()
+    plain = P.forward(c, w, tokens).numpy()
+    assert np.abs(ref - plain).max() > 1e-2 * np.abs(plain).max()     # the arrangement and the scales matter
+    slot = cache.open_slot()
+    helpers.assert_logits_close(runner.step([entry(slot, tokens)]).cpu(), ref, dtype, "sandwich block, whole")
+    cache.close_slot(slot)
+    slot = cache.open_slot()
+    rows = [runner.step([entry(slot, tokens[:40])]), runner.step([entry(slot, tokens[40:57])])]
+    rows += [runner.step([entry(slot, [t])]) for t in tokens[57:]]
+    helpers.assert_logits_close(torch.cat(rows).cpu(), ref, dtype, "sandwich block, in steps")
+
+
+def test_a_windowed_model_generates_one_step_ahead(engine, tmp_path):
+    """A model whose cache group has a window keeps the decode bookkeeping in arrays and the
+    generation loop one step ahead like any other; tokens equal step-by-step generation."""
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    from llama_rs_metal_b200.config import LlamaConfig
+    from llama_rs_metal_b200.engine.session import write_random_model
+    from llama_rs_metal_b200.registry import register_architecture
+    register_architecture("WindowedLlamaForTest", LlamaConfig, lambda c: _llama_like_plan(c, window=40))
+    cfg = dict(helpers.TINY["B"]["config"], architectures=["WindowedLlamaForTest"], model_type="windowed_test")
+    folder = write_random_model(str(tmp_path), cfg, seed=5, std=0.05, norm_std=0.1)
+    plain_cfg, tensors = P.read_model(folder)
+    for dtype in ("float32", "bfloat16"):
+        model = engine.load(folder, dtype=dtype)
+        ahead, plain = model.session(context=256, max_batch=3), model.session(context=256, max_batch=3)
+        plain.runner.use_graphs = False
+        assert ahead.can_decode_ahead
+        prompts = [helpers.random_tokens(70 + i, n, 512) for i, n in enumerate([3, 90, 45, 7])]
+        options = GenerationOptions(max_tokens=100, sampling=Sampling(temperature=0.0))
+        want = plain.generate(prompts, options, stop_token_ids=())
+        got = ahead.generate(prompts, options, stop_token_ids=())
+        assert [r.tokens for r in got] == [r.tokens for r in want]
+        assert ahead.cache.held_pages() == [0]
+        if dtype == "float32":
+            seq = list(prompts[1])
+            for token in want[1].tokens[:20]:
+                logits = P.forward(plain_cfg, tensors, seq, window=40)[-1].numpy()
+                best = int(np.argmax(logits))
+                assert token == best or logits[best] - logits[token] <= 4e-5 * np.abs(logits).max()
+                seq.append(token)

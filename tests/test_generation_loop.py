@@ -260,3 +260,37 @@ def test_running_ahead_keeps_a_step_in_flight():
     generate(stepper, AheadSampler(), [[1, 2], [3]], options, max_batch=2)
     kinds = [k for k, _ in stepper.log]
     assert kinds == ["prefill", "decode", "ahead", "ahead", "ahead", "ahead"]
+
+
+class RewindStepper(AheadStepper):
+    """An ahead stepper whose last step can be taken back (what a cache of keys and values allows)."""
+
+    can_rewind = True
+
+    def rewind(self, slots, tokens=1):
+        assert tokens == 1
+        kind, rows = self.log[-1]
+        assert kind == "ahead" and {s for s, _ in rows} >= set(slots), "only the step in flight is taken back"
+        self.log[-1] = ("dropped", rows)
+        for slot in slots:
+            self.live[slot].pop()
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_a_step_in_flight_is_dropped_whole_when_a_stop_token_ends_a_sequence(seed):
+    """With a stepper that can take a step back, every step that counts is a step the plain loop
+    runs: same sequences, same tokens, in the same order. (Equal batches are what makes the
+    device results equal bit for bit.)"""
+    rng = np.random.default_rng(100 + seed)
+    prompts = [[int(t) for t in rng.integers(0, 50, size=int(rng.integers(1, 9)))] for _ in range(int(rng.integers(2, 8)))]
+    stop = [int(t) for t in rng.integers(0, 50, size=int(rng.integers(1, 8)))]
+    options = GenerationOptions(max_tokens=int(rng.integers(2, 12)), sampling=Sampling(temperature=0.0))
+    context = int(rng.integers(9, 16))
+    plain = ScriptedStepper(slots=3)
+    want = generate(plain, ArgmaxSampler(), prompts, options, stop_token_ids=stop, max_batch=3, context=context)
+    ahead = RewindStepper(slots=3)
+    got = generate(ahead, AheadSampler(), prompts, options, stop_token_ids=stop, max_batch=3, context=context)
+    assert not ahead.live
+    assert [(r.tokens, r.finish_reason) for r in got] == [(r.tokens, r.finish_reason) for r in want]
+    counted = [rows for kind, rows in ahead.log if kind in ("decode", "ahead")]
+    assert counted == [rows for kind, rows in plain.log if kind == "decode"]

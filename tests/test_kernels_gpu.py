@@ -323,6 +323,87 @@ def test_attention_decode_window_edge(ops, kernel_choice, dtype):
     assert torch.equal(again, got)
 
 
+def extend_case(ops, lengths, portions, Hq, Hk, d, dtype, seed=0):
+    """Sequences in the paged cache, whose last `portions[b]` tokens are the step's packed queries."""
+    _, view, slots, ks, vs = paged_case(ops, lengths, Hq, Hk, d, dtype, seed=seed)
+    T = sum(portions)
+    q = rnd(T, Hq, d, dtype=dtype, seed=seed + 77)
+    cu = [0]
+    for n in portions:
+        cu.append(cu[-1] + n)
+    seq_of = [b for b, n in enumerate(portions) for _ in range(n)]
+    positions = [lengths[b] - portions[b] + i for b in range(len(lengths)) for i in range(portions[b])]
+    return q, view, slots, ks, vs, cu, seq_of, positions
+
+
+def plain_extend(q, ks, vs, cu, lengths, portions, window=None):
+    out = []
+    for b, (kb, vb) in enumerate(zip(ks, vs)):
+        n, m = lengths[b], portions[b]
+        qq = torch.zeros(n, q.shape[1], q.shape[2], dtype=F64)
+        qq[n - m:] = q[cu[b]:cu[b + 1]].double().cpu()
+        out.append(P.attention(qq, kb.double().cpu(), vb.double().cpu(), window)[n - m:].reshape(m, -1))
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hk,d", [(4, 2, 16), (3, 1, 48), (8, 2, 128), (32, 8, 64), (3, 1, 32)])
+@pytest.mark.parametrize("window", [None, 64, 100])
+def test_attention_extend_over_poisoned_pages(ops, kernel_choice, dtype, Hq, Hk, d, window):
+    """Portions of 1, 2, 63, 64, 65 and 130 tokens onto sequences that cross page edges before,
+    inside and after the portion; one sequence is its portion (nothing cached before)."""
+    lengths = [64, 66, 300, 129, 65, 1000]
+    portions = [1, 2, 63, 64, 65, 130]
+    q, view, slots, ks, vs, cu, seq_of, positions = extend_case(ops, lengths, portions, Hq, Hk, d, dtype)
+    got = ops.attention_extend(q, view, i32(cu), i32(seq_of), i32(positions), i32(slots), i32(lengths),
+                               max(portions), d ** -0.5, window)
+    close(got, plain_extend(q, ks, vs, cu, lengths, portions, window), TOL[dtype], f"extend window {window}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_extend_window_edge_inside_a_portion(ops, kernel_choice, dtype):
+    """Within one portion the window moves: for the portion's first query the key just outside
+    its window would win every score, for a later query another one; the keys just inside must
+    still count, and each query must see exactly its own window."""
+    lengths, portions, window = [200, 140], [70, 100], 64
+    q, view, slots, ks, vs, cu, seq_of, positions = extend_case(ops, lengths, portions, 4, 2, 32, dtype, seed=3)
+    table = view.page_table.cpu()
+    probes = []
+    for b, (n, m) in enumerate(zip(lengths, portions)):
+        for row in (0, m // 2, m - 1):                       # three queries of the portion
+            pos = n - m + row
+            q[cu[b] + row] = 0
+            q[cu[b] + row, :, 1 + len(probes) % 3] = 30.0
+            for key, strength in ((pos - window, 60.0), (pos - window + 1, 30.0)):
+                if key < 0:
+                    continue
+                ks[b][key] = 0
+                ks[b][key, :, 1 + len(probes) % 3] = strength
+                view.k[int(table[slots[b], key // 64]), :, key % 64] = ks[b][key]
+            probes.append((b, row, pos))
+    got = ops.attention_extend(q, view, i32(cu), i32(seq_of), i32(positions), i32(slots), i32(lengths),
+                               max(portions), 32 ** -0.5, window)
+    close(got, plain_extend(q, ks, vs, cu, lengths, portions, window), TOL[dtype], "window edge inside a portion")
+    for b, row, pos in probes:
+        if pos - window + 1 >= 0:
+            close(got[cu[b] + row].view(4, 32)[0], vs[b][pos - window + 1, 0].double(), 3e-2,
+                  "the key at the window's edge")
+
+
+def test_float32_extend_equals_prefill_bit_for_bit(ops):
+    """In float32 a prompt's last tokens, run as a portion over the cache, get the bits the whole
+    prompt gets: same keys in the same order, same arithmetic."""
+    lengths, portions = [70, 5, 129], [17, 5, 66]
+    q, view, slots, ks, vs, cu, seq_of, positions = extend_case(ops, lengths, portions, 4, 2, 16, torch.float32, seed=7)
+    ext = ops.attention_extend(q, view, i32(cu), i32(seq_of), i32(positions), i32(slots), i32(lengths),
+                               max(portions), 0.25)
+    for b, (n, m) in enumerate(zip(lengths, portions)):
+        qq = rnd(n, 4, 16, seed=99)
+        qq[n - m:] = q[cu[b]:cu[b + 1]]
+        pre = ops.attention_prefill(qq, ks[b].contiguous(), vs[b].contiguous(), i32([0, n]), i32([0] * n), n, 0.25)
+        assert torch.equal(pre[n - m:], ext[cu[b]:cu[b + 1]])
+
+
 def test_float32_decode_equals_prefill_bit_for_bit(ops):
     lengths = [70, 5, 129]
     q, view, slots, ks, vs = paged_case(ops, lengths, 4, 2, 16, torch.float32, seed=7)
@@ -420,20 +501,7 @@ def test_argmax_rows_ties_and_non_finite(ops):
     assert ops.argmax_rows(small).tolist() == [1]
 
 
-def gumbel_twin(logits, temperature, seed, key):
-    """The kernel's draw, restated on the CPU with the same integer hash (csrc/sampling.cu)."""
-    mask = (1 << 64) - 1
-
-    def mix(z):
-        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
-        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
-        return z ^ (z >> 31)
-    scores = []
-    for i, v in enumerate(logits):
-        z = mix((mix((seed + 0x9E3779B97F4A7C15 * (key + 1)) & mask) + i) & mask)
-        u = (float(z >> 40) + 0.5) / 16777216.0
-        scores.append(float(v) / temperature - math.log(-math.log(u)))
-    return scores
+from helpers import gumbel_twin  # noqa: E402  (the kernel's draw restated on the CPU)
 
 
 def test_gumbel_sampling_matches_its_cpu_twin_and_ignores_batch_company(ops):
@@ -527,6 +595,34 @@ def test_linear_bfloat16_few_rows_on_the_tensor_cores_and_on_the_streaming_kerne
         close(ops.linear(x, wide_w), P.linear(xd, wide_w.double().cpu()), 6e-3, f"wide, stream={forced}")
         resid = rnd(M, 300, seed=3)
         want = resid.double().cpu() + P.linear(xd, small_w.double().cpu())
-        ops.linear(x, small_w, epilogue=ops.ADD, out=resid)          # K cut into slices that add atomically
-        close(resid, want, 2e-5 * math.sqrt(520), f"split-K add, stream={forced}")
+        ops.linear(x, small_w, epilogue=ops.ADD, out=resid)
+        close(resid, want, 2e-5 * math.sqrt(520), f"add in place, stream={forced}")
+    gemm_dispatch.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 300, 4096), (8, 2048, 8192), (8, 2048, 2048), (17, 300, 4096), (40, 2048, 8192),
+                                   (64, 520, 4104), (5, 64, 64)])
+def test_linear_slices_sum_to_the_product_in_a_fixed_order(ops, M, N, K):
+    """A narrow product for the residual stream is cut into K slices stored as planes; whoever
+    reads the stream next adds them in plane order (here the standalone kernel and the norm's
+    fold). No atomics: two runs give the same bits."""
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    want = P.linear(x.double().cpu(), w.double().cpu())
+    planes = ops.linear_slices(x, w)
+    if (M, N, K) == (5, 64, 64):
+        assert planes is None                     # too small to be worth cutting: added in place
+        return
+    assert planes is not None and planes.shape[0] >= 2 and tuple(planes.shape[1:]) == (M, N)
+    close(planes.double().sum(0), want, 2e-5 * math.sqrt(K), "sum of the slices")
+    again = ops.linear_slices(x, w)
+    assert torch.equal(planes, again)
+    resid = rnd(M, N, seed=2)
+    folded = resid.clone()
+    ops.add_planes_(resid, planes)
+    close(resid, folded.double().cpu() + want, 2e-5 * math.sqrt(K), "slices added to the stream")
+    weight = torch.ones(N, device=DEV)
+    y = ops.rms_norm(folded, weight, 1e-5, torch.float32, partials=planes)
+    assert torch.equal(folded, resid)             # the norm adds them in the same order
+    close(y, P.rms_norm(resid.double().cpu(), torch.ones(N, dtype=F64), 1e-5), 1e-5, "norm of the folded stream")
     gemm_dispatch.check_status()

@@ -1,0 +1,68 @@
+"""Whole-model parity at the widths the benchmark is quoted on.
+
+The tiny configurations never reach the kernels the headline numbers come from: the tcgen05
+prompt attention (head sizes 64 and 128), the 128 x 256 and 256 x 256 tensor-core tiles with the
+SiLU epilogue at real K, the cluster decode kernel at group size 4. Here the true Llama 3.2 1B
+widths (hidden 2048, intermediate 8192, vocabulary 128,256, 32 heads in 8 groups of head size 64)
+run with 2 of the 16 layers against the plain implementation, in float32 and in bfloat16; and a
+narrow model with head size 128 and an untied head, the 3B / 8B geometry. The reference gates its
+numbers the same way on the real checkpoint (tools/benchmarks/verify.py:38-59,222-225;
+crates/llama-rs/tests/mlx_checkpoint.rs:15-83).
+"""
+import pytest
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+LLAMA_1B_WIDTHS = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=2048, intermediate_size=8192,
+    num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=64, vocab_size=128256,
+    rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
+
+HEAD_128 = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=1024, intermediate_size=3584,
+    num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=32064,
+    rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=131072)
+
+
+@pytest.fixture(scope="module")
+def engine():
+    from llama_rs_metal_b200 import Engine
+    return Engine()
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from llama_rs_metal_b200.engine.session import write_random_model
+    return {
+        "1b": write_random_model(str(tmp_path_factory.mktemp("widths_1b")), LLAMA_1B_WIDTHS, seed=0, std=0.02),
+        "head128": write_random_model(str(tmp_path_factory.mktemp("head_128")), HEAD_128, seed=1, std=0.03,
+                                      norm_std=0.05),
+    }
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["1b", "head128"])
+def test_whole_model_parity_at_benchmark_widths(engine, folders, which, dtype):
+    worst = helpers.parity_with_plain(engine, folders[which], dtype, prompt_lengths=(300, 170, 40), decode_steps=8)
+    print(f"{which} {dtype}: worst error {worst:.3e} of the largest logit")
+
+
+def test_a_smaller_model_can_share_a_larger_models_weights(engine, folders, tmp_path):
+    """The loader skips stored tensors nobody asked for, so a 1-layer model reads its tensors out
+    of the 2-layer folder's file (how bench.py's gate gets a short model out of the long one)."""
+    from llama_rs_metal_b200.engine.session import build_model
+    from llama_rs_metal_b200.runtime import Runtime
+    import torch
+    small = helpers.narrowed_copy(folders["head128"], str(tmp_path / "one"), 1)
+    _, plan, model, _ = build_model(small, Runtime(engine.device, torch.bfloat16))
+    assert len(plan.layers) == 1
+    assert any(name.startswith("model.layers.1.") for name in model.unexpected_tensors)
+    helpers.parity_with_plain(engine, small, "bfloat16", prompt_lengths=(70, 9), decode_steps=2)

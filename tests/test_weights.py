@@ -92,9 +92,27 @@ def test_tied_model_ignores_a_saved_head(tmp_path):
     tensors = random_tensors(specs, seed=1)
     tensors["lm_head.weight"] = torch.zeros(256, 64, dtype=torch.bfloat16)
     write_model_folder(str(tmp_path), helpers.TINY["A"]["config"], tensors)
-    assert "lm_head.weight" not in load_tensors(str(tmp_path), specs, ignored=plan.ignored_names)
+    loaded = load_tensors(str(tmp_path), specs, ignored=plan.ignored_names)
+    assert "lm_head.weight" not in loaded and loaded.unexpected == ()
     with pytest.raises(WeightError):
-        load_tensors(str(tmp_path), specs)  # without the plan's ignore list it is unexpected
+        load_tensors(str(tmp_path), specs, strict=True)  # without the plan's ignore list it is unexpected
+
+
+def test_unknown_tensors_are_skipped_and_listed(tmp_path):
+    """A stored name no part asked for is no error by itself (crates/model-format/src/mlx/mod.rs:41-43
+    skips unknown names, e.g. the other towers of a multimodal export): it is left on disk and
+    reported; `strict` turns it into the one error."""
+    _, specs = specs_of("A")
+    tensors = {"language_model." + n: t for n, t in random_tensors(specs, seed=1).items()}
+    tensors["vision_tower.patch_embed.weight"] = torch.zeros(8, 3, dtype=torch.bfloat16)
+    tensors["language_model.model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    write_model_folder(str(tmp_path), helpers.TINY["A"]["config"], tensors)
+    loaded = load_tensors(str(tmp_path), specs)
+    assert set(loaded) == set(specs)
+    assert loaded.unexpected == ("model.layers.0.self_attn.rotary_emb.inv_freq", "vision_tower.patch_embed.weight")
+    with pytest.raises(WeightError) as info:
+        load_tensors(str(tmp_path), specs, strict=True)
+    assert info.value.unexpected == list(loaded.unexpected) and not info.value.missing
 
 
 def test_language_model_prefixes_are_stripped(tmp_path):

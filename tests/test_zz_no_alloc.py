@@ -42,10 +42,13 @@ def run(lib, symbol, q, k, v, table, slots, lens, splits, scratch=None):
         args.append(p(scratch))
     args += [p(out), p(table), table.shape[1], p(slots), p(lens), B, Hq, k.shape[1], d, 64,
              ctypes.c_float(d ** -0.5), 0, splits, stream]
-    before = torch.cuda.memory_allocated()
+    torch.cuda.synchronize()
+    before, free_before = torch.cuda.memory_allocated(), torch.cuda.mem_get_info()[0]
     code = getattr(lib, symbol)(*args)
     torch.cuda.synchronize()
-    return code, out, torch.cuda.memory_allocated() - before
+    # what torch's allocator handed out, and what the driver says is free on the device: the
+    # second also sees an allocation made behind torch's back
+    return code, out, (torch.cuda.memory_allocated() - before, free_before - torch.cuda.mem_get_info()[0])
 
 
 def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
@@ -54,17 +57,24 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice_in_a_row():
     lib.lrm_attention_static_scratch_error.restype = ctypes.c_char_p
     capacity = lib.lrm_attention_static_scratch_floats()
     assert capacity == 1 << 20
-    for seed, lengths, splits in ((1, [300, 64, 1, 129], 3), (2, [40, 513], 5)):
+    # The first call on a device looks the array's address up (and may make the driver load the
+    # module): it is made here, before anything is measured. It is also a large one, so that the
+    # array is full of another problem's partials when the smaller problems below run; the last
+    # of them has more splits than some sequences have pages (splits that see no key).
+    q, k, v, table, slots, lens = case(9, [700] * 8, Hq=32, Hk=8)
+    code, _, _ = run(lib, "lrm_attention_decode_tiled_static_scratch", q, k, v, table, slots, lens, 7)
+    assert code == 0, lib.lrm_attention_static_scratch_error(code).decode()
+    for seed, lengths, splits in ((1, [300, 64, 1, 129], 3), (2, [40, 513], 5), (3, [1, 64, 65], 6)):
         q, k, v, table, slots, lens = case(seed, lengths)
-        scratch = torch.empty(len(lengths) * 8 * splits * 66, dtype=torch.float32, device=DEV)
+        scratch = torch.full((len(lengths) * 8 * splits * 66,), float("nan"), dtype=torch.float32, device=DEV)
         code, want, _ = run(lib, "lrm_attention_decode_tiled", q, k, v, table, slots, lens, splits, scratch)
         assert code == 0
-        code, got, grown = run(lib, "lrm_attention_decode_tiled_static_scratch", q, k, v, table, slots, lens, splits)
+        code, got, (from_torch, from_driver) = run(lib, "lrm_attention_decode_tiled_static_scratch", q, k, v, table,
+                                                   slots, lens, splits)
         assert code == 0, lib.lrm_attention_static_scratch_error(code).decode()
-        assert grown == 0                                       # nothing came from torch's allocator
+        assert from_torch == 0 and from_driver <= 0             # nothing was allocated, by anyone
         assert torch.isfinite(got.float()).all()
-        scale = want.float().abs().max().item()
-        assert (got.float() - want.float()).abs().max().item() <= 1.2e-2 * scale   # the kernel tests' bfloat16 tolerance
+        assert torch.equal(got, want)                           # the same kernels in the same order: the same bits
     # a problem whose partials do not fit is refused, with a sentence that says why
     q, k, v, table, slots, lens = case(3, [64] * 64, Hq=32, Hk=8)
     code, _, _ = run(lib, "lrm_attention_decode_tiled_static_scratch", q, k, v, table, slots, lens, 8)
