@@ -456,7 +456,7 @@ def _llama_like_plan(config, window=None, schedule=None):
     layers = []
     for layer in plan.layers:
         params = dict(layer.mixer.params, window=window)
-        layers.append(dataclasses.replace(layer, mixer=PartSpec("attention", params, layer.mixer.prefix)))
+        layers.append(layer.with_parts(mixer=PartSpec("attention", params, layer.mixer.prefix)))
     return dataclasses.replace(plan, layers=tuple(layers), schedule=tuple(schedule or plan.schedule))
 
 
