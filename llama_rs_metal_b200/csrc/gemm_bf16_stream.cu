@@ -225,13 +225,16 @@ LRM_API int lrm_gemm_bf16_stream_supports(int M, int N, int K) {
 static int chunk_of(int M) { return M <= 16 ? 64 : 128; }  // Chunk<NT>::kK for this many rows
 
 // How many K slices a product to be added to the residual stream is cut into: `requested`, or with
-// 0 the kernel's own rule (slices of at least 1024 until about 28 warps per SM stream weights).
-// The answer is the number of [M, N] planes epilogue 4 writes.
+// 0 the kernel's own rule: slices of at least 4096 until about 28 warps per SM stream weights.
+// (Measured over a 16-layer chain of the 1B products at 1-8 rows: the 2048 x 8192 product in two
+// slices and the 2048 x 2048 one whole take 495 us, against 540 us with 8 and 2 slices and 568 us
+// uncut; every plane costs the norm that adds it a read that only as many SMs share as there are
+// rows.) The answer is the number of [M, N] planes epilogue 4 writes.
 static int pick_splits(int N, int K, int requested) {
   if (requested > 0) return requested;
   const int tiles = (N + 15) / 16;
   int splits = 1;
-  while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 1024) splits *= 2;
+  while (splits < 8 && tiles * splits * 8 < 148 * 28 && K / (splits * 2) >= 4096) splits *= 2;
   return splits;
 }
 

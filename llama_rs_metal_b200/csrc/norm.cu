@@ -36,7 +36,16 @@ __global__ void rms_norm_kernel(float* __restrict__ x, const W* __restrict__ w, 
     const int i = threadIdx.x + e * blockDim.x;
     float v = i < hidden ? xr[i] : 0.f;
     if (n_partials > 0 && i < hidden) {
-      for (int p = 0; p < n_partials; ++p) v += partials[p * partial_stride + src + i];
+      // eight slices' loads are in flight together; they are added in slice order
+      for (int p0 = 0; p0 < n_partials; p0 += 8) {
+        float part[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          part[u] = p0 + u < n_partials ? partials[(p0 + u) * partial_stride + src + i] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (p0 + u < n_partials) v += part[u];
+      }
       if (rows == nullptr) xr[i] = v;  // the folded sum becomes the residual stream
     }
     xv[e] = v;
@@ -94,9 +103,16 @@ __global__ void rms_norm_vec_kernel(float* __restrict__ x, const W* __restrict__
     const int c = threadIdx.x + e * blockDim.x;
     float4 v = c < groups ? load4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
     if (n_partials > 0 && c < groups) {
-      for (int p = 0; p < n_partials; ++p) {
-        const float4 d = load4(partials + p * partial_stride + src + 4 * c);
-        v.x += d.x, v.y += d.y, v.z += d.z, v.w += d.w;
+      // eight slices' loads are in flight together; they are added in slice order
+      for (int p0 = 0; p0 < n_partials; p0 += 8) {
+        float4 part[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          part[u] = p0 + u < n_partials ? load4(partials + (p0 + u) * partial_stride + src + 4 * c)
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (p0 + u < n_partials) v.x += part[u].x, v.y += part[u].y, v.z += part[u].z, v.w += part[u].w;
       }
       if (rows == nullptr) store4(xr + 4 * c, v);  // the folded sum becomes the residual stream
     }

@@ -600,7 +600,7 @@ def test_linear_bfloat16_few_rows_on_the_tensor_cores_and_on_the_streaming_kerne
     gemm_dispatch.check_status()
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 300, 4096), (8, 2048, 8192), (8, 2048, 2048), (17, 300, 4096), (40, 2048, 8192),
+@pytest.mark.parametrize("M,N,K", [(1, 300, 8192), (8, 2048, 8192), (8, 2048, 2048), (17, 300, 8192), (40, 2048, 8192),
                                    (64, 520, 4104), (5, 64, 64)])
 def test_linear_slices_sum_to_the_product_in_a_fixed_order(ops, M, N, K):
     """A narrow product for the residual stream is cut into K slices stored as planes; whoever
@@ -610,8 +610,8 @@ def test_linear_slices_sum_to_the_product_in_a_fixed_order(ops, M, N, K):
     x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
     want = P.linear(x.double().cpu(), w.double().cpu())
     planes = ops.linear_slices(x, w)
-    if (M, N, K) == (5, 64, 64):
-        assert planes is None                     # too small to be worth cutting: added in place
+    if (M, N, K) in ((5, 64, 64), (8, 2048, 2048)):
+        assert planes is None                     # too short to be worth cutting: added in place
         return
     assert planes is not None and planes.shape[0] >= 2 and tuple(planes.shape[1:]) == (M, N)
     close(planes.double().sum(0), want, 2e-5 * math.sqrt(K), "sum of the slices")
