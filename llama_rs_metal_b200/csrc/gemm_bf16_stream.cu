@@ -21,9 +21,18 @@
 //
 // Epilogues: 0 store bf16, 1 store f32, 2 add into f32 in place, 3 SiLU gate
 // (rows alternate in blocks of 8 gate / 8 up rows, so a 16-row tile holds 8
-// gated pairs; out is [M, N/2] bf16), 4 store f32 partials per K slice.
+// gated pairs; out is [M, N/2] bf16), 4 store f32 partials per K slice, 5 token choice: the
+// product is a head's logits and only the chosen token is wanted, so every CTA finds, per
+// activation row, the best (score, id) of its 16 vocabulary rows (score = logit for the greedy
+// choice, logit / T + Gumbel noise for temperature sampling, as csrc/sampling.cu) and offers it
+// to the row's running best with one 64-bit atomic maximum; the logits themselves are never
+// written. A maximum does not depend on the order of the offers, so the choice is the same
+// every time. lrm_gemm_bf16_stream_pick turns the winners into ids right after (reference: the
+// head product and the GPU argmax go out in one submission,
+// crates/model-runtime/src/execute.rs:238-247).
 // (Reference role: the gemv_* family, crates/metal-backend/src/shaders/matrix.metal:10-37.)
 #include "common.cuh"
+#include "pick.cuh"
 
 namespace {
 
@@ -53,11 +62,20 @@ __device__ __forceinline__ uint4 ldg_keep(const void* p) {  // activations: reus
 
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
 
+// What epilogue 5 needs beyond the product's own arguments.
+struct PickArgs {
+  unsigned long long* best;  // [M] running best per row as pick_key(score, id); 0 before the launch
+  int* bad;                  // [M] set when a row held a non-finite logit; 0 before the launch
+  const long long* keys;     // [M] per-row stream of the Gumbel noise, or nullptr for the greedy choice
+  float inv_temperature;     // scores are logit * this + noise (1 for greedy)
+  unsigned long long seed;
+};
+
 // MINB: CTAs per SM the register budget must allow (a single wave for the usual sizes).
 template <int NT, int WARPS, int MINB>
 __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
     const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
-    int M, int N, int K_total, int mode, int k_per_split) {
+    int M, int N, int K_total, int mode, int k_per_split, PickArgs pick) {
   extern __shared__ float red[];  // [WARPS][NT][32 lanes][4]
   pdl_trigger();  // the next kernel may be scheduled at once (its CTAs fetch their first weights while
                   // this kernel streams); it waits for this one where it must
@@ -159,6 +177,40 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
     // sum.x/.y: weight row n0+gg, batch rows 8j+2tt, +1;  sum.z/.w: weight row n0+gg+8
     const int m0 = 8 * j + 2 * tt;
     const float vals[2][2] = {{sum.x, sum.z}, {sum.y, sum.w}};  // [batch row offset][weight row half]
+    if (mode == 5) {
+      // This warp holds tile j's 8 activation rows x 16 vocabulary rows: a lane has rows m0, m0 + 1
+      // and vocabulary ids n0 + gg, n0 + gg + 8. The best of a row's 16 is found over the lanes
+      // that share tt (xor 4, 8, 16); ties go to the lower id, so the result does not depend on
+      // how the vocabulary is cut into tiles.
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = m0 + e;
+        Best best{-INFINITY, -1};
+        bool bad = false;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int n = n0 + gg + 8 * half;
+          if (n >= N || m >= M) continue;
+          float v = vals[e][half];
+          bad |= !isfinite(v);
+          if (pick.keys != nullptr)
+            v = fmaf(v, pick.inv_temperature,
+                     gumbel_noise(pick.seed, static_cast<uint64_t>(pick.keys[m]), static_cast<uint32_t>(n)));
+          best = better(best, Best{v, n});
+        }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          Best other{__shfl_xor_sync(0xffffffffu, best.value, o), __shfl_xor_sync(0xffffffffu, best.id, o)};
+          best = better(best, other);
+          bad |= __shfl_xor_sync(0xffffffffu, static_cast<int>(bad), o) != 0;
+        }
+        if (gg == 0 && m < M) {
+          if (best.id >= 0) atomicMax(pick.best + m, pick_key(best.value, best.id));
+          if (bad) atomicOr(pick.bad + m, 1);
+        }
+      }
+      continue;
+    }
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int m = m0 + e;
@@ -187,7 +239,7 @@ __global__ __launch_bounds__(WARPS * 32, MINB) void gemm_bf16_stream_kernel(
 
 template <int NT, int WARPS, int MINB>
 int launch_variant(const void* X, const void* W, void* out, int M, int N, int K, int mode, int splits,
-                   cudaStream_t stream) {
+                   const PickArgs& pick, cudaStream_t stream) {
   constexpr int smem = WARPS * NT * 32 * 4 * static_cast<int>(sizeof(float));
   auto kernel = gemm_bf16_stream_kernel<NT, WARPS, MINB>;
   if (smem > 48 * 1024) {
@@ -198,7 +250,7 @@ int launch_variant(const void* X, const void* W, void* out, int M, int N, int K,
   const int k_per_split = ((K + splits - 1) / splits + kChunk - 1) / kChunk * kChunk;
   const dim3 grid((N + 15) / 16, (K + k_per_split - 1) / k_per_split);
   LRM_LAUNCH(kernel, grid, WARPS * 32, smem, stream, static_cast<const __nv_bfloat16*>(X),
-             static_cast<const __nv_bfloat16*>(W), out, M, N, K, mode, k_per_split);
+             static_cast<const __nv_bfloat16*>(W), out, M, N, K, mode, k_per_split, pick);
   return 0;
 }
 
@@ -206,13 +258,29 @@ int launch_variant(const void* X, const void* W, void* out, int M, int N, int K,
 // 128 beyond (the accumulators of 4 or 8 column tiles need them).
 template <int NT>
 int launch_stream(const void* X, const void* W, void* out, int M, int N, int K, int mode, int warps,
-                  int splits, cudaStream_t stream) {
+                  int splits, const PickArgs& pick, cudaStream_t stream) {
   constexpr int kWarpsPerSm = NT <= 2 ? 32 : 16;
-  if (warps >= 16) return launch_variant<NT, 16, kWarpsPerSm / 16>(X, W, out, M, N, K, mode, splits, stream);
-  if (warps >= 8) return launch_variant<NT, 8, kWarpsPerSm / 8>(X, W, out, M, N, K, mode, splits, stream);
-  if (warps >= 4) return launch_variant<NT, 4, kWarpsPerSm / 4>(X, W, out, M, N, K, mode, splits, stream);
-  if (warps >= 2) return launch_variant<NT, 2, kWarpsPerSm / 2>(X, W, out, M, N, K, mode, splits, stream);
-  return launch_variant<NT, 1, kWarpsPerSm>(X, W, out, M, N, K, mode, splits, stream);
+  if (warps >= 16) return launch_variant<NT, 16, kWarpsPerSm / 16>(X, W, out, M, N, K, mode, splits, pick, stream);
+  if (warps >= 8) return launch_variant<NT, 8, kWarpsPerSm / 8>(X, W, out, M, N, K, mode, splits, pick, stream);
+  if (warps >= 4) return launch_variant<NT, 4, kWarpsPerSm / 4>(X, W, out, M, N, K, mode, splits, pick, stream);
+  if (warps >= 2) return launch_variant<NT, 2, kWarpsPerSm / 2>(X, W, out, M, N, K, mode, splits, pick, stream);
+  return launch_variant<NT, 1, kWarpsPerSm>(X, W, out, M, N, K, mode, splits, pick, stream);
+}
+
+int launch_rows(const void* X, const void* W, void* out, int M, int N, int K, int mode, int warps, int splits,
+                const PickArgs& pick, cudaStream_t stream) {
+  // enough warps per CTA that each has at least one chunk
+  const int tiles = (N + 15) / 16;
+  const int chunks = ((K + splits - 1) / splits + 127) / 128;
+  if (warps == 0) {
+    warps = 4;
+    while (warps < 16 && tiles * splits * warps < 148 * 16 && warps * 2 <= chunks) warps *= 2;
+    while (warps > 1 && warps > chunks) warps /= 2;
+  }
+  if (M <= 8) return launch_stream<1>(X, W, out, M, N, K, mode, warps, splits, pick, stream);
+  if (M <= 16) return launch_stream<2>(X, W, out, M, N, K, mode, warps, splits, pick, stream);
+  if (M <= 32) return launch_stream<4>(X, W, out, M, N, K, mode, warps, splits, pick, stream);
+  return launch_stream<8>(X, W, out, M, N, K, mode, warps < 8 ? warps : 8, splits, pick, stream);
 }
 
 }  // namespace
@@ -255,19 +323,31 @@ LRM_API int lrm_gemm_bf16_stream_shaped(const void* X, const void* W, void* out,
   if (mode < 0 || mode > 4 || (mode == 3 && N % 16 != 0)) return LRM_BAD_ARGUMENT;
   if (warps < 0 || warps > 16 || splits < 0 || splits > 64 || (splits > 1 && mode != 4)) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
-  // then enough warps per CTA that each has at least one chunk
-  const int tiles = (N + 15) / 16;
   splits = mode == 4 ? pick_splits(N, K, splits) : 1;
-  const int chunks = ((K + splits - 1) / splits + 127) / 128;
-  if (warps == 0) {
-    warps = 4;
-    while (warps < 16 && tiles * splits * warps < 148 * 16 && warps * 2 <= chunks) warps *= 2;
-    while (warps > 1 && warps > chunks) warps /= 2;
-  }
-  if (M <= 8) return launch_stream<1>(X, W, out, M, N, K, mode, warps, splits, stream);
-  if (M <= 16) return launch_stream<2>(X, W, out, M, N, K, mode, warps, splits, stream);
-  if (M <= 32) return launch_stream<4>(X, W, out, M, N, K, mode, warps, splits, stream);
-  return launch_stream<8>(X, W, out, M, N, K, mode, warps < 8 ? warps : 8, splits, stream);
+  return launch_rows(X, W, out, M, N, K, mode, warps, splits, PickArgs{}, stream);
+}
+
+// The head product with the token choice in its epilogue: ids[m] = the chosen vocabulary row for
+// activation row m of X [M, K] against W [N, K] (N = vocabulary), never writing the logits.
+// keys == nullptr: greedy (largest logit, lowest id on ties). Otherwise a draw from
+// softmax(logits / temperature) by Gumbel-max with the noise of lrm_sample_gumbel_rows (same
+// seed, keys and hash), so both ways choose the same token from the same logits. A row with a
+// non-finite logit gives -1. Scratch: `best` (M 64-bit words) and `bad` (M ints), all zero before
+// the call and zero again after it (the second kernel clears what it read), so one allocation
+// serves every call that follows on the same stream; calls that overlap on the GPU must not
+// share it. Two launches (the product, then the winners' ids).
+LRM_API int lrm_gemm_bf16_stream_pick(const void* X, const void* W, int M, int N, int K,
+                                      unsigned long long* best, int* bad, int* ids, float temperature,
+                                      unsigned long long seed, const long long* keys, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (N <= 0 || !lrm_gemm_bf16_stream_supports(M, N, K)) return LRM_UNSUPPORTED;
+  if (best == nullptr || bad == nullptr || ids == nullptr) return LRM_BAD_ARGUMENT;
+  if (keys != nullptr && !(temperature > 0.f)) return LRM_BAD_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
+  PickArgs pick{best, bad, keys, keys != nullptr ? 1.0f / temperature : 1.0f, seed};
+  const int code = launch_rows(X, W, nullptr, M, N, K, 5, 0, 1, pick, stream);
+  if (code != 0) return code;
+  return lrm_pick_winners(best, bad, ids, M, stream);
 }
 
 LRM_API int lrm_gemm_bf16_stream(const void* X, const void* W, void* out, int M, int N, int K,

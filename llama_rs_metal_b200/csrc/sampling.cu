@@ -11,28 +11,7 @@
 // does not depend on what else is in the batch, and no ordered prefix sum over
 // the vocabulary is needed. The draw is distributed as softmax(logits / T).
 #include "common.cuh"
-
-__device__ __forceinline__ uint64_t mix64(uint64_t z) {
-  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
-  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
-  return z ^ (z >> 31);
-}
-
-// uniform in (0,1) with 24 random bits, exactly representable in float32
-__device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t key, uint32_t i) {
-  const uint64_t z = mix64(mix64(seed + 0x9e3779b97f4a7c15ull * (key + 1)) + i);
-  return (static_cast<float>(static_cast<uint32_t>(z >> 40)) + 0.5f) * (1.0f / 16777216.0f);
-}
-
-struct Best {
-  float value;
-  int id;
-};
-__device__ __forceinline__ Best better(Best a, Best b) {
-  // ids < 0 mean "nothing"; a non-finite value never wins because its row is rejected anyway
-  if (b.id >= 0 && (a.id < 0 || b.value > a.value || (b.value == a.value && b.id < a.id))) return b;
-  return a;
-}
+#include "pick.cuh"
 
 // Stage 1: block (row, piece) scans its piece of the row and leaves its best (value, id) and
 // whether it saw a non-finite logit. Stage 2: one block per row reduces the pieces.
@@ -59,8 +38,7 @@ __global__ void pick_pieces_kernel(const float* __restrict__ logits, float* __re
     float v = x[i];
     bad |= !isfinite(v);
     if (GUMBEL) {
-      const float u = hash_uniform(seed, key, static_cast<uint32_t>(i));
-      v = fmaf(v, inv_temperature, -logf(-logf(u)));
+      v = fmaf(v, inv_temperature, gumbel_noise(seed, key, static_cast<uint32_t>(i)));
     }
     best = better(best, Best{v, i});
   }
@@ -88,12 +66,15 @@ __global__ void pick_pieces_kernel(const float* __restrict__ logits, float* __re
 __global__ void pick_reduce_kernel(const float* __restrict__ piece_value,
                                    const int* __restrict__ piece_id, int* __restrict__ out,
                                    int pieces) {
+  __shared__ float s_value[32];
+  __shared__ int s_id[32];
+  __shared__ int s_bad[32];
   pdl_trigger();
   pdl_wait();
   const int row = blockIdx.x;
   Best best{-INFINITY, -1};
   bool bad = false;
-  for (int i = threadIdx.x; i < pieces; i += 32) {
+  for (int i = threadIdx.x; i < pieces; i += blockDim.x) {
     const int id = piece_id[static_cast<size_t>(row) * pieces + i];
     bad |= id == -2;
     best = better(best, Best{piece_value[static_cast<size_t>(row) * pieces + i], id});
@@ -104,13 +85,63 @@ __global__ void pick_reduce_kernel(const float* __restrict__ piece_value,
     best = better(best, other);
   }
   bad = __any_sync(0xffffffffu, bad);
-  if (threadIdx.x == 0) out[row] = bad ? -1 : best.id;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+  if (warps == 1) {
+    if (threadIdx.x == 0) out[row] = bad ? -1 : best.id;
+    return;
+  }
+  if (lane == 0) {
+    s_value[warp] = best.value;
+    s_id[warp] = best.id;
+    s_bad[warp] = bad;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    Best total{-INFINITY, -1};
+    bool any_bad = false;
+    for (int w = 0; w < warps; ++w) {
+      total = better(total, Best{s_value[w], s_id[w]});
+      any_bad |= s_bad[w] != 0;
+    }
+    out[row] = any_bad ? -1 : total.id;
+  }
 }
 
 constexpr int kPiece = 4096;  // logits one stage-1 block scans
 
+// The second stage alone (also the end of the head product that chooses in its epilogue): a warp
+// per row for a few pieces, a block of 256 threads for thousands.
+LRM_API int lrm_pick_reduce(const float* piece_value, const int* piece_id, int* out, int rows, int pieces,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (pieces <= 0 || piece_value == nullptr || piece_id == nullptr || out == nullptr) return LRM_BAD_ARGUMENT;
+  LRM_LAUNCH(pick_reduce_kernel, dim3(rows), pieces > 256 ? 256 : 32, 0, stream, piece_value, piece_id, out, pieces);
+  return 0;
+}
+
 // scratch: rows * pieces floats and as many ints, pieces = ceil(vocab / 4096)
 LRM_API int lrm_pick_pieces(int vocab) { return (vocab + kPiece - 1) / kPiece; }
+
+// The end of a head product that chose in its epilogue (csrc/gemm_bf16_stream.cu, epilogue 5).
+__global__ void pick_winners_kernel(unsigned long long* __restrict__ best, int* __restrict__ bad,
+                                    int* __restrict__ out, int rows) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const unsigned long long key = best[row];
+  const int flag = bad[row];
+  out[row] = flag ? -1 : pick_key_id(key);
+  best[row] = 0ull;  // ready for the next product
+  bad[row] = 0;
+}
+
+LRM_API int lrm_pick_winners(unsigned long long* best, int* bad, int* out, int rows, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (best == nullptr || bad == nullptr || out == nullptr) return LRM_BAD_ARGUMENT;
+  LRM_LAUNCH(pick_winners_kernel, dim3((rows + 63) / 64), 64, 0, stream, best, bad, out, rows);
+  return 0;
+}
 
 static int pick_rows(const float* logits, int* out, float* piece_value, int* piece_id, int rows,
                      int vocab, bool gumbel, float inv_temperature, uint64_t seed,
@@ -124,8 +155,7 @@ static int pick_rows(const float* logits, int* out, float* piece_value, int* pie
   else
     LRM_LAUNCH(pick_pieces_kernel<false>, grid, 256, 0, stream, logits, piece_value, piece_id, vocab, kPiece,
                1.f, static_cast<uint64_t>(0), static_cast<const long long*>(nullptr));
-  LRM_LAUNCH(pick_reduce_kernel, dim3(rows), 32, 0, stream, piece_value, piece_id, out, pieces);
-  return 0;
+  return lrm_pick_reduce(piece_value, piece_id, out, rows, pieces, stream);
 }
 
 LRM_API int lrm_argmax_rows(const float* logits, int* out, float* piece_value, int* piece_id,

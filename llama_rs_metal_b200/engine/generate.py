@@ -169,12 +169,16 @@ def _run_batch(stepper, sampler, live: List[_Live], options, stop, context, canc
             entries = [StepEntry(seq.slot, [seq.pending], [0]) for seq in active]
             for seq in active:
                 seq.pending = None
-        logits = stepper.step(entries)
-        picked = sampler.pick(
-            logits,
-            [seq.result.request for seq in active],
-            [len(seq.result.tokens) for seq in active],
-            [seq.result.prompt + seq.result.tokens for seq in active])
+        requests = [seq.result.request for seq in active]
+        steps = [len(seq.result.tokens) for seq in active]
+        device = sampler.device_picker(requests, steps) if hasattr(sampler, "device_picker") else None
+        if device is not None and hasattr(stepper, "step_pick"):
+            # tokens only: the step chooses on the device and writes no logits
+            picked = stepper.step_pick(entries, device)
+        else:
+            logits = stepper.step(entries)
+            picked = sampler.pick(logits, requests, steps,
+                                  [seq.result.prompt + seq.result.tokens for seq in active])
         if check is not None:
             check()  # the pick above already synchronized with the device
         active = _settle(stepper, active, picked, options, stop, on_token)

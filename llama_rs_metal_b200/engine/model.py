@@ -117,6 +117,35 @@ class DecoderModel:
     # -- forward ---------------------------------------------------------------------
     def forward(self, ctx, cache) -> torch.Tensor:
         """float32 logits [len(ctx.wanted_rows), vocab] for one step."""
+        x = self._hidden_of_wanted_rows(ctx, cache)
+        if x is None:
+            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.runtime.device)
+        logits = self.head(x, out_dtype=torch.float32)
+        if self.plan.logit_scale is not None:
+            ops.scale_(logits, self.plan.logit_scale)
+        return logits
+
+    def forward_pick(self, ctx, cache, temperature=None, seed: int = 0, keys=None) -> torch.Tensor:
+        """int32 [len(ctx.wanted_rows)]: the token chosen at each wanted place, for a caller that
+        wants no logits (generation): greedy when `temperature` is None, else a draw from
+        softmax(logits / temperature) keyed per row by `keys` (int64). The head product chooses in
+        its epilogue where a kernel can (crates/model-runtime/src/execute.rs:238-247 pairs the head
+        with the GPU argmax the same way). -1 marks a row with a non-finite logit."""
+        x = self._hidden_of_wanted_rows(ctx, cache)
+        if x is None:
+            return torch.empty((0,), dtype=torch.int32, device=self.runtime.device)
+        scale = self.plan.logit_scale
+        if scale is not None and scale <= 0:
+            logits = ops.scale_(self.head(x, out_dtype=torch.float32), scale)
+            return ops.argmax_rows(logits) if temperature is None else \
+                ops.sample_gumbel_rows(logits, temperature, seed, keys)
+        if temperature is not None and scale is not None:
+            temperature = temperature / scale  # (s z) / T = z / (T / s)
+        return self.head.pick(x, temperature, seed, keys)
+
+    def _hidden_of_wanted_rows(self, ctx, cache) -> Optional[torch.Tensor]:
+        """Embedding, the scheduled blocks and the final norm on the wanted rows; None when no
+        row is wanted (the cache is filled all the same)."""
         plan = self.plan
         hidden = ops.embed_rows(self.embedding, ctx.token_ids, plan.embedding_scale)
         wanted = ctx.wanted_rows.numel() > 0
@@ -136,11 +165,7 @@ class DecoderModel:
         ctx.next_folds_pending = False
         if not wanted:
             ctx.take_pending()
-            return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=hidden.device)
+            return None
         # the head runs only on the rows whose logits are wanted
         # (crates/model-runtime/src/execute.rs:238-247 does it for the last row)
-        x = self.final_norm.forward(hidden, ctx, rows=ctx.wanted_rows)
-        logits = self.head(x, out_dtype=torch.float32)
-        if plan.logit_scale is not None:
-            ops.scale_(logits, plan.logit_scale)
-        return logits
+        return self.final_norm.forward(hidden, ctx, rows=ctx.wanted_rows)

@@ -145,6 +145,10 @@ class Session:
         buffer that the next step overwrites."""
         return self.runner.step(entries, borrow=True)
 
+    def step_pick(self, entries: Sequence[StepEntry], picker):
+        """For the generation loop when only tokens are wanted: chosen on the device, no logits."""
+        return self.runner.step_pick(entries, picker)
+
     def check_device_status(self) -> None:
         self.runner.check_device_status()
 
@@ -246,6 +250,8 @@ class Session:
         self._own_slot, self._own_tokens, self._last_logits = None, [], None
         self._cancel = False
         self.runner.poisoned = False
+        from ..kernels import ops
+        ops.reset_pick_scratch()  # a step that failed half-way may have left its running bests behind
 
     def snapshot(self, entry: int):
         if self._own_slot is None:

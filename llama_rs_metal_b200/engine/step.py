@@ -71,18 +71,25 @@ def length_bucket(n: int) -> int:
 
 
 class _DecodeGraph:
-    """One captured decode step: static inputs, the graph, its logits [B, vocab]."""
+    """One captured decode step: static inputs, the graph, and what it leaves: float32 logits
+    [B, vocab] with their greedy choice, or (for a caller that only wants tokens, `choice` =
+    (temperature or None, seed)) just the chosen ids, picked in the head product's epilogue."""
 
     RING = 4
 
-    def __init__(self, runner: "StepRunner", batch: int, bucket: int):
+    def __init__(self, runner: "StepRunner", batch: int, bucket: int, choice=None):
         rt = runner.runtime
-        self.batch = batch
+        self.batch, self.choice = batch, choice
         groups = len(runner.cache.kv_groups)
         self.size = (7 + groups) * batch + 1  # pack_host's layout with T = B and every row wanted
-        self.static = torch.zeros(self.size, dtype=torch.int32, device=rt.device)
+        # behind it, 8-byte aligned: one int64 key per row for the noise of temperature sampling
+        self.keys_at = self.size + (self.size & 1)
+        total = self.keys_at + 2 * batch
+        self.static = torch.zeros(total, dtype=torch.int32, device=rt.device)
+        self.keys = self.static[self.keys_at:].view(torch.int64)
         self.ctx = context_over(self.static, rt, "decode", batch, batch, batch, 1, bucket, groups)
-        self.pinned = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.pinned = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.ids: Optional[torch.Tensor] = None  # int32 [B]: the chosen tokens (graphs with a `choice`)
         self.events = [torch.cuda.Event() for _ in range(self.RING)]
         self.turn = 0
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -91,11 +98,14 @@ class _DecodeGraph:
         self.launches = 0
         self.reports_status = False  # the graph holds kernels that write the device status word
 
-    def upload(self, host: np.ndarray) -> None:
+    def upload(self, host: np.ndarray, keys: Optional[Sequence[int]] = None) -> None:
         i = self.turn % self.RING
         self.turn += 1
         self.events[i].synchronize()  # the copy that last used this staging buffer is done
-        self.pinned[i].numpy()[:] = host
+        staged = self.pinned[i].numpy()
+        staged[:self.size] = host
+        if keys is not None:
+            staged[self.keys_at:].view(np.int64)[:] = keys
         self.static.copy_(self.pinned[i], non_blocking=True)
         self.events[i].record()
 
@@ -130,7 +140,7 @@ class StepRunner:
         self.use_graphs = use_graphs and runtime.device.type == "cuda" and model.graph_safe
         # captured decode steps by (batch size, length bucket), least recently used first; each
         # holds its own [batch, vocab] logits, so only the newest `max_graphs` are kept
-        self._graphs: "OrderedDict[Tuple[int, int], _DecodeGraph]" = OrderedDict()
+        self._graphs: "OrderedDict[Tuple, _DecodeGraph]" = OrderedDict()
         self.max_graphs = 24
         self._pool = None
         self.last_launches = 0  # kernels of this library launched by the last step
@@ -182,6 +192,50 @@ class StepRunner:
         cache.commit(growth)
         self.steps_run += 1
         return logits
+
+    def step_pick(self, entries: Sequence[StepEntry], picker) -> List[int]:
+        """A step for a caller that wants tokens, not logits: runs the entries like step() and
+        returns, on the host, the token chosen at every wanted place (entry order, then `want`
+        order) by `picker` (a sampling.device.DevicePick: greedy, or temperature sampling with one
+        key per wanted place). The head product chooses in its epilogue where a kernel can, so no
+        logits are written. -1 marks a place whose logits were not finite."""
+        if self.poisoned:
+            raise PoisonedError("a device error poisoned this session; reset it")
+        entries = list(entries)
+        cache = self.cache
+        if (self.use_graphs and entries and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+                and all(cache.open_mask[e.slot] and cache.lengths[e.slot] > 0 for e in entries
+                        if 0 <= e.slot < cache.max_slots)):
+            return self.decode_ahead([e.slot for e in entries], [e.tokens[0] for e in entries], None, picker).ids()
+        validate_entries(entries, self.model.plan.vocab_size)
+        before = [cache.length(e.slot) for e in entries]
+        phase = classify_step(entries, before)
+        growth = [(e.slot, n + len(e.tokens)) if phase == "prefill" else (e.slot, n + len(e.tokens), n)
+                  for e, n in zip(entries, before)]
+        cache.check_growth(growth)
+        cache.grow(growth)
+        cache.sync()
+        dest_rows = cache.destination_rows([e.slot for e in entries], before, [len(e.tokens) for e in entries])
+        try:
+            ctx = pack_step(entries, before, self.runtime, phase, dest_rows)
+            if phase == "decode":
+                ctx.max_kv_len = length_bucket(ctx.max_kv_len)
+            keys = None
+            if picker.temperature is not None:
+                if len(picker.keys) != ctx.wanted_rows.numel():
+                    raise InvalidError("one sampling key per wanted place")
+                keys = torch.tensor(picker.keys, dtype=torch.int64).pin_memory().to(self.runtime.device,
+                                                                                      non_blocking=True)
+            start = ops.launch_count()
+            ids = self.model.forward_pick(ctx, cache, picker.temperature, picker.seed, keys)
+            self.last_launches = ops.launch_count() - start
+            host = ids.tolist()
+        except Exception:
+            self.poisoned = True
+            raise
+        cache.commit(growth)
+        self.steps_run += 1
+        return host
 
     def check_device_status(self) -> None:
         """Raise if a kernel recorded that it gave up on a bounded wait (reads 4 bytes back,
@@ -292,12 +346,13 @@ class StepRunner:
             raise UnsupportedError("decode_ahead needs open, started sequences")
         host, before = prepared
         try:
-            graph = self._graph_for(batch, int(before.max()) + 1)
-            graph.upload(host)
+            choice = (picker.temperature, picker.seed) if hasattr(picker, "temperature") else None
+            graph = self._graph_for(batch, int(before.max()) + 1, choice)
+            graph.upload(host, picker.keys if choice is not None and picker.temperature is not None else None)
             if tokens is None:
                 graph.static[:batch].copy_(previous.device_ids)  # the ids chosen by the step before
             self._launch(graph)
-            device_ids = picker(graph.logits)
+            device_ids = graph.ids if choice is not None else picker(graph.logits)
             pending = self._pending_slot()
             pending.launch(device_ids, batch)
         except Exception:
@@ -334,8 +389,8 @@ class StepRunner:
             return logits.index_select(0, index)
         return logits if borrow else logits.clone()
 
-    def _graph_for(self, batch: int, max_kv_len: int) -> _DecodeGraph:
-        key = (batch, length_bucket(max_kv_len))
+    def _graph_for(self, batch: int, max_kv_len: int, choice=None) -> _DecodeGraph:
+        key = (batch, length_bucket(max_kv_len), choice)
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = _DecodeGraph(self, *key)
@@ -359,7 +414,13 @@ class StepRunner:
     def _capture(self, graph: _DecodeGraph) -> None:
         # One eager run first: it loads every kernel the step needs and writes
         # exactly what the replay will write again, so it changes no result.
-        self.model.forward(graph.ctx, self.cache)
+        def run():
+            if graph.choice is None:
+                return self.model.forward(graph.ctx, self.cache)
+            temperature, seed = graph.choice
+            return self.model.forward_pick(graph.ctx, self.cache, temperature, seed,
+                                           graph.keys if temperature is not None else None)
+        run()
         torch.cuda.current_stream().synchronize()
         if self._pool is None:
             self._pool = torch.cuda.graph_pool_handle()
@@ -368,11 +429,14 @@ class StepRunner:
         start = ops.launch_count()
         status_launches = gemm_dispatch.status_launch_count()
         with torch.cuda.graph(captured, pool=self._pool):
-            graph.logits = self.model.forward(graph.ctx, self.cache)
-            # the greedy pick rides along (two small kernels): a sampler that wants it finds it
-            # as `logits.greedy_ids` and needs no launch of its own
-            graph.greedy = ops.argmax_rows(graph.logits)
-            graph.logits.greedy_ids = graph.greedy
+            if graph.choice is not None:
+                graph.ids = run()
+            else:
+                graph.logits = run()
+                # the greedy pick rides along (two small kernels): a sampler that wants it finds it
+                # as `logits.greedy_ids` and needs no launch of its own
+                graph.greedy = ops.argmax_rows(graph.logits)
+                graph.logits.greedy_ids = graph.greedy
         graph.launches = ops.launch_count() - start  # the pick's two kernels included
         graph.reports_status = gemm_dispatch.status_launch_count() > status_launches
         graph.graph = captured

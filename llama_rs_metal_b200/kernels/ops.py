@@ -415,6 +415,65 @@ def _pick_scratch(logits: torch.Tensor):
     return values, ids
 
 
+PICK_ROWS = 12  # up to this many rows the streaming product is the head's fastest kernel, and it can choose
+
+_pick_words_by_device = {}
+
+
+def _pick_words(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Per device: 64 running-best words and 64 flags for the head product that chooses in its
+    epilogue. Zero between calls (the kernel that reads the winners clears them), so every call
+    on a stream can share them; reset_pick_scratch() zeroes them after a failed step."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _pick_words_by_device:
+        _pick_words_by_device[index] = (torch.zeros(64, dtype=torch.int64, device=device),
+                                        torch.zeros(64, dtype=torch.int32, device=device))
+    return _pick_words_by_device[index]
+
+
+def reset_pick_scratch() -> None:
+    for best, bad in _pick_words_by_device.values():
+        best.zero_()
+        bad.zero_()
+
+
+def linear_pick(x: torch.Tensor, weight: torch.Tensor, temperature: Optional[float] = None, seed: int = 0,
+                keys: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """int32 [M]: the token chosen from the logits x . weight^T of each row, without writing the
+    logits: every CTA of the head product offers its best (score, id) per row to the row's
+    running best with an atomic maximum, and a second small kernel reads the winners.
+    temperature None: greedy, as argmax_rows; else a draw from softmax(logits / temperature) with
+    the noise of sample_gumbel_rows for the same seed and keys (int64 [M]). -1 marks a row with a
+    non-finite logit. None when no kernel takes this product that way (float32, more rows than
+    the streaming product is the fastest for, unaligned): the caller then writes the logits and
+    picks from them."""
+    _check(x, "x", dims=2)
+    _check(weight, "weight", dims=2)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise InvalidError(f"linear_pick: x has {K} columns, weight has {weight.shape[1]}")
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or M > PICK_ROWS:
+        return None
+    lib = _lib()
+    if not lib.lrm_gemm_bf16_stream_supports(M, N, K) or x.data_ptr() % 16 or weight.data_ptr() % 16:
+        return None
+    if temperature is not None:
+        if keys is None or not temperature > 0:
+            raise InvalidError("linear_pick: temperature sampling needs a positive temperature and one key per row")
+        _check(keys, "keys", torch.int64, 1)
+        if keys.numel() != M:
+            raise InvalidError("linear_pick: one key per row")
+    best, bad = _pick_words(x.device)
+    out = torch.empty((M,), dtype=torch.int32, device=x.device)
+    _done(lib.lrm_gemm_bf16_stream_pick(_ptr(x), _ptr(weight), M, N, K, _ptr(best), _ptr(bad), _ptr(out),
+                                        ctypes.c_float(temperature if temperature is not None else 1.0),
+                                        ctypes.c_ulonglong(seed & ((1 << 64) - 1)),
+                                        _ptr(keys if temperature is not None else None), _stream()),
+          "gemm_bf16_stream_pick", launches=2)
+    return out
+
+
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     """int32 [n]: largest logit per row, lowest id on ties, -1 for a row with a non-finite logit."""
     _check(logits, "logits", torch.float32, 2)

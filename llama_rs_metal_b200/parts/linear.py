@@ -23,6 +23,19 @@ class LinearWeight:
     def out_features(self) -> int:
         return self.weight.shape[0]
 
+    def pick(self, x: torch.Tensor, temperature=None, seed: int = 0, keys=None):
+        """The token chosen from each row's logits x . W^T (greedy, or temperature sampling with
+        per-row keys), int32 [M], -1 for a row with a non-finite logit. The logits are not
+        written where a kernel chooses in the product's epilogue."""
+        if x.dtype == self.weight.dtype:
+            ids = ops.linear_pick(x, self.weight, temperature, seed, keys)
+            if ids is not None:
+                return ids
+        logits = self(x, out_dtype=torch.float32)
+        if temperature is None:
+            return ops.argmax_rows(logits)
+        return ops.sample_gumbel_rows(logits, temperature, seed, keys)
+
     def supports_fused_gate(self, x_dtype: torch.dtype) -> bool:
         return self.weight.dtype == torch.bfloat16 and x_dtype == torch.bfloat16
 

@@ -11,6 +11,23 @@ from .host import SplitMix64, sample_host
 from .options import Sampling
 
 
+class DevicePick:
+    """How a step's tokens are chosen on the device: greedy (`temperature` None) or a draw from
+    softmax(logits / temperature) whose noise is keyed by (seed, keys[row]). Called on logits it
+    enqueues the choice and returns int32 [rows] ids without waiting; a stepper that reads the
+    fields instead can choose inside the head product and never write the logits."""
+
+    def __init__(self, temperature, seed: int, keys: Sequence[int]):
+        self.temperature, self.seed, self.keys = temperature, seed, list(keys)
+
+    def __call__(self, logits: torch.Tensor) -> torch.Tensor:
+        if self.temperature is None:
+            ready = getattr(logits, "greedy_ids", None)
+            return ready if ready is not None and ready.shape[0] == logits.shape[0] else ops.argmax_rows(logits)
+        keys = torch.tensor(self.keys, dtype=torch.int64).pin_memory().to(logits.device, non_blocking=True)
+        return ops.sample_gumbel_rows(logits, self.temperature, self.seed, keys)
+
+
 class BatchSampler:
     """Picks one token per row of a step's logits.
 
@@ -32,17 +49,11 @@ class BatchSampler:
         tensor of chosen ids that enqueues work but never waits for the device; None for the
         host sampler. -1 in its result marks a row with non-finite logits."""
         o = self.options
+        keys = [(r << 32) | s for r, s in zip(requests, steps)]
         if o.greedy:
-            def greedy(logits):
-                ready = getattr(logits, "greedy_ids", None)
-                return ready if ready is not None and ready.shape[0] == logits.shape[0] else ops.argmax_rows(logits)
-            return greedy
+            return DevicePick(None, 0, keys)
         if o.plain_temperature:
-            keys = torch.tensor([(r << 32) | s for r, s in zip(requests, steps)], dtype=torch.int64)
-
-            def gumbel(logits):
-                return ops.sample_gumbel_rows(logits, o.temperature, o.seed, keys.to(logits.device, non_blocking=True))
-            return gumbel
+            return DevicePick(o.temperature, o.seed, keys)
         return None
 
     def pick(self, logits: torch.Tensor, requests: Sequence[int], steps: Sequence[int],

@@ -504,6 +504,45 @@ def test_argmax_rows_ties_and_non_finite(ops):
 from helpers import gumbel_twin  # noqa: E402  (the kernel's draw restated on the CPU)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 12])
+@pytest.mark.parametrize("N,K", [(5003, 72), (40, 520), (128256, 64)])
+def test_head_product_that_chooses_in_its_epilogue(ops, M, N, K):
+    """The head product that leaves only the chosen token: equal to the choice over the logits the
+    same product writes, for the greedy rule (ties to the lowest id, whether the tied ids share a
+    16-row tile or not; -1 for a row with a non-finite logit) and for temperature sampling."""
+    x, w = rnd(M, K, dtype=torch.bfloat16), rnd(N, K, dtype=torch.bfloat16, seed=1)
+    w[N - 1] = w[3]                       # a tie across tiles ...
+    w[20] = w[17]                         # ... and one inside a tile
+    x[0] = 0
+    x[0, :8] = 4.0
+    w[3, :8] = w[N - 1, :8] = 8.0         # row 0: ids 3 and N - 1 tie for the largest logit
+    if M > 2:
+        x[2] = 0
+        x[2, 8:16] = 4.0
+        w[17, 8:16] = w[20, 8:16] = 8.0   # row 2: ids 17 and 20 tie
+    logits = ops.linear(x, w, out_dtype=torch.float32)
+    got = ops.linear_pick(x, w)
+    assert got is not None and got.dtype == torch.int32
+    assert got.tolist() == ops.argmax_rows(logits).tolist()
+    assert got[0].item() == 3 and (M <= 2 or got[2].item() == 17)
+    for r in range(M):
+        assert got[r].item() == P.argmax_lowest(logits[r].cpu())
+    keys = torch.tensor([(r << 32) | 5 for r in range(M)], dtype=torch.int64, device=DEV)
+    drawn = ops.linear_pick(x, w, temperature=0.8, seed=9, keys=keys)
+    assert drawn.tolist() == ops.sample_gumbel_rows(logits, 0.8, 9, keys).tolist()
+    if M > 1:
+        bad = w.clone()
+        bad[N // 2, 0] = float("inf")
+        x2 = x.clone()
+        x2[1, 0] = 1.0                    # row 1 meets the infinite weight; a row with x = 0 there gives nan
+        out = ops.linear_pick(x2, bad).tolist()
+        assert out[1] == -1
+    assert ops.linear_pick(x.float(), w.float()) is None          # no such kernel in float32: the caller picks from logits
+    wide = rnd(13, K, dtype=torch.bfloat16)
+    assert ops.linear_pick(wide, w) is None                        # more rows go to the tensor-core product, which writes logits
+    assert ops.linear_pick(x, w).tolist() == got.tolist()          # the shared scratch was left clean
+
+
 def test_gumbel_sampling_matches_its_cpu_twin_and_ignores_batch_company(ops):
     logits = rnd(6, 333, scale=2.0)
     keys = torch.tensor([(r << 32) | 3 for r in range(6)], dtype=torch.int64, device=DEV)
