@@ -1,18 +1,27 @@
 #!/usr/bin/env python3
-"""Decode and prefill throughput of the Llama 3.2 1B shape on one B200.
+"""Decode and prefill throughput of the Llama 3 shapes on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 1b|3b|8b] [--profile]
 
-Prints ONE JSON line. A "step" is one decode step of a batch of 8 sequences at
-context 4,096 (every sequence's next token: model forward plus the greedy pick).
+Prints ONE JSON line. A "step" is one decode step of a batch of sequences (every
+sequence's next token: model forward plus the greedy pick, as generation runs it).
 `value` is decoded tokens per second timed on the device with CUDA events;
 `e2e` is the same through the Python entry point (Session.generate: host token
 ids in, host token ids out, every step's inputs copied from pinned host memory
 and every step's picked ids read back). Also on the line: the prefill of one
-2,048-token prompt, the decode step's HBM roofline, decode at batch 1 and 64.
+2,048-token prompt, the decode step's HBM roofline, decode at other batch sizes,
+and the plain CPU implementation's speed on a tiny configuration beside the
+engine's (what the kernels are worth against the formulas run as written).
 
-Weights are random (seeded), token ids synthetic; the reference publishes no
-number for this configuration, so `vs_baseline` is null.
+The default is the Llama 3.2 1B shape at context 4,096 and batch 8; `--shape 3b`
+and `--shape 8b` run the other shapes the baseline lists (16 unequal prompts at
+the 3B shape; context 8,192 and batches 1/8/32 at the 8B shape).
+
+Before anything is timed, the build's logits are compared with the plain
+implementation at the shape's full widths (see correctness_gate); a build that
+fails prints no number. Weights are random (seeded), token ids synthetic; the
+reference publishes no number for these configurations, so `vs_baseline` is null.
 """
 import argparse
 import json
@@ -28,16 +37,27 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# The Llama 3.2 1B shape: the configuration the benchmark is quoted on
-LLAMA_1B = dict(
-    architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=2048, intermediate_size=8192,
-    num_hidden_layers=16, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
-    vocab_size=128256, rope_theta=500000.0,
-    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
-                      original_max_position_embeddings=8192),
-    rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
-FULL_LAYERS = 16
-CONTEXT = 4096
+
+def llama(hidden, inter, layers, heads, kv_heads, head_dim, factor, tied):
+    return dict(
+        architectures=["LlamaForCausalLM"], model_type="llama", hidden_size=hidden, intermediate_size=inter,
+        num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim,
+        vocab_size=128256, rope_theta=500000.0,
+        rope_scaling=dict(rope_type="llama3", factor=factor, low_freq_factor=1.0, high_freq_factor=4.0,
+                          original_max_position_embeddings=8192),
+        rms_norm_eps=1e-5, tie_word_embeddings=tied, max_position_embeddings=131072)
+
+
+# name -> the shape's config.json, the benchmark context, the batch of the main number, the other
+# batches measured, and how the requests' lengths are drawn
+SHAPES = {
+    "1b": dict(name="Llama-3.2-1B shape", config=llama(2048, 8192, 16, 32, 8, 64, 32.0, True), context=4096,
+               batch=8, points=(1, 64), prompts=(256, 2048), to_context=True),
+    "3b": dict(name="Llama-3.2-3B shape", config=llama(3072, 8192, 28, 24, 8, 128, 32.0, True), context=8192,
+               batch=16, points=(), prompts=(64, 4096), to_context=False),
+    "8b": dict(name="Llama-3.1-8B shape", config=llama(4096, 14336, 32, 32, 8, 128, 8.0, False), context=8192,
+               batch=8, points=(1, 32), prompts=(256, 2048), to_context=True),
+}
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
@@ -102,9 +122,9 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(clocks))
 
 
-def decode_bytes(config, layers, kv_lens, batch):
+def decode_bytes(config, kv_lens, batch):
     """Bytes a decode step has to read: every weight it uses once, and the live requests' cache."""
-    h, inter = config["hidden_size"], config["intermediate_size"]
+    h, inter, layers = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
     q = config["num_attention_heads"] * config["head_dim"]
     kv = config["num_key_value_heads"] * config["head_dim"]
     per_layer = (h * (q + 2 * kv) + q * h + 3 * h * inter) * 2 + 2 * h * 2
@@ -113,8 +133,8 @@ def decode_bytes(config, layers, kv_lens, batch):
     return weights + cache
 
 
-def prefill_flops(config, layers, tokens):
-    h, inter = config["hidden_size"], config["intermediate_size"]
+def prefill_flops(config, tokens):
+    h, inter, layers = config["hidden_size"], config["intermediate_size"], config["num_hidden_layers"]
     q = config["num_attention_heads"] * config["head_dim"]
     kv = config["num_key_value_heads"] * config["head_dim"]
     linear = 2 * tokens * (h * (q + 2 * kv) + q * h + 3 * h * inter)
@@ -122,26 +142,63 @@ def prefill_flops(config, layers, tokens):
     return layers * (linear + attention) + 2 * config["vocab_size"] * h
 
 
-def correctness_gate(engine, model_dir) -> str:
-    """Numbers are recorded only from a build whose logits agree with the plain implementation
-    (the reference times only what passed its numerical gate, tools/benchmarks/run.py:130-145).
-    The first two layers of the very weights that are timed, at their full widths, run in true
-    float32 and in bfloat16, whole prompts, an unequal batch with decoding, and portions, against
-    the plain CPU implementation under tests/. Takes some seconds; raises AssertionError."""
+def tests_on_path():
     tests = os.path.join(ROOT, "tests")
     if tests not in sys.path:
         sys.path.insert(0, tests)
+
+
+def correctness_gate(engine, config) -> str:
+    """Numbers are recorded only from a build whose logits agree with the plain implementation
+    (the reference times only what passed its numerical gate, tools/benchmarks/run.py:130-145).
+    A model with the first two layers of the shape that is timed, at its full widths, is written
+    as a folder and run in true float32 and in bfloat16: whole prompts, an unequal batch with
+    decoding, and portions, against the plain CPU implementation under tests/. Some seconds;
+    raises AssertionError."""
+    tests_on_path()
     import helpers
+    from llama_rs_metal_b200.engine.session import write_random_model
     started = time.perf_counter()
-    small = helpers.narrowed_copy(model_dir, model_dir + "_gate", min(2, json.load(
-        open(os.path.join(model_dir, "config.json")))["num_hidden_layers"]))
-    worst = {}
-    for dtype in ("float32", "bfloat16"):
-        worst[dtype] = helpers.parity_with_plain(engine, small, dtype, prompt_lengths=(150, 70, 9), decode_steps=3)
+    folder = tempfile.mkdtemp(prefix="bench_gate_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    try:
+        write_random_model(folder, dict(config, num_hidden_layers=min(2, config["num_hidden_layers"])), seed=0, std=0.02)
+        worst = {dtype: helpers.parity_with_plain(engine, folder, dtype, prompt_lengths=(150, 70, 9), decode_steps=3)
+                 for dtype in ("float32", "bfloat16")}
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
     return (f"passed: 2 layers at full widths vs the plain CPU implementation, worst error "
             f"{worst['float32']:.1e} (float32, allowed {helpers.TOLERANCE['float32']:.0e}) and "
             f"{worst['bfloat16']:.1e} (bfloat16, allowed {helpers.TOLERANCE['bfloat16']:.0e}) of the largest "
             f"logit, {time.perf_counter() - started:.0f} s")
+
+
+def plain_cpu_point(engine):
+    """The plain implementation on the CPU and the engine on the GPU, same tiny model (configuration A
+    of the tests, float32), same greedy workload: tokens per second of each."""
+    tests_on_path()
+    import helpers
+    import plain_llama
+    from llama_rs_metal_b200 import GenerationOptions, Sampling
+    folder = tempfile.mkdtemp(prefix="bench_tiny_")
+    try:
+        helpers.make_model_dir(folder, "A")
+        config, tensors = plain_llama.read_model(folder)
+        prompts = [helpers.random_tokens(1 + i, n, 256) for i, n in enumerate((5, 11, 17))]
+        steps = 8
+        started = time.perf_counter()
+        want = [plain_llama.greedy_continue(config, tensors, p, steps) for p in prompts]
+        cpu = len(prompts) * steps / (time.perf_counter() - started)
+        session = engine.load(folder, dtype="float32").session(context=128, max_batch=3)
+        options = GenerationOptions(max_tokens=steps, sampling=Sampling(temperature=0.0))
+        session.generate(prompts, options, stop_token_ids=())
+        started = time.perf_counter()
+        got = session.generate(prompts, options, stop_token_ids=())
+        gpu = len(prompts) * steps / (time.perf_counter() - started)
+        same = sum(a == b for r, w in zip(got, want) for a, b in zip(r.tokens, w))
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    return {"plain_cpu_tiny_a_tok_s": round(cpu, 1), "engine_tiny_a_tok_s": round(gpu, 1),
+            "tiny_a_tokens_equal": f"{same}/{len(prompts) * steps}"}
 
 
 def main() -> int:
@@ -150,14 +207,18 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=16)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=FULL_LAYERS,
-                        help="fewer layers than the configuration's 16 (named in config when used)")
-    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 / prefill extras")
+    parser.add_argument("--shape", default="1b", choices=sorted(SHAPES))
+    parser.add_argument("--batch", type=int, default=None, help="batch of the main number (default: the shape's)")
+    parser.add_argument("--layers", type=int, default=None,
+                        help="fewer layers than the shape has (both numbers are named in config)")
+    parser.add_argument("--no-points", action="store_true", help="skip the other batch sizes, prefill and CPU extras")
     parser.add_argument("--no-gate", action="store_true",
                         help="skip the correctness gate (profiling runs only; the line then says so)")
     parser.add_argument("--only", choices=["prefill"], default=None,
                         help="run just this part (a small case for profiling); prints a shorter line")
+    parser.add_argument("--profile", action="store_true",
+                        help="time every kernel launch (LRM_PROFILE=1) and print the table to stderr; the "
+                             "line's numbers are then those of unfused, uncaptured launches")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -170,38 +231,42 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.profile:
+        os.environ["LRM_PROFILE"] = "1"
 
     import numpy as np
     import torch
     from llama_rs_metal_b200 import Engine, GenerationOptions, Sampling
     from llama_rs_metal_b200.engine.batch import StepEntry
-    from llama_rs_metal_b200.engine.session import write_random_model
-    from llama_rs_metal_b200.kernels import ops
+    from llama_rs_metal_b200.sampling.device import DevicePick
 
+    shape = SHAPES[args.shape]
+    full_layers = shape["config"]["num_hidden_layers"]
+    layers = args.layers or full_layers
+    config = dict(shape["config"], num_hidden_layers=layers)
+    context, batch_main = shape["context"], args.batch or shape["batch"]
     peaks, peak_source = load_peaks()
-    config = dict(LLAMA_1B, num_hidden_layers=args.layers)
-    scratch = tempfile.mkdtemp(prefix="bench_model_", dir="/dev/shm" if os.path.isdir("/dev/shm") else None)
+    engine = Engine(0)
     gate = "skipped (--no-gate)"
-    try:
-        write_random_model(scratch, config, seed=0, std=0.02)
-        engine = Engine(0)
-        if not args.no_gate:
-            gate = correctness_gate(engine, scratch)   # raises: no numbers from a build that computes wrongly
-        model = engine.load(scratch, dtype="bfloat16")
-    except AssertionError as failure:
-        print(f"correctness gate failed, nothing was timed: {failure}", file=sys.stderr)
-        return 1
-    finally:
-        shutil.rmtree(scratch, ignore_errors=True)
-        shutil.rmtree(scratch + "_gate", ignore_errors=True)
+    if not args.no_gate:
+        try:
+            gate = correctness_gate(engine, config)   # raises: no numbers from a build that computes wrongly
+        except AssertionError as failure:
+            print(f"correctness gate failed, nothing was timed: {failure}", file=sys.stderr)
+            return 1
+    model = engine.random(config, seed=0, std=0.02)   # drawn on the device: seconds even at the 8B shape
     vocab = config["vocab_size"]
     rng = np.random.default_rng(0)
+    low, high = shape["prompts"]
 
     def start_lengths(batch):
-        """Each request's prompt is U[256, 2048] tokens and it generates to 4,096 in total; the
-        timed steps run at the midpoint of that generation, where a step costs its average."""
-        prompts = rng.integers(256, 2049, size=batch)
-        return [int((p + CONTEXT) // 2) for p in prompts]
+        """Prompt lengths are U[low, high]. Where requests generate to the full context, the timed
+        steps run at the midpoint of that generation (where a step costs its average); where a fixed
+        number of steps follows the prompts, they start right after the prompts."""
+        prompts = rng.integers(low, high + 1, size=batch)
+        if shape["to_context"]:
+            return [int((p + context) // 2) for p in prompts]
+        return [int(p) for p in prompts]
 
     def fill(session, lengths):
         """Open a slot per sequence and run its tokens up to `lengths` through real prefill steps."""
@@ -217,14 +282,16 @@ def main() -> int:
         return slots
 
     def time_decode(batch, steps, warmup, sample_clocks=False):
-        session = model.session(context=CONTEXT, max_batch=batch)
+        session = model.session(context=context, max_batch=batch)
         lengths = start_lengths(batch)
         slots = fill(session, lengths)
         tokens = rng.integers(0, vocab, size=(warmup + steps, batch))
+        greedy = DevicePick(None, 0, [0] * batch)
 
-        def one(i):
-            logits = session.runner.step([StepEntry(s, [int(t)], (0,)) for s, t in zip(slots, tokens[i])], borrow=True)
-            return logits.greedy_ids if hasattr(logits, "greedy_ids") else ops.argmax_rows(logits)
+        def one(i):  # the step generation runs: tokens in, the chosen tokens out, no logits kept
+            if args.profile:  # uncaptured, so that every launch passes through its timed wrapper
+                return session.runner.step_pick([StepEntry(s, [int(t)], (0,)) for s, t in zip(slots, tokens[i])], greedy)
+            return session.runner.decode_ahead(slots, tokens[i].tolist(), None, greedy)
         for i in range(warmup):
             one(i)
         torch.cuda.synchronize()
@@ -234,23 +301,23 @@ def main() -> int:
             time.sleep(0.3)
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         begin.record()
-        graph_launches = 0
+        launches = 0
         for i in range(warmup, warmup + steps):
             one(i)
-            graph_launches += session.runner.last_launches
+            launches += session.runner.last_launches
         end.record()
         torch.cuda.synchronize()
         clocks = sampler.stop() if sample_clocks else None
+        session.runner.check_device_status()
         ms = begin.elapsed_time(end) / steps
         mid = [n + warmup + steps // 2 for n in lengths]
-        launches = graph_launches           # the step's kernels, the greedy pick's two among them
         for s in slots:
             session.close_slot(s)
-        return dict(ms=ms, tokens_per_s=batch * 1000.0 / ms, bytes=decode_bytes(config, args.layers, mid, batch),
+        return dict(ms=ms, tokens_per_s=batch * 1000.0 / ms, bytes=decode_bytes(config, mid, batch),
                     kv_mean=sum(mid) / batch, launches=launches, clocks=clocks)
 
     def time_e2e(batch, steps):
-        session = model.session(context=CONTEXT, max_batch=batch)
+        session = model.session(context=context, max_batch=batch)
         prompts = [rng.integers(0, vocab, size=n).tolist() for n in start_lengths(batch)]
         options = GenerationOptions(max_tokens=steps + 1, sampling=Sampling(temperature=0.0))
         session.generate(prompts, options, stop_token_ids=())   # warm-up: the same steps once, untimed
@@ -261,10 +328,11 @@ def main() -> int:
         torch.cuda.synchronize()
         done = time.perf_counter()
         first = stamps[batch - 1]           # every request's first token (the prefill's) is out
-        return batch * steps / (done - first), (8 * batch + 1) * 4, batch * 4
+        groups = len(session.cache.kv_groups)
+        return batch * steps / (done - first), ((7 + groups) * batch + 1) * 4, batch * 4
 
     def time_prefill(tokens, reps=5):
-        session = model.session(context=CONTEXT, max_batch=1)
+        session = model.session(context=context, max_batch=1)
         ids = rng.integers(0, vocab, size=tokens).tolist()
         times = []
         for rep in range(reps + 2):
@@ -277,32 +345,40 @@ def main() -> int:
             session.close_slot(slot)
             if rep >= 2:
                 times.append(begin.elapsed_time(end))
+        session.runner.check_device_status()
         return statistics.median(times)
 
     if args.only == "prefill":
         ms = time_prefill(PREFILL_TOKENS, reps=max(1, args.steps))
-        flops = prefill_flops(config, args.layers, PREFILL_TOKENS)
+        flops = prefill_flops(config, PREFILL_TOKENS)
         print(json.dumps({"metric": "prefill tok/s, one 2048-token prompt", "value": round(PREFILL_TOKENS / (ms * 1e-3), 1),
-                          "unit": "tok/s", "ms": round(ms, 3), "layers": args.layers,
+                          "unit": "tok/s", "ms": round(ms, 3), "layers": layers, "shape": shape["name"],
                           "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "peaks": peak_source,
                           "gate": gate}))
         return 0
-    main_run = time_decode(args.batch, args.steps, args.warmup, sample_clocks=True)
-    e2e_value, h2d, d2h = time_e2e(args.batch, args.steps)
+    steps = args.steps
+    if not shape["to_context"]:
+        steps = min(steps, 256)  # the 3B workload is 256 decode steps after the prompts
+    main_run = time_decode(batch_main, steps, args.warmup, sample_clocks=True)
+    e2e_value, h2d, d2h = time_e2e(batch_main, steps)
     achieved = main_run["bytes"] / (main_run["ms"] * 1e-3) / 1e9
+    cfg = config
+    lengths_note = (f"U[{low},{high}], generating to {context}; timed at each request's midpoint" if shape["to_context"]
+                    else f"U[{low},{high}], then {steps} decode steps")
     line = {
-        "metric": "decode tok/s at batch 8, context 4096 (Llama 3.2 1B shape, random bf16 weights)",
-        "value": round(main_run["tokens_per_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
+        "metric": f"decode tok/s at batch {batch_main}, context {context} ({shape['name']}, random bf16 weights)",
+        "value": round(main_run["tokens_per_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": steps,
         "warmup": args.warmup, "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
         "impl": "ours", "gate": gate,
         "config": {
-            "model": "Llama-3.2-1B shape", "layers": args.layers, "layers_of_config": FULL_LAYERS,
-            "hidden": 2048, "heads": 32, "kv_heads": 8, "head_dim": 64, "intermediate": 8192,
-            "vocab": 128256, "global_batch": args.batch, "seq_len": CONTEXT,
-            "kv_len_mean": round(main_run["kv_mean"], 1), "prompt_lengths": "U[256,2048], generating to 4096; "
-            "timed at each request's midpoint", "parallelism": "single GPU", "l2": "step reads > L2 (weights 2.5 GB)",
-            "peaks": peak_source, "cuda_graph": True,
+            "model": shape["name"], "layers": layers, "layers_of_config": full_layers,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied_head": cfg["tie_word_embeddings"], "global_batch": batch_main, "seq_len": context,
+            "kv_len_mean": round(main_run["kv_mean"], 1), "prompt_lengths": lengths_note,
+            "parallelism": "single GPU", "l2": "step reads > L2 (weights alone are GBs)",
+            "peaks": peak_source, "cuda_graph": not args.profile,
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(main_run["launches"]),
@@ -312,16 +388,21 @@ def main() -> int:
     }
     if not args.no_points:
         ms = time_prefill(PREFILL_TOKENS)
-        flops = prefill_flops(config, args.layers, PREFILL_TOKENS)
+        flops = prefill_flops(config, PREFILL_TOKENS)
         line["prefill"] = {"value": round(PREFILL_TOKENS / (ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
                            "ms": round(ms, 3), "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
         points = {}
-        for batch in (1, 64):
-            run = time_decode(batch, max(16, args.steps // 2), 4)
+        for batch in shape["points"]:
+            run = time_decode(batch, max(16, steps // 2), 4)
             points[f"decode_b{batch}"] = round(run["tokens_per_s"], 1)
             points[f"decode_b{batch}_hbm_frac"] = round(run["bytes"] / (run["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        points.update(plain_cpu_point(engine))
         line["points"] = points
     print(json.dumps(line))
+    if args.profile:
+        from llama_rs_metal_b200.kernels import profile
+        profile.report()
+        profile.reset()
     return 0
 
 

@@ -63,6 +63,15 @@ class Engine:
     def load(self, model_dir: str, dtype="bfloat16") -> "Model":
         return Model(self, model_dir, parse_dtype(dtype))
 
+    def random(self, config: dict, seed: int = 0, std: float = 0.02, norm_mean: float = 1.0,
+               norm_std: float = 0.0, dtype="bfloat16") -> "Model":
+        """A model of the architecture `config` (a config.json dict) names with random weights drawn
+        on the device: no folder, no file, seconds even for billions of weights. For measurements
+        at sizes whose folder would take minutes to write; write_random_model() is the mode that
+        leaves a loadable folder."""
+        return Model(self, None, parse_dtype(dtype), random=dict(config=config, seed=seed, std=std,
+                                                                norm_mean=norm_mean, norm_std=norm_std))
+
 
 def build_model(model_dir: str, runtime: Runtime):
     """(config, plan, model with weights bound, bytes of weights) for a model folder. Stored
@@ -80,16 +89,32 @@ def build_model(model_dir: str, runtime: Runtime):
     return config, plan, model, weight_bytes
 
 
+def build_random_model(spec: dict, runtime: Runtime):
+    """build_model() for weights drawn on the device instead of read from a folder."""
+    arch = find_architecture(spec["config"])
+    config = arch.config_class.from_dict(spec["config"])
+    plan = arch.plan(config)
+    model = DecoderModel(plan, runtime)
+    tensors = random_tensors(model.tensor_specs(), spec["seed"], std=spec["std"], vector_mean=spec["norm_mean"],
+                             vector_std=spec["norm_std"],
+                             dtype=torch.float32 if runtime.float32 else torch.bfloat16, device=runtime.device)
+    model.bind(tensors)
+    return config, plan, model, sum(t.numel() * t.element_size() for t in tensors.values())
+
+
 class Model:
-    def __init__(self, engine: Engine, model_dir: str, dtype: torch.dtype):
+    def __init__(self, engine: Engine, model_dir: Optional[str], dtype: torch.dtype, random: Optional[dict] = None):
         self.engine = engine
         self.model_dir = model_dir
         self.runtime = Runtime(engine.device, dtype)
-        self.config, self.plan, self.decoder, self.weight_bytes = build_model(model_dir, self.runtime)
+        if random is not None:
+            self.config, self.plan, self.decoder, self.weight_bytes = build_random_model(random, self.runtime)
+        else:
+            self.config, self.plan, self.decoder, self.weight_bytes = build_model(model_dir, self.runtime)
         # stored tensors no part asked for: skipped, as the reference skips unknown names
         # (crates/model-format/src/mlx/mod.rs:41-43)
         self.unexpected_tensors = self.decoder.unexpected_tensors
-        stops = set(self.plan.stop_token_ids) | set(read_generation_eos(model_dir))
+        stops = set(self.plan.stop_token_ids) | set(read_generation_eos(model_dir) if model_dir else ())
         self.stop_token_ids = tuple(sorted(stops))
 
     def memory(self, context: int, max_batch: int = 1) -> MemoryEstimate:

@@ -62,6 +62,16 @@ def validate_entries(entries: Sequence[StepEntry], vocab_size: int) -> None:
                 raise InvalidError(f"wanted place {p} is outside the {len(e.tokens)} tokens of the entry")
 
 
+def _tell_profiler(before: Sequence[int], counts: Sequence[int], phase: str = "") -> None:
+    """What the per-kernel timing cannot read off the kernels' arguments: how many cached tokens
+    the step's attention reads and how many (query, key) pairs its causal triangle has."""
+    from ..kernels import profile
+    if profile.enabled:
+        profile.hints["phase"] = phase
+        profile.hints["kv_tokens"] = float(sum(b + n for b, n in zip(before, counts)))
+        profile.hints["pairs"] = float(sum(n * b + n * (n + 1) // 2 for b, n in zip(before, counts)))
+
+
 def length_bucket(n: int) -> int:
     """Launch geometry of decode attention depends on the longest sequence only through this."""
     bucket = 256
@@ -137,7 +147,10 @@ class StepRunner:
         self.model, self.cache, self.runtime = model, cache, runtime
         self.poisoned = False
         self.steps_run = 0
-        self.use_graphs = use_graphs and runtime.device.type == "cuda" and model.graph_safe
+        from ..kernels import profile
+        # per-kernel timing (LRM_PROFILE=1) needs every launch to pass through its wrapper
+        self.use_graphs = (use_graphs and runtime.device.type == "cuda" and model.graph_safe
+                           and not profile.enabled)
         # captured decode steps by (batch size, length bucket), least recently used first; each
         # holds its own [batch, vocab] logits, so only the newest `max_graphs` are kept
         self._graphs: "OrderedDict[Tuple, _DecodeGraph]" = OrderedDict()
@@ -176,6 +189,7 @@ class StepRunner:
         cache.grow(growth)
         cache.sync()
         dest_rows = cache.destination_rows([e.slot for e in entries], before, [len(e.tokens) for e in entries])
+        _tell_profiler(before, [len(e.tokens) for e in entries], phase)
         try:
             if phase == "decode" and self.use_graphs:
                 logits = self._decode_with_graph(entries, before, borrow, dest_rows)
@@ -216,6 +230,7 @@ class StepRunner:
         cache.grow(growth)
         cache.sync()
         dest_rows = cache.destination_rows([e.slot for e in entries], before, [len(e.tokens) for e in entries])
+        _tell_profiler(before, [len(e.tokens) for e in entries], phase)
         try:
             ctx = pack_step(entries, before, self.runtime, phase, dest_rows)
             if phase == "decode":

@@ -151,4 +151,7 @@ def load() -> ctypes.CDLL:
             # let their successor start at once, large ones after their main loop (letting every
             # kernel do so at once made the whole step slower). LRM_PDL=0 switches it off.
             _library.lrm_set_pdl(0 if os.environ.get("LRM_PDL", "1") == "0" else 1)
+            from . import profile
+            if profile.enabled:  # LRM_PROFILE=1: every launch is timed (see profile.py)
+                _library = profile.ProfiledLibrary(_library)
         return _library

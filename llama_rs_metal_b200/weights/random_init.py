@@ -19,27 +19,33 @@ from .loader import TensorSpec
 from .safetensors_io import write_safetensors
 
 
-def _generator(seed: int, name: str) -> torch.Generator:
+def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
     digest = hashlib.sha256(f"{seed}:{name}".encode("utf-8")).digest()
-    return torch.Generator().manual_seed(int.from_bytes(digest[:8], "little") >> 1)
+    return torch.Generator(device=device).manual_seed(int.from_bytes(digest[:8], "little") >> 1)
 
 
 def random_tensors(wanted: Mapping[str, TensorSpec], seed: int, std: float = 0.02,
                    vector_mean: float = 1.0, vector_std: float = 0.0,
                    dtype: torch.dtype = torch.bfloat16,
-                   is_vector: Callable[[str, TensorSpec], bool] = None) -> Dict[str, torch.Tensor]:
-    """N(0, std) for matrices; N(vector_mean, vector_std) for 1-D scale vectors (norm weights)."""
+                   is_vector: Callable[[str, TensorSpec], bool] = None, device="cpu") -> Dict[str, torch.Tensor]:
+    """N(0, std) for matrices; N(vector_mean, vector_std) for 1-D scale vectors (norm weights).
+
+    With a CUDA `device` the numbers are drawn there (large models in seconds, no folder in
+    between); the device's generator draws other numbers than the CPU's for the same seed, so a
+    folder written on the CPU and a model drawn on the device are different random models."""
     out = {}
     for name, spec in wanted.items():
-        gen = _generator(seed, name)
+        gen = _generator(seed, name, device)
         vector = is_vector(name, spec) if is_vector else len(spec.shape) == 1
         if spec.kind == "integer":
-            out[name] = torch.zeros(spec.shape, dtype=torch.int32)
+            out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif vector:
-            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * vector_std + vector_mean
+            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device) * vector_std + vector_mean
             out[name] = t.to(dtype)
         else:
-            out[name] = (torch.randn(spec.shape, generator=gen, dtype=torch.float32) * std).to(dtype)
+            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
+            out[name] = t.mul_(std).to(dtype)
+            del t
     return out
 
 
