@@ -10,12 +10,16 @@ dispatch and prints a table, crates/metal-backend/src/apple/commands.rs:187-209)
 Under the flag decode steps are not captured in CUDA graphs and no kernel
 starts before its predecessor has finished (the events sit between them), so
 the times are those of each kernel alone; a whole step is faster than their
-sum. Bytes and flops are what the operation needs by its arguments (every
-operand once), not what the hardware moved.
+sum. A bracketed launch on an idle device also counts the launch's own
+start-up: the report measures that floor with an empty-handed kernel and
+prints it, and small kernels are to be read against it. Bytes and flops are
+what the operation needs by its arguments (every operand once), not what the
+hardware moved.
 """
 from __future__ import annotations
 
 import atexit
+import ctypes
 import os
 import sys
 from typing import Callable, Dict, List, Optional, Tuple
@@ -148,6 +152,26 @@ def table() -> List[dict]:
     return sorted(out, key=lambda r: -r["ms"])
 
 
+def launch_floor_us() -> float:
+    """What a bracketed launch of a kernel with nothing to do takes (median of 20)."""
+    from . import library
+    lib = getattr(library.load(), "_lib", library.load())
+    x = torch.zeros(1, dtype=torch.float32, device="cuda")
+    y = torch.zeros(1, dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.current_stream()
+    raw = ctypes.c_void_p(stream.cuda_stream)
+    pairs = []
+    for _ in range(20):
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        lib.lrm_cast(ctypes.c_void_p(x.data_ptr()), 0, ctypes.c_void_p(y.data_ptr()), 1, ctypes.c_longlong(1), raw)
+        end.record(stream)
+        pairs.append((begin, end))
+    torch.cuda.synchronize()
+    times = sorted(b.elapsed_time(e) for b, e in pairs)
+    return times[len(times) // 2] * 1e3
+
+
 def report(file=None) -> None:
     if not _rows:
         return
@@ -160,8 +184,8 @@ def report(file=None) -> None:
     for r in rows:
         print(f"{r['kernel'][4:]:34s} {r['phase']:8s} {r['calls']:7d} {r['ms']:9.3f} {r['ms'] / total:6.1%} {r['us_per_call']:9.2f} "
               f"{r['gb_per_s']:8.0f} {r['tflop_per_s']:8.1f} {r['frac_of_peak']:8.2f}", file=file)
-    print(f"{'total':34s} {'':8s} {sum(r['calls'] for r in rows):7d} {total:9.3f}   (each kernel alone; peaks: {source})",
-          file=file)
+    print(f"{'total':34s} {'':8s} {sum(r['calls'] for r in rows):7d} {total:9.3f}   (each kernel alone; peaks: {source}; "
+          f"a bracketed launch of an empty kernel takes {launch_floor_us():.1f} us)", file=file)
 
 
 if enabled:
