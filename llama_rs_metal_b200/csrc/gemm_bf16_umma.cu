@@ -201,6 +201,11 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   constexpr uint32_t A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t SET = MT * BN;                      // columns of one set of accumulators
   constexpr uint32_t NBUF = 2 * SET <= 512 ? 2 : 1;      // sets that fit in tensor memory
+  // tensor memory is handed out in powers of two of at least 32 columns (any other count is an
+  // illegal instruction)
+  constexpr uint32_t ALLOC = NBUF * SET <= 32 ? 32 : NBUF * SET <= 64 ? 64 : NBUF * SET <= 128 ? 128
+                             : NBUF * SET <= 256 ? 256 : 512;
+  static_assert(NBUF * SET <= 512, "accumulators do not fit in tensor memory");
   pdl_trigger();  // the next kernel may be scheduled as soon as an SM has room; it waits where it must
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   // operand ring first (1024-byte aligned for the swizzle), then barriers
@@ -232,7 +237,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, NBUF * SET);
+    tmem_alloc(tmem_slot, ALLOC);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -346,7 +351,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, NBUF * SET);
+  if (warp == 1) tmem_dealloc(tmem_base, ALLOC);
 }
 
 // ------------------------------------------------------------------------- host side
@@ -428,7 +433,9 @@ LRM_API int lrm_gemm_bf16_umma_supports(int M, int N, int K) {
 // writes a nonzero code there (the result is then invalid and the caller must raise).
 // `splits` > 1 cuts K into slices whose partial products go to the planes of an
 // [lrm_gemm_bf16_umma_slices(K, splits), M, N] float32 tensor (epilogue 4 only).
-// `tile`: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256 (rows x columns of the output per item).
+// `tile`: 0 = 128 x 128, 1 = 128 x 256, 2 = 256 x 256, 3 = 128 x 192 (rows x columns of the output
+// per item; the last one exists for products whose tiles would otherwise fill the SMs one and a
+// bit times over).
 // `x_rows` >= M: rows of X that may be read (the tensor map is built over them; rows from M on only
 // feed accumulator rows that are never stored). TMA was measured slower on maps of fewer than 32
 // rows, so a caller whose buffer holds 32 rows says so.
@@ -439,8 +446,9 @@ LRM_API int lrm_gemm_bf16_umma_rows(const void* X, const void* W, void* out, int
   if (mode < 0 || mode > 4 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
   if (splits < 1 || splits > 64 || (splits > 1 && mode != 4)) return LRM_BAD_ARGUMENT;
-  if (tile < 0 || tile > 2) return LRM_BAD_ARGUMENT;
+  if (tile < 0 || tile > 3) return LRM_BAD_ARGUMENT;
   if (x_rows < M) return LRM_BAD_ARGUMENT;
+  if (tile == 3) return launch_umma<192, 5>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
   if (tile == 2) return launch_umma<256, 3, 2>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
   if (tile == 1) return launch_umma<256, 4>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
   return launch_umma<128, 6>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);

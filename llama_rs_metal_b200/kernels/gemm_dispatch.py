@@ -25,7 +25,7 @@ from .ops import _done, _ptr, _stream  # noqa: PLC2701  (same package)
 
 SM_COUNT = 148
 force_tiled = False  # tests switch the fast kernels off to compare both paths
-umma_width: Optional[int] = None  # tests pin the tile: 128 (128 x 128), 256 (128 x 256), 512 (256 x 256)
+umma_width: Optional[int] = None  # tests pin the tile: 128 (128 x 128), 256 (128 x 256), 512 (256 x 256), 192 (128 x 192)
 
 _status: Dict[int, torch.Tensor] = {}
 _status_dirty = False
@@ -77,13 +77,14 @@ def check_status() -> None:
 def _tile_costs(K: int, mode: int):
     k_blocks = max(1, -(-K // 64))
     epilogue = 1.1 if mode == 3 else 0.55
-    return ((128, 128, 1.0), (128, 256, 1.4), (256, 256, 1.4 * (1.55 + epilogue * 32 / k_blocks)))
+    return ((128, 128, 1.0), (128, 256, 1.4), (256, 256, 1.4 * (1.55 + epilogue * 32 / k_blocks)), (128, 192, 1.2))
 
 
 def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0) -> int:
-    """0: 128 x 128, 1: 128 x 256, 2: 256 x 256 output tiles: least rounds over the SMs times cost."""
+    """0: 128 x 128, 1: 128 x 256, 2: 256 x 256, 3: 128 x 192 output tiles: least rounds over the SMs
+    times cost."""
     if umma_width is not None:
-        return {128: 0, 256: 1, 512: 2}[umma_width]
+        return {128: 0, 256: 1, 512: 2, 192: 3}[umma_width]
     best, best_cost = 0, None
     for index, (rows, columns, cost) in enumerate(_tile_costs(K, mode)):
         rounds = -(-(-(-M // rows) * -(-N // columns)) // SM_COUNT)

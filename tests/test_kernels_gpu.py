@@ -585,7 +585,7 @@ UMMA_SHAPES = [(65, 128, 64), (128, 128, 128), (129, 72, 8), (200, 300, 72), (33
                (2048, 512, 256), (70, 16, 2048), (256, 1100, 136), (700, 40000, 72)]
 
 
-@pytest.mark.parametrize("width", [128, 256, 512])
+@pytest.mark.parametrize("width", [128, 192, 256, 512])
 @pytest.mark.parametrize("M,N,K", UMMA_SHAPES)
 def test_linear_bfloat16_tensor_core_tiles(ops, monkeypatch, width, M, N, K):
     from llama_rs_metal_b200.kernels import gemm_dispatch
@@ -601,7 +601,7 @@ def test_linear_bfloat16_tensor_core_tiles(ops, monkeypatch, width, M, N, K):
     gemm_dispatch.check_status()
 
 
-@pytest.mark.parametrize("width", [128, 256, 512])
+@pytest.mark.parametrize("width", [128, 192, 256, 512])
 @pytest.mark.parametrize("M,I,K", [(70, 136, 64), (300, 520, 200), (128, 8, 16), (513, 20000, 64)])
 def test_linear_bfloat16_tensor_core_silu_gate(ops, monkeypatch, width, M, I, K):
     from llama_rs_metal_b200.kernels import gemm_dispatch
