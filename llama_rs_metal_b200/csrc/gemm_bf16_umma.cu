@@ -30,102 +30,13 @@
 // No cluster multicast is used anywhere.
 // (Reference role: the tiled simdgroup GEMM,
 // crates/metal-backend/src/shaders/matrix.metal:236-282.)
-#include <cuda.h>
-
-#include "common.cuh"
+#include "umma.cuh"
 
 namespace {
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Bounded wait. Returns false (and records `where`) if the barrier never completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
-    if (mbar_try_wait(bar, parity)) return true;
-  if (status != nullptr) atomicCAS(status, 0, where);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst, uint32_t columns) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)),
-               "r"(columns));
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t columns) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(columns));
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// K-major operand tile in shared memory, 128-byte swizzle: rows are 128 bytes apart, groups
-// of 8 rows 1024 bytes apart. Fields: start address >> 4 | leading offset (1) << 16 |
-// stride offset (1024 >> 4) << 32 | version 1 << 46 | SWIZZLE_128B (2) << 61.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-__device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
-      "%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(addr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
 
 // status codes (where a wait gave up)
 enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain = 4, kStuckTmemFree = 5 };
@@ -233,8 +144,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
       mbar_init(acc_free + a, 4);
     }
     *bail = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, ALLOC);
@@ -281,10 +191,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- issuer: one thread drives the tensor core
-      // instruction descriptor: D float32 (1 << 4), A and B bfloat16 (1 << 7, 1 << 10), both
-      // K-major, N >> 3 at bit 17, M >> 4 at bit 24
-      constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
-                                 (static_cast<uint32_t>(BM >> 4) << 24);
+      constexpr uint32_t idesc = umma_idesc(BM, BN);  // both operands K-major
       uint32_t it = 0, local = 0;
       for (int item = blockIdx.x; item < items && !*bail; item += gridDim.x, ++local) {
         const int kb_begin = (item / (m_tiles * n_tiles)) * kb_per_split;
@@ -355,44 +262,11 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
 }
 
 // ------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  static bool looked = false;
-  if (!looked) {
-    looked = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
-// Row-major [rows, K] bfloat16 matrix, boxes of `box_rows` x 64 elements, 128-byte swizzle,
-// out-of-range elements read as zero.
-bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_tiled();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-  const cuuint32_t box[2] = {BK, static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 template <int BN, int STAGES, int MT = 1>
 int launch_umma(const void* X, const void* W, void* out, int M, int x_rows, int N, int K, int mode, int splits,
                 int* status, cudaStream_t stream) {
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, X, x_rows, K, BM) || !make_map(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
+  if (!make_map_bf16(&map_x, X, x_rows, K, BM) || !make_map_bf16(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
   constexpr int smem = STAGES * (MT * BM * BK * 2 + BN * BK * 2) + 1024 + 256;
   auto kernel = gemm_bf16_umma_kernel<BN, STAGES, MT>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

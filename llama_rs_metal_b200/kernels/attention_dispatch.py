@@ -17,6 +17,7 @@ rotation, cache write and attention kernels for the step's phase and geometry.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -28,6 +29,7 @@ force_rowwise = False  # tests switch the tiled kernels off to compare both path
 force_warp_level = False  # tests keep prompts off the tcgen05 kernel to cover the warp-level one
 force_unfused_decode = False  # tests keep decode steps on the separate rotation / attention / merge kernels
 force_cluster_size = None  # tests fix the CTAs per cluster of the fused decode kernel
+prefill_pingpong = os.environ.get("LRM_PREFILL_ATTENTION", "2") != "1"  # two query tiles per CTA (1: the older kernel)
 
 
 def _tiled(q, page_size: int) -> bool:
@@ -43,6 +45,13 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
             and lib.lrm_attention_prefill_umma_supports(d)):
         from . import gemm_dispatch
         gemm_dispatch.mark_status_dirty()
+        if prefill_pingpong:
+            _done(lib.lrm_attention_prefill_pingpong(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), T,
+                                                     cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
+                                                     ctypes.c_float(scale), window,
+                                                     _ptr(gemm_dispatch._status_word(q.device)), _stream()),
+                  "attention_prefill_pingpong")
+            return
         _done(lib.lrm_attention_prefill_umma(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), T,
                                              cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
                                              ctypes.c_float(scale), window,

@@ -63,8 +63,11 @@ def check_status() -> None:
             word.zero_()
             names = {1: "a free stage", 2: "operand tiles", 3: "the accumulator", 4: "copies in flight",
                      5: "a free accumulator", 11: "the query tile", 12: "a key/value tile", 13: "scores",
-                     14: "probabilities", 15: "weighted values", 16: "a free key/value stage"}
-            kernel = "attention_prefill_umma" if code >= 11 else "gemm_bf16_umma"
+                     14: "probabilities", 15: "weighted values", 16: "a free key/value stage",
+                     17: "aligned shared memory", 21: "the query tiles", 22: "a key/value tile", 23: "scores",
+                     24: "probabilities", 25: "the output", 26: "a free key/value stage", 27: "aligned shared memory"}
+            kernel = "attention_prefill_pingpong" if code >= 21 else \
+                "attention_prefill_umma" if code >= 11 else "gemm_bf16_umma"
             raise LlamaError(f"{kernel} gave up waiting for {names.get(code, code)}; its result is invalid")
 
 
