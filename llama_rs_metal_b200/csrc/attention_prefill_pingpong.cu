@@ -1,7 +1,8 @@
 // Causal grouped-query flash attention for prompts on the 5th-generation tensor cores, with
-// two query tiles per CTA taking turns on the tensor core.
+// scores, probabilities and output in tensor memory and two query tiles taking turns on each
+// SM's tensor core.
 //
-// One CTA = 256 queries (two tiles of 128) of one head of one sequence; keys and values arrive
+// One CTA = one or two tiles of 128 queries of one head of one sequence; keys and values arrive
 // in tiles of 128 through TMA (cp.async.bulk.tensor, 128-byte swizzle, a ring of stages). For
 // query tile i and key tile j:
 //   S_i = Q_i K_j^T   tcgen05.mma, M 128 x N 128, K = head size, into tensor memory
@@ -12,12 +13,15 @@
 //   O_i += P_i V_j    tcgen05.mma with P read from tensor memory as the A operand and V from
 //                     shared memory as an MN-major operand exactly as TMA laid it down; O stays
 //                     in tensor memory for the whole row of key tiles
-// The issuing thread alternates between the tiles (P_0 V, the next S_0, P_1 V, the next S_1), so
-// one tile's softmax runs under the other tile's products. O is rescaled only when a row's
+// With two query tiles per CTA (head size 128: 256 queries, one CTA per SM) the issuing thread
+// alternates between the tiles (P_0 V, the next S_0, P_1 V, the next S_1), so one tile's softmax
+// runs under the other tile's products. With one tile per CTA (head size 64: its tiles leave room
+// for two CTAs per SM, in shared and in tensor memory) the two CTAs of an SM take turns the same
+// way, and short prompts get twice as many CTAs to spread over the SMs. O is rescaled only when a row's
 // maximum has moved by more than 2^8 since the scale O was last brought to (the row's own
 // thread multiplies its O row in tensor memory); P is formed against that older maximum
 // meanwhile and stays below 2^8, and the division by the mass at the end makes the result
-// exact regardless. Tensor memory: S_0 | S_1 | O_0 | O_1 = 128 + 128 + 2 D columns.
+// exact regardless. Tensor memory per query tile: S 128 + O D columns.
 //
 // Rows and keys outside a sequence are zero-filled by TMA or belong to a neighbouring sequence
 // of the packed batch; the causal mask hides such keys and such rows are never stored.
@@ -29,21 +33,23 @@
 namespace {
 
 constexpr int BQ = 128, BKV = 128, UMMA_K = 16;
-constexpr int kSoftmaxWarps = 8;                           // four per query tile
-constexpr int kLoaderWarp = 8, kIssuerWarp = 9;
-constexpr int kThreadsPerCta = 10 * 32;
+// warps of a CTA with NQ query tiles: four softmax warps per tile, then the loader, then the issuer
+constexpr int threads_per_cta(int nq) { return (4 * nq + 2) * 32; }
 constexpr float kRescaleStep = 8.0f;                       // log2: O is rescaled when the maximum moved this far
 
 enum : int { kStuckQ = 21, kStuckKV = 22, kStuckScores = 23, kStuckProbabilities = 24, kStuckOutput = 25,
              kStuckStage = 26, kMisaligned = 27 };
 
-template <int D> struct Ring { static constexpr int kStages = D == 64 ? 3 : 2; };
+// Key/value stages by head size (with head size 64 and one query tile two CTAs fit on an SM).
+template <int D> struct Shape {
+  static constexpr int kStages = D == 64 ? 3 : 2;
+};
 
 // Shared memory (1024-byte aligned): Q [2][128][D] | stages of (K [128][D] | V [128][D]) |
 // barriers. A [128][D] tile with D = 128 is two [128][64] blocks of 16 KB one after the other
 // (a swizzle row is 128 bytes = 64 elements).
-template <int D>
-__global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_kernel(
+template <int D, int NQ>
+__global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attention_prefill_pingpong_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window,
@@ -51,14 +57,15 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
   constexpr uint32_t TILE = BQ * D * 2;       // bytes of one [128][D] tile
   constexpr uint32_t BLOCK = BQ * 64 * 2;     // bytes of one [128][64] block
   constexpr int DB = D / 64;                  // 64-column blocks per tile
-  constexpr int STAGES = Ring<D>::kStages;
+  constexpr int STAGES = Shape<D>::kStages;
+  constexpr int kLoaderWarp = 4 * NQ, kIssuerWarp = 4 * NQ + 1;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need it; give up rather than compute nonsense
     if (threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, kMisaligned);
     return;
   }
-  unsigned char* q_tiles = smem_raw;                        // [2] tiles
-  unsigned char* kv_tiles = q_tiles + 2 * TILE;             // stage s: K at s * 2 * TILE, V right after
+  unsigned char* q_tiles = smem_raw;                        // [NQ] tiles
+  unsigned char* kv_tiles = q_tiles + NQ * TILE;            // stage s: K at s * 2 * TILE, V right after
   uint64_t* bars = reinterpret_cast<uint64_t*>(kv_tiles + STAGES * 2 * TILE);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;               // [STAGES]
@@ -74,14 +81,14 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
   const int pair = gridDim.z - 1 - blockIdx.z;
   const int h = blockIdx.x, b = blockIdx.y;
   const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
-  const int q0 = pair * 2 * BQ;
+  const int q0 = pair * NQ * BQ;
   if (q0 >= len) return;
   const int kh = h / (q_heads / kv_heads);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt_first = window > 0 ? max(0, q0 - window + 1) / BKV : 0;
   // key tiles per query tile: up to its diagonal tile; the second tile may not exist
   const int n0 = q0 / BKV - kt_first + 1;
-  const int n1 = q0 + BQ < len ? n0 + 1 : 0;
+  const int n1 = NQ == 2 && q0 + BQ < len ? n0 + 1 : 0;
   const int n_tiles = max(n0, n1);
 
   if (threadIdx.x == 0) {
@@ -98,7 +105,7 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
     *bail = 0;
     mbar_fence_init();
   }
-  constexpr uint32_t kTmemColumns = 512;
+  constexpr uint32_t kTmemColumns = NQ == 2 ? 512 : 256;  // a power of two that holds NQ (128 + D) columns
   if (warp == kIssuerWarp) {
     tmem_alloc(tmem_slot, kTmemColumns);
     tmem_relinquish();
@@ -108,7 +115,7 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tmem_o[2] = {tmem_base + 256, tmem_base + 256 + D};
+  const uint32_t tmem_o[2] = {tmem_base + NQ * 128, tmem_base + NQ * 128 + D};
 
   if (warp == kLoaderWarp) {
     if (lane == 0) {
@@ -210,28 +217,31 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
       const int key0 = (kt_first + j) * BKV;
       const int first_row = q0 + i * BQ;
       const bool edge = key0 + BKV - 1 > first_row || (window > 0 && key0 <= first_row + BQ - 1 - window);
-      // the whole row of scores comes into registers at once (four loads in flight, one wait)
-      uint32_t sc[4][32];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_load32_async(my_s + c * 32, sc[c]);
-      tmem_load_wait();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_pin(sc[c]);
-      // the row's maximum over this tile (only tiles on the diagonal or the window's edge need the mask)
+      // pass 1: the row's maximum over this tile; the whole row comes into registers at once (four
+      // loads in flight, one wait) and is dropped again (only tiles on the diagonal or the window's
+      // edge need the mask)
       float mx = -INFINITY;
-      if (edge) {
+      {
+        uint32_t sc[4][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c) tmem_load32_async(my_s + c * 32, sc[c]);
+        tmem_load_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int key = key0 + c * 32 + e;
-            if (key <= row && (window <= 0 || key > row - window)) mx = fmaxf(mx, __uint_as_float(sc[c][e]));
-          }
-      } else {
+        for (int c = 0; c < 4; ++c) tmem_pin(sc[c]);
+        if (edge) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sc[c][e]));
+            for (int e = 0; e < 32; ++e) {
+              const int key = key0 + c * 32 + e;
+              if (key <= row && (window <= 0 || key > row - window)) mx = fmaxf(mx, __uint_as_float(sc[c][e]));
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sc[c][e]));
+        }
       }
       m_run = fmaxf(m_run, mx * scale_log2);
       // bring O and the mass to the new maximum only when it has moved far (always for the first
@@ -254,11 +264,17 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
         if (far) m_ref = m_run;
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;  // a row that has seen no key yet
-      // probabilities against m_ref, rounded to bfloat16, written over the scores they came from:
-      // keys 32 c .. 32 c + 31 become columns 16 c .. 16 c + 15
+      // pass 2: probabilities against m_ref, rounded to bfloat16, written over the scores they came
+      // from: keys 32 c .. 32 c + 31 become columns 16 c .. 16 c + 15 (read by then). The next
+      // chunk of scores is on its way while this one is worked on.
       float sum = 0.f;
+      uint32_t sc[2][32];
+      tmem_load32_async(my_s, sc[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        tmem_load_wait();
+        tmem_pin(sc[c & 1]);
+        if (c + 1 < 4) tmem_load32_async(my_s + (c + 1) * 32, sc[(c + 1) & 1]);
         uint32_t packed[16];
         if (edge) {
 #pragma unroll
@@ -266,16 +282,16 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
             const int key = key0 + c * 32 + e;
             const bool v0 = key <= row && (window <= 0 || key > row - window);
             const bool v1 = key + 1 <= row && (window <= 0 || key + 1 > row - window);
-            const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(sc[c][e]), scale_log2, -m_use)) : 0.f;
-            const float p1 = v1 ? fast_exp2(fmaf(__uint_as_float(sc[c][e + 1]), scale_log2, -m_use)) : 0.f;
+            const float p0 = v0 ? fast_exp2(fmaf(__uint_as_float(sc[c & 1][e]), scale_log2, -m_use)) : 0.f;
+            const float p1 = v1 ? fast_exp2(fmaf(__uint_as_float(sc[c & 1][e + 1]), scale_log2, -m_use)) : 0.f;
             sum += p0 + p1;
             packed[e >> 1] = pack_bf16(p0, p1);
           }
         } else {
 #pragma unroll
           for (int e = 0; e < 32; e += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sc[c][e]), scale_log2, -m_use));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sc[c][e + 1]), scale_log2, -m_use));
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sc[c & 1][e]), scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sc[c & 1][e + 1]), scale_log2, -m_use));
             sum += p0 + p1;
             packed[e >> 1] = pack_bf16(p0, p1);
           }
@@ -320,7 +336,7 @@ __global__ __launch_bounds__(kThreadsPerCta, 1) void attention_prefill_pingpong_
   if (warp == kIssuerWarp) tmem_dealloc(tmem_base, kTmemColumns);
 }
 
-template <int D>
+template <int D, int NQ>
 int launch(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens, int tokens,
            int seqs, int max_seq_len, int q_heads, int kv_heads, float scale, int window, int* status,
            cudaStream_t stream) {
@@ -329,14 +345,14 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
       !make_map_bf16(&map_k, k, tokens, static_cast<long long>(kv_heads) * D, BKV) ||
       !make_map_bf16(&map_v, v, tokens, static_cast<long long>(kv_heads) * D, BKV))
     return LRM_UNSUPPORTED;
-  constexpr int smem = (2 + 2 * Ring<D>::kStages) * BQ * D * 2 + 256;
-  auto kernel = attention_prefill_pingpong_kernel<D>;
+  constexpr int smem = (NQ + 2 * Shape<D>::kStages) * BQ * D * 2 + 256;
+  auto kernel = attention_prefill_pingpong_kernel<D, NQ>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
-  const int pairs = (max_seq_len + 2 * BQ - 1) / (2 * BQ);
+  const int pairs = (max_seq_len + NQ * BQ - 1) / (NQ * BQ);
   if (seqs > 65535 || pairs > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(q_heads, seqs, pairs);
-  kernel<<<grid, kThreadsPerCta, smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
+  kernel<<<grid, threads_per_cta(NQ), smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
                                                  q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
   LRM_LAUNCH_CHECK();
   return 0;
@@ -360,11 +376,14 @@ LRM_API int lrm_attention_prefill_pingpong(const void* q, const void* k, const v
   if (reinterpret_cast<uintptr_t>(q) % 16 || reinterpret_cast<uintptr_t>(k) % 16 ||
       reinterpret_cast<uintptr_t>(v) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
     return LRM_UNSUPPORTED;
+  // Two query tiles per CTA where the head is wide (the tensor core then has work to hide a tile's
+  // softmax under); with head size 64 one tile per CTA and two CTAs per SM (measured: the other
+  // two combinations are slower at every length).
   if (d == 64)
-    return launch<64>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
-                      status, stream);
+    return launch<64, 1>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
+                         status, stream);
   if (d == 128)
-    return launch<128>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
-                       status, stream);
+    return launch<128, 2>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
+                          status, stream);
   return LRM_UNSUPPORTED;
 }

@@ -19,110 +19,14 @@
 // Every mbarrier wait is bounded; a wait that gives up records a code in `status`, and the CTA
 // winds down and frees its tensor memory. No cluster multicast.
 // (Reference: crates/metal-backend/src/shaders/attention.metal:28-57, the streaming softmax.)
-#include <cuda.h>
-
-#include "common.cuh"
+#include "umma.cuh"
 
 namespace {
 
 constexpr int BQ = 128, BKV = 128, UMMA_K = 16;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int where) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
-    if (mbar_try_wait(bar, parity)) return true;
-  if (status != nullptr) atomicCAS(status, 0, where);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Shared-memory operand descriptor, 128-byte swizzle: start address >> 4 | leading byte offset
-// >> 4 at bit 16 | stride byte offset >> 4 at bit 32 | version 1 at bit 46 | SWIZZLE_128B at 61.
-// K-major tile (rows of 128 bytes along K): leading offset unused (1), stride 1024 (8 rows).
-// MN-major tile (rows of 128 bytes along N, one row per k): leading offset = distance between
-// 64-element blocks along N, stride 1024 (8 k).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t leading_bytes) {
-  return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(leading_bytes >> 4) << 16) |
-         (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ void tmem_load32(uint32_t addr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,"
-      "%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
-        "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
-        "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
-        "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(addr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_store1(uint32_t addr, uint32_t value) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(addr), "r"(value) : "memory");
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t tmem_load1(uint32_t addr) {
-  uint32_t value;
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(value) : "r"(addr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-  return value;
-}
 __device__ __forceinline__ void pair_barrier(int id) {  // the two warps that share a row quadrant
   asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
-}
-// 2^x on the special-function unit (2 ulp; the probabilities are rounded to bfloat16 anyway)
-__device__ __forceinline__ float fast_exp2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 constexpr int kSoftmaxWarps = 8;   // two per 32 query rows: each takes half of a tile's keys
@@ -188,14 +92,12 @@ __global__ __launch_bounds__(kThreadsPerCta, D == 64 ? 2 : 1) void attention_pre
     mbar_init(pv_full, 1);
     *bail = 0;
     for (int i = 0; i < 8; ++i) pair_fail[i] = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_fence_init();
   }
   constexpr uint32_t kTmemColumns = D == 64 ? 256u : 512u;  // scores 128 | weighted values D | 2 to exchange
   if (warp == kSoftmaxWarps) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(kTmemColumns));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    tmem_alloc(tmem_slot, kTmemColumns);
+    tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
@@ -407,37 +309,7 @@ __global__ __launch_bounds__(kThreadsPerCta, D == 64 ? 2 : 1) void attention_pre
   tc_fence_before();
   __syncthreads();
   if (warp == kSoftmaxWarps)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_s), "r"(kTmemColumns));
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  static bool looked = false;
-  if (!looked) {
-    looked = true;
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-// [tokens, heads * d] bfloat16, boxes of 128 tokens x 64 columns, 128-byte swizzle, zero fill.
-bool make_map(CUtensorMap* map, const void* base, int tokens, int width) {
-  EncodeTiledFn fn = encode_tiled();
-  if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(tokens)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(width) * 2};
-  const cuuint32_t box[2] = {64, 128};
-  const cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    tmem_dealloc(tmem_s, kTmemColumns);
 }
 
 template <int D>
@@ -445,8 +317,9 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
            int seqs, int max_seq_len, int q_heads, int kv_heads, float scale, int window, int* status,
            cudaStream_t stream) {
   CUtensorMap map_q, map_k, map_v;
-  if (!make_map(&map_q, q, tokens, q_heads * D) || !make_map(&map_k, k, tokens, kv_heads * D) ||
-      !make_map(&map_v, v, tokens, kv_heads * D))
+  if (!make_map_bf16(&map_q, q, tokens, static_cast<long long>(q_heads) * D, BQ) ||
+      !make_map_bf16(&map_k, k, tokens, static_cast<long long>(kv_heads) * D, BKV) ||
+      !make_map_bf16(&map_v, v, tokens, static_cast<long long>(kv_heads) * D, BKV))
     return LRM_UNSUPPORTED;
   constexpr int smem = 5 * BQ * D * 2 + 2 * BQ * 64 * 2 + 256;
   auto kernel = attention_prefill_umma_kernel<D>;

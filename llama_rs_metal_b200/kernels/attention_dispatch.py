@@ -29,7 +29,7 @@ force_rowwise = False  # tests switch the tiled kernels off to compare both path
 force_warp_level = False  # tests keep prompts off the tcgen05 kernel to cover the warp-level one
 force_unfused_decode = False  # tests keep decode steps on the separate rotation / attention / merge kernels
 force_cluster_size = None  # tests fix the CTAs per cluster of the fused decode kernel
-prefill_pingpong = os.environ.get("LRM_PREFILL_ATTENTION", "2") != "1"  # two query tiles per CTA (1: the older kernel)
+prefill_kernel = None  # tests pin the tcgen05 prompt kernel: "pingpong" or "single" (None: the rule in prefill())
 
 
 def _tiled(q, page_size: int) -> bool:
@@ -45,7 +45,16 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
             and lib.lrm_attention_prefill_umma_supports(d)):
         from . import gemm_dispatch
         gemm_dispatch.mark_status_dirty()
-        if prefill_pingpong:
+        # Two tcgen05 kernels. The one that keeps probabilities and output in tensor memory and lets
+        # two query tiles take turns wins on long prompts (measured at 32 heads: head size 128 from
+        # 2,048 tokens on, 66 against 90 us, 1,023 against 585 TFLOP/s at 32,768; head size 64 from
+        # 4,096 on, 585 against 530 TFLOP/s at 32,768); the older one, with twice the threads per
+        # row and more, smaller CTAs, on short ones.
+        longest = max_seq_len
+        pingpong = longest >= (1536 if d == 128 else 3072)
+        if prefill_kernel is not None:
+            pingpong = prefill_kernel == "pingpong"
+        if pingpong:
             _done(lib.lrm_attention_prefill_pingpong(_ptr(q), _ptr(k), _ptr(v), _ptr(out), _ptr(cu_seqlens), T,
                                                      cu_seqlens.numel() - 1, max_seq_len, Hq, k.shape[1], d,
                                                      ctypes.c_float(scale), window,

@@ -52,8 +52,10 @@ def test_one_launch_or_three():
 
 
 def test_tile_shape_of_prompt_products():
-    choice = gemm_dispatch.tile_choice              # 0: 128 x 128, 1: 128 x 256, 2: 256 x 256
-    assert choice(2048, 16384, 2048, 3) == 1 and choice(2048, 3072, 2048, 0) == 1
+    choice = gemm_dispatch.tile_choice              # 0: 128 x 128, 1: 128 x 256, 2: 256 x 256, 3: 128 x 192
+    assert choice(2048, 16384, 2048, 3) == 1
+    assert choice(2048, 3072, 2048, 0) == 3         # 192 tiles of 128 x 256 would fill 148 SMs 1.3 times: 256 of 128 x 192 do better
+    assert choice(4096, 3072, 2048, 0) == 1
     assert choice(2048, 2048, 8192, 2) == 1         # 64 large tiles would leave most SMs idle
     assert choice(8192, 2048, 8192, 2) == 2         # long K: the 256 x 256 tile pays
     assert choice(8192, 16384, 2048, 3) == 1        # short K and a costly epilogue: it does not

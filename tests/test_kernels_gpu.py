@@ -91,11 +91,17 @@ def test_linear_float32_row_does_not_depend_on_the_batch(ops):
         assert torch.equal(ops.linear(x[r:r + 1].contiguous(), w)[0], full[r])
 
 
-@pytest.fixture(params=["fast kernels", "warp-level attention", "fallback kernels"])
+@pytest.fixture(params=["fast kernels", "prompt attention in tensor memory", "warp-level attention",
+                        "fallback kernels"])
 def kernel_choice(request, monkeypatch):
-    """Run a test with the kernels the dispatchers pick, with prompts kept off the tcgen05
-    attention, and with every fallback forced."""
+    """Run a test with the kernels the dispatchers pick for short prompts, with the tcgen05 prompt
+    attention that long prompts get, with prompts kept off the tcgen05 attention, and with every
+    fallback forced."""
     from llama_rs_metal_b200.kernels import attention_dispatch, gemm_dispatch
+    if request.param == "fast kernels":
+        monkeypatch.setattr(attention_dispatch, "prefill_kernel", "single")
+    if request.param == "prompt attention in tensor memory":
+        monkeypatch.setattr(attention_dispatch, "prefill_kernel", "pingpong")
     if request.param == "fallback kernels":
         monkeypatch.setattr(gemm_dispatch, "force_tiled", True)
         monkeypatch.setattr(attention_dispatch, "force_rowwise", True)
