@@ -137,7 +137,9 @@ static int launch_norm(float* x, const void* w, void* out, const int* rows, cons
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   if (hidden % 4 == 0 && aligned(x) && aligned(w) && aligned(out) && aligned(partials)) {
     const int groups = hidden / 4;
-    const int vthreads = groups >= 1024 ? 1024 : (groups >= 512 ? 256 : (groups >= 64 ? 128 : 32));
+    // up to eight groups of four per thread: 256 threads reach rows of 8,192 elements (a block of
+    // 1,024 threads per row was measured at a third of the memory rate at 4,096 elements)
+    const int vthreads = groups > 2048 ? 1024 : (groups >= 512 ? 256 : (groups >= 64 ? 128 : 32));
     const int per4 = (groups + vthreads - 1) / vthreads;
 #define LRM_NORM_VEC(P4)                                                                               \
   return static_cast<int>(lrm_launch(rms_norm_vec_kernel<W, O, P4>, n_rows, vthreads, 0, stream, x,   \
