@@ -190,7 +190,8 @@ def plain_cpu_point(engine):
         cpu = len(prompts) * steps / (time.perf_counter() - started)
         session = engine.load(folder, dtype="float32").session(context=128, max_batch=3)
         options = GenerationOptions(max_tokens=steps, sampling=Sampling(temperature=0.0))
-        session.generate(prompts, options, stop_token_ids=())
+        for _ in range(2):  # warm-up: the prompt step's graph is captured the second time its shape comes
+            session.generate(prompts, options, stop_token_ids=())
         started = time.perf_counter()
         got = session.generate(prompts, options, stop_token_ids=())
         gpu = len(prompts) * steps / (time.perf_counter() - started)
@@ -396,6 +397,8 @@ def main() -> int:
             run = time_decode(batch, max(16, steps // 2), 4)
             points[f"decode_b{batch}"] = round(run["tokens_per_s"], 1)
             points[f"decode_b{batch}_hbm_frac"] = round(run["bytes"] / (run["ms"] * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+        for tokens in (128, 512):  # short prompts: what one request waits for before its first token
+            points[f"prefill_{tokens}_ms"] = round(time_prefill(tokens), 3)
         points.update(plain_cpu_point(engine))
         line["points"] = points
     print(json.dumps(line))

@@ -69,21 +69,38 @@ class StepContext:
         return residual
 
 
-def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_rows=()):
+def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_rows=(), pad_to: int = 0):
     """The step's int32 arrays in one host buffer, laid out as
     [token ids T | positions T | sequence of token T | cu_seqlens B+1 | slots B | kv lengths B |
-     wanted rows n | destination rows T per key/value group]."""
+     wanted rows n | destination rows T per key/value group].
+
+    With `pad_to` > the step's tokens (a prompt step only) the step is filled up to that many
+    rows with a sequence of padding of its own: token 0 at positions 0, 1, ..., stored nowhere
+    (destination -1), in no slot (-1), wanted by nobody. T and B then count it, so that steps of
+    different sizes share one launch geometry; rows do not depend on one another, so padding
+    changes no result."""
     counts = [len(e.tokens) for e in entries]
-    T, B = sum(counts), len(entries)
+    real_T, real_B = sum(counts), len(entries)
+    padding = max(0, pad_to - real_T)
+    T, B = real_T + padding, real_B + (1 if padding else 0)
     n_want = sum(len(e.want) for e in entries)
     base = 3 * T + (B + 1) + 2 * B + n_want
     host = np.empty(base + T * len(dest_rows), dtype=np.int32)
     for g, rows in enumerate(dest_rows):
-        host[base + g * T:base + (g + 1) * T] = rows
+        host[base + g * T:base + g * T + real_T] = rows
+        host[base + g * T + real_T:base + (g + 1) * T] = -1
     token_ids, positions, seq_of = host[:T], host[T:2 * T], host[2 * T:3 * T]
     o = 3 * T
     cu, slots, kv_lens, wanted = host[o:o + B + 1], host[o + B + 1:o + 2 * B + 1], \
         host[o + 2 * B + 1:o + 3 * B + 1], host[o + 3 * B + 1:base]
+    if padding:
+        token_ids[real_T:] = 0
+        positions[real_T:] = np.arange(padding, dtype=np.int32)
+        seq_of[real_T:] = real_B
+        cu[B] = T
+        slots[real_B] = -1
+        kv_lens[real_B] = padding
+        counts = counts + [padding]
     at, w = 0, 0
     cu[0] = 0
     for b, (e, before) in enumerate(zip(entries, lengths_before)):
@@ -116,9 +133,9 @@ def context_over(dev: torch.Tensor, runtime: Runtime, phase: str, T: int, B: int
 
 
 def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runtime: Runtime,
-              phase: str, dest_rows=()) -> StepContext:
+              phase: str, dest_rows=(), pad_to: int = 0) -> StepContext:
     """Build the packed int32 arrays on the host and copy them to the device in one transfer."""
-    host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, lengths_before, dest_rows)
+    host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, lengths_before, dest_rows, pad_to)
     device = runtime.device
     if device.type == "cuda":
         dev = torch.from_numpy(host).pin_memory().to(device, non_blocking=True)

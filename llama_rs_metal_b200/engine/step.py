@@ -31,7 +31,7 @@ from ..cache import Cache
 from ..errors import InvalidError, PoisonedError, UnsupportedError
 from ..kernels import ops
 from ..runtime import Runtime
-from .batch import StepEntry, context_over, pack_host, pack_step
+from .batch import StepEntry, context_over, pack_host
 from .model import DecoderModel
 
 
@@ -80,24 +80,27 @@ def length_bucket(n: int) -> int:
     return bucket
 
 
-class _DecodeGraph:
-    """One captured decode step: static inputs, the graph, and what it leaves: float32 logits
-    [B, vocab] with their greedy choice, or (for a caller that only wants tokens, `choice` =
-    (temperature or None, seed)) just the chosen ids, picked in the head product's epilogue."""
+class _StepGraph:
+    """One captured step of a fixed geometry: static inputs, the graph, and what it leaves: float32
+    logits [wanted, vocab] with their greedy choice, or (for a caller that only wants tokens,
+    `choice` = (temperature or None, seed)) just the chosen ids, picked in the head product's
+    epilogue where a kernel can. A decode step has one token and one wanted row per sequence; a
+    short prompt step is filled up to a whole number of 64 rows (see pack_host)."""
 
     RING = 4
 
-    def __init__(self, runner: "StepRunner", batch: int, bucket: int, choice=None):
+    def __init__(self, runner: "StepRunner", phase: str, tokens: int, seqs: int, wanted: int, max_seq_len: int,
+                 max_kv_len: int, choice=None):
         rt = runner.runtime
-        self.batch, self.choice = batch, choice
+        self.batch, self.choice = seqs, choice
         groups = len(runner.cache.kv_groups)
-        self.size = (7 + groups) * batch + 1  # pack_host's layout with T = B and every row wanted
-        # behind it, 8-byte aligned: one int64 key per row for the noise of temperature sampling
+        self.size = (3 + groups) * tokens + 3 * seqs + 1 + wanted  # pack_host's layout
+        # behind it, 8-byte aligned: one int64 key per wanted row for the noise of temperature sampling
         self.keys_at = self.size + (self.size & 1)
-        total = self.keys_at + 2 * batch
+        total = self.keys_at + 2 * max(wanted, 1)
         self.static = torch.zeros(total, dtype=torch.int32, device=rt.device)
-        self.keys = self.static[self.keys_at:].view(torch.int64)
-        self.ctx = context_over(self.static, rt, "decode", batch, batch, batch, 1, bucket, groups)
+        self.keys = self.static[self.keys_at:self.keys_at + 2 * wanted].view(torch.int64)
+        self.ctx = context_over(self.static, rt, phase, tokens, seqs, wanted, max_seq_len, max_kv_len, groups)
         self.pinned = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.ids: Optional[torch.Tensor] = None  # int32 [B]: the chosen tokens (graphs with a `choice`)
         self.events = [torch.cuda.Event() for _ in range(self.RING)]
@@ -115,7 +118,7 @@ class _DecodeGraph:
         staged = self.pinned[i].numpy()
         staged[:self.size] = host
         if keys is not None:
-            staged[self.keys_at:].view(np.int64)[:] = keys
+            staged[self.keys_at:self.keys_at + 2 * len(keys)].view(np.int64)[:] = keys
         self.static.copy_(self.pinned[i], non_blocking=True)
         self.events[i].record()
 
@@ -153,8 +156,14 @@ class StepRunner:
                            and not profile.enabled)
         # captured decode steps by (batch size, length bucket), least recently used first; each
         # holds its own [batch, vocab] logits, so only the newest `max_graphs` are kept
-        self._graphs: "OrderedDict[Tuple, _DecodeGraph]" = OrderedDict()
-        self.max_graphs = 24
+        self._graphs: "OrderedDict[Tuple, _StepGraph]" = OrderedDict()
+        self.max_graphs = 32
+        # Short prompt steps are filled up to whole 64 rows (with or without graphs, so that both ways
+        # launch the same kernels on the same shapes): steps of a few hundred tokens are bound by the
+        # host's time per launch, and a geometry seen for the second time is captured and replayed.
+        # Only for models whose parts never look at the step's arrays on the host.
+        self.pads_prompts = model.graph_safe
+        self._prompt_shapes_seen = set()
         self._pool = None
         self.last_launches = 0  # kernels of this library launched by the last step
         # pinned buffers for the ids of steps that do not wait (two are in flight at most)
@@ -178,34 +187,7 @@ class StepRunner:
             logits = self._decode_vectorized(entries, borrow)
             if logits is not None:
                 return logits
-        validate_entries(entries, self.model.plan.vocab_size)
-        before = [cache.length(e.slot) for e in entries]
-        phase = classify_step(entries, before)
-        if phase == "prefill":  # attention reads the step's own keys: the cache keeps what later steps see
-            growth = [(e.slot, n + len(e.tokens)) for e, n in zip(entries, before)]
-        else:                   # attention reads the cache from each portion's first query on
-            growth = [(e.slot, n + len(e.tokens), n) for e, n in zip(entries, before)]
-        cache.check_growth(growth)  # raises before anything changes
-        cache.grow(growth)
-        cache.sync()
-        dest_rows = cache.destination_rows([e.slot for e in entries], before, [len(e.tokens) for e in entries])
-        _tell_profiler(before, [len(e.tokens) for e in entries], phase)
-        try:
-            if phase == "decode" and self.use_graphs:
-                logits = self._decode_with_graph(entries, before, borrow, dest_rows)
-            else:
-                ctx = pack_step(entries, before, self.runtime, phase, dest_rows)
-                if phase == "decode":  # the geometry a captured step would have
-                    ctx.max_kv_len = length_bucket(ctx.max_kv_len)
-                start = ops.launch_count()
-                logits = self.model.forward(ctx, cache)
-                self.last_launches = ops.launch_count() - start
-        except Exception:
-            self.poisoned = True
-            raise
-        cache.commit(growth)
-        self.steps_run += 1
-        return logits
+        return self._run(entries, None, borrow)
 
     def step_pick(self, entries: Sequence[StepEntry], picker) -> List[int]:
         """A step for a caller that wants tokens, not logits: runs the entries like step() and
@@ -221,36 +203,80 @@ class StepRunner:
                 and all(cache.open_mask[e.slot] and cache.lengths[e.slot] > 0 for e in entries
                         if 0 <= e.slot < cache.max_slots)):
             return self.decode_ahead([e.slot for e in entries], [e.tokens[0] for e in entries], None, picker).ids()
+        return self._run(entries, picker, True).tolist()
+
+    PROMPT_PAD_LIMIT = 1024  # prompt steps of up to this many tokens are filled up to whole 64 rows
+
+    def _run(self, entries: List[StepEntry], picker, borrow: bool) -> torch.Tensor:
+        """The general path of step() (picker None: logits) and step_pick() (chosen ids)."""
+        cache = self.cache
         validate_entries(entries, self.model.plan.vocab_size)
         before = [cache.length(e.slot) for e in entries]
         phase = classify_step(entries, before)
-        growth = [(e.slot, n + len(e.tokens)) if phase == "prefill" else (e.slot, n + len(e.tokens), n)
-                  for e, n in zip(entries, before)]
-        cache.check_growth(growth)
+        counts = [len(e.tokens) for e in entries]
+        if phase == "prefill":  # attention reads the step's own keys: the cache keeps what later steps see
+            growth = [(e.slot, n + c) for e, n, c in zip(entries, before, counts)]
+        else:                   # attention reads the cache from each portion's first query on
+            growth = [(e.slot, n + c, n) for e, n, c in zip(entries, before, counts)]
+        cache.check_growth(growth)  # raises before anything changes
         cache.grow(growth)
         cache.sync()
-        dest_rows = cache.destination_rows([e.slot for e in entries], before, [len(e.tokens) for e in entries])
-        _tell_profiler(before, [len(e.tokens) for e in entries], phase)
+        dest_rows = cache.destination_rows([e.slot for e in entries], before, counts)
+        _tell_profiler(before, counts, phase)
         try:
-            ctx = pack_step(entries, before, self.runtime, phase, dest_rows)
-            if phase == "decode":
-                ctx.max_kv_len = length_bucket(ctx.max_kv_len)
-            keys = None
-            if picker.temperature is not None:
-                if len(picker.keys) != ctx.wanted_rows.numel():
-                    raise InvalidError("one sampling key per wanted place")
-                keys = torch.tensor(picker.keys, dtype=torch.int64).pin_memory().to(self.runtime.device,
-                                                                                      non_blocking=True)
-            start = ops.launch_count()
-            ids = self.model.forward_pick(ctx, cache, picker.temperature, picker.seed, keys)
-            self.last_launches = ops.launch_count() - start
-            host = ids.tolist()
+            if phase == "decode" and self.use_graphs and picker is None:
+                result = self._decode_with_graph(entries, before, borrow, dest_rows)
+            else:
+                result = self._run_packed(entries, before, counts, phase, dest_rows, picker, borrow)
         except Exception:
             self.poisoned = True
             raise
         cache.commit(growth)
         self.steps_run += 1
-        return host
+        return result
+
+    def _run_packed(self, entries, before, counts, phase: str, dest_rows, picker, borrow: bool) -> torch.Tensor:
+        rt = self.runtime
+        pad_to = 0
+        if phase == "prefill" and self.pads_prompts and sum(counts) <= self.PROMPT_PAD_LIMIT:
+            pad_to = -(-sum(counts) // 64) * 64
+        host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, before, dest_rows, pad_to)
+        if pad_to:  # the geometry of every step that fills the same rows
+            max_seq_len = max_kv_len = -(-max_seq_len // 64) * 64
+        if phase == "decode":  # the geometry a captured step would have
+            max_kv_len = length_bucket(max_kv_len)
+        choice, keys = None, None
+        if picker is not None:
+            choice = (picker.temperature, picker.seed)
+            if picker.temperature is not None:
+                if len(picker.keys) != n_want:
+                    raise InvalidError("one sampling key per wanted place")
+                keys = picker.keys
+        key = (phase, T, B, n_want, max_seq_len, max_kv_len, choice)
+        if pad_to and self.use_graphs and key in self._prompt_shapes_seen:
+            graph = self._graph_of(key)  # a geometry that came before: captured once, replayed since
+            graph.upload(host, keys)
+            self._launch(graph)
+            if picker is not None:
+                return graph.ids
+            return graph.logits if borrow else graph.logits.clone()
+        if pad_to:
+            self._prompt_shapes_seen.add(key)
+        if rt.device.type == "cuda":
+            dev = torch.from_numpy(host).pin_memory().to(rt.device, non_blocking=True)
+        else:
+            dev = torch.from_numpy(host).to(rt.device)
+        ctx = context_over(dev, rt, phase, T, B, n_want, max_seq_len, max_kv_len, len(dest_rows))
+        start = ops.launch_count()
+        if picker is None:
+            result = self.model.forward(ctx, self.cache)
+        else:
+            device_keys = None
+            if keys is not None:
+                device_keys = torch.tensor(keys, dtype=torch.int64).pin_memory().to(rt.device, non_blocking=True)
+            result = self.model.forward_pick(ctx, self.cache, picker.temperature, picker.seed, device_keys)
+        self.last_launches = ops.launch_count() - start
+        return result
 
     def check_device_status(self) -> None:
         """Raise if a kernel recorded that it gave up on a bounded wait (reads 4 bytes back,
@@ -404,18 +430,23 @@ class StepRunner:
             return logits.index_select(0, index)
         return logits if borrow else logits.clone()
 
-    def _graph_for(self, batch: int, max_kv_len: int, choice=None) -> _DecodeGraph:
-        key = (batch, length_bucket(max_kv_len), choice)
+    def _graph_for(self, batch: int, max_kv_len: int, choice=None) -> _StepGraph:
+        bucket = length_bucket(max_kv_len)
+        return self._graph_of(("decode", batch, batch, batch, 1, bucket, choice))
+
+    def _graph_of(self, key: Tuple) -> _StepGraph:
+        """The captured step of geometry `key` = (phase, tokens, sequences, wanted rows, longest
+        portion, longest sequence, how tokens are chosen); made on first use."""
         graph = self._graphs.get(key)
         if graph is None:
-            graph = self._graphs[key] = _DecodeGraph(self, *key)
+            graph = self._graphs[key] = _StepGraph(self, *key)
             while len(self._graphs) > self.max_graphs:
                 self._graphs.popitem(last=False)  # the least recently used one and its buffers
         else:
             self._graphs.move_to_end(key)
         return graph
 
-    def _launch(self, graph: _DecodeGraph) -> None:
+    def _launch(self, graph: _StepGraph) -> None:
         from ..kernels import gemm_dispatch
         if graph.graph is None:
             self._capture(graph)
@@ -426,7 +457,7 @@ class StepRunner:
             # wrappers: say here that the status word has to be read at the next check
             gemm_dispatch.mark_status_dirty()
 
-    def _capture(self, graph: _DecodeGraph) -> None:
+    def _capture(self, graph: _StepGraph) -> None:
         # One eager run first: it loads every kernel the step needs and writes
         # exactly what the replay will write again, so it changes no result.
         def run():

@@ -140,7 +140,21 @@ def gemm_bf16_slices(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Te
     lib = library.load()
     stream_ok, umma_ok = _fast_kernels(x, weight, lib)
     if not stream_ok:
-        return None
+        if not umma_ok or M <= 64:
+            return None
+        # A short prompt (a few hundred rows): few 128 x 128 tiles and a long K leave most SMs idle
+        # (the 2048 x 8192 product of a 128-token prompt: 16 CTAs, 42 us), so K is cut until the
+        # items fill the SMs once, no slice shorter than 256 (the same product in 9 slices: 12 us).
+        tiles = -(-M // 128) * -(-N // 128)
+        splits = min(-(-K // 64) // 4, SM_COUNT // tiles)
+        planes = lib.lrm_gemm_bf16_umma_slices(K, splits) if splits > 1 else 1
+        if planes <= 1:
+            return None
+        out = torch.empty((planes, M, N), dtype=torch.float32, device=x.device)
+        mark_status_dirty()
+        _done(lib.lrm_gemm_bf16_umma_rows(_ptr(x), _ptr(weight), _ptr(out), M, M, N, K, 4, 0, splits,
+                                          _ptr(_status_word(x.device)), _stream()), "gemm_bf16_umma")
+        return out
     use_umma, splits = False, 1
     if umma_ok and M > STREAM_ROWS and not force_stream:
         use_umma, splits = _few_rows_plan(M, N, K, 4)

@@ -827,7 +827,8 @@ def test_device_memory_is_constant_over_many_decode_steps(engine, model_dirs, dt
     session = model.session(context=128, max_batch=3)
     prompts = [helpers.random_tokens(i, 3 + i, 256) for i in range(3)]
     options = GenerationOptions(max_tokens=65, sampling=Sampling(temperature=0.0))
-    session.generate(prompts, options, stop_token_ids=())          # warm-up: graphs, staging buffers
+    for _ in range(2):                                             # warm-up: graphs (the prompt step's is
+        session.generate(prompts, options, stop_token_ids=())      # captured the second time), staging buffers
     torch.cuda.synchronize()
     in_use, reserved = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
     free_before = torch.cuda.mem_get_info()[0]
@@ -1021,3 +1022,40 @@ def test_a_windowed_model_generates_one_step_ahead(engine, tmp_path):
                 best = int(np.argmax(logits))
                 assert token == best or logits[best] - logits[token] <= 4e-5 * np.abs(logits).max()
                 seq.append(token)
+
+
+# --------------------------------------------------------------------------- short prompts
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompt_steps_are_filled_to_whole_rows_and_replayed_from_a_graph(engine, model_dirs, plain_models, dtype):
+    """A prompt step of a few hundred tokens is filled up to a whole number of 64 rows with a
+    sequence of padding, so that steps of different sizes share a geometry; the second step of a
+    geometry is captured in a CUDA graph and later ones replay it. Padding changes no result, and
+    the replayed step gives the bits of the uncaptured one."""
+    vocab = helpers.TINY["D"]["config"]["vocab_size"]
+    runner, cache, _ = open_runner(engine, model_dirs["D"], dtype)
+    assert runner.pads_prompts
+    sets = [[helpers.random_tokens(400 + 10 * s + i, n, vocab) for i, n in enumerate(lengths)]
+            for s, lengths in enumerate(([5, 70, 33], [9, 66, 30], [5, 70, 33], [1, 127, 0][:2]))]
+    sets[2] = sets[0]
+    outs = []
+    for prompts in sets:
+        slots = [cache.open_slot() for _ in prompts]
+        out = runner.step([entry(sl, p) for sl, p in zip(slots, prompts)]).clone()
+        at = 0
+        for p in prompts:
+            ref = P.forward(*plain_models["D"], p).numpy()
+            helpers.assert_logits_close(out[at:at + len(p)].cpu(), ref, dtype, f"prompt of {len(p)} in a filled step")
+            at += len(p)
+        assert out.shape[0] == at                                  # no row of padding comes back
+        # decoding goes on from what the filled step stored
+        nxt = runner.step([entry(slots[0], [3])]).cpu()
+        ref = P.forward(*plain_models["D"], prompts[0] + [3]).numpy()
+        helpers.assert_logits_close(nxt, ref[-1:], dtype, "decoding after a filled step")
+        for sl in slots:
+            cache.close_slot(sl)
+        outs.append(out)
+    prompt_graphs = [k for k in runner._graphs if k[0] == "prefill"]
+    # wanted rows differ between the sets (108, 105, 108, 128 logits), so three geometries were seen;
+    # the third set repeats the first one's and replays a graph
+    assert len(prompt_graphs) == 1 and prompt_graphs[0][1] == 128
+    assert torch.equal(outs[2], outs[0])                           # replayed = uncaptured, bit for bit
