@@ -5,10 +5,12 @@
 // One thread-block cluster per (sequence, kv head, group of 16 query heads); the cluster's
 // CTAs take the sequence's 64-key pages in turn (CTA r: pages r, r + S, ...), each through a
 // three-stage cp.async ring, and reduce their partial results through distributed shared
-// memory: every CTA leaves (acc, max, mass) per query head in its own shared memory, the
-// cluster synchronises, and each CTA then finishes a slice of the output from all partials:
-// out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M). Nothing goes through global memory between
-// the split and the merge, and no second kernel runs.
+// memory: every CTA sends (acc, max, mass) per query head to the CTA that finishes that part of
+// the output, into a region of its shared memory kept for nothing else; the cluster
+// synchronises once, and each finishing CTA reads only its own shared memory:
+// out = sum acc_i 2^(m_i-M) / sum l_i 2^(m_i-M). Nobody reads a peer's memory, so nobody has to
+// wait before it leaves. Nothing goes through global memory between the split and the merge,
+// and no second kernel runs. A cluster of one CTA writes its output without any of this.
 //
 // The step's fused q|k|v projection is the input. The CTA that owns the sequence's last page
 // rotates the new k row, writes it and the v row to the cache and places both in its shared
@@ -30,6 +32,11 @@ namespace cg = cooperative_groups;
 namespace {
 
 constexpr int kStages = 3;
+
+// The cluster's barrier in two halves: everybody arrives early and waits where it first needs the
+// others (all threads of every CTA execute both).
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 
 // Rotate the query fragments in registers: columns c < SPAN * 16 pair with c + SPAN * 16, which
 // the same thread holds in fragment ks + SPAN. Same operations as rope_store.cu.
@@ -91,6 +98,12 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
   const bool owner = n_mine > 0 && rank + (n_mine - 1) * n_ranks == n_pages - 1;  // has the last page
   const int new_row = (len - 1) % kTile;
 
+  const size_t qkv_row = static_cast<size_t>(q_heads + 2 * kv_heads) * D;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(b) * qkv_row;
+  uint32_t qa[D / 16][4];
+  // A CTA's peers must have started before it writes into their shared memory: everybody arrives
+  // here and waits just before the first such write, long after.
+  if (n_ranks > 1) cluster_arrive();
   auto issue = [&](int i) {  // my i-th page into ring slot i % kStages (nothing if I have no such page)
     if (i < n_mine) {
       const int page_index = rank + i * n_ranks;
@@ -109,8 +122,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
   pdl_wait();
 
   // ---- rotation: table of cos/sin for this sequence's position, q fragments, the new k/v row
-  const size_t qkv_row = static_cast<size_t>(q_heads + 2 * kv_heads) * D;
-  const __nv_bfloat16* src = qkv + static_cast<size_t>(b) * qkv_row;
   const int half = rotary / 2;
   const bool rotate = inv_freq != nullptr && half > 0;
   if (rotate && threadIdx.x < half) {
@@ -137,7 +148,6 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
     }
     if (threadIdx.x < D) v_new = src[static_cast<size_t>(q_heads + kv_heads + kh) * D + threadIdx.x];
   }
-  uint32_t qa[D / 16][4];
   load_q<D>(qa, src + static_cast<size_t>(head0) * D, D, rows);
   __syncthreads();  // the table is complete
   if (rotate) {
@@ -217,10 +227,9 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
   cp_async_wait<0>();  // only empty groups can be left
 
   // Combine the four warps (each saw 16 keys of every page) through shared memory, which the
-  // K/V tiles no longer need: per warp [16 rows][D + 2] floats, then this CTA's partial.
+  // K/V tiles no longer need: per warp [16 rows][D + 2] floats (acc, max, mass).
   __syncthreads();
   float* all = reinterpret_cast<float*>(smem_raw);
-  float* mine = all + 4 * 16 * PART;
   {
     float* stage = all + warp * 16 * PART;
 #pragma unroll
@@ -228,17 +237,49 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
       float total = l[hf];
       total += __shfl_xor_sync(0xffffffffu, total, 1);
       total += __shfl_xor_sync(0xffffffffu, total, 2);
-      float* dst = stage + (g + 8 * hf) * PART;
+      if (g + 8 * hf < rows) {
+        float* dst = stage + (g + 8 * hf) * PART;
 #pragma unroll
-      for (int dn = 0; dn < D / 8; ++dn)
-        *reinterpret_cast<float2*>(dst + 8 * dn + 2 * t) = make_float2(o[dn][2 * hf], o[dn][2 * hf + 1]);
-      if (t == 0) {
-        dst[D] = m[hf];
-        dst[D + 1] = total;
+        for (int dn = 0; dn < D / 8; ++dn)
+          *reinterpret_cast<float2*>(dst + 8 * dn + 2 * t) = make_float2(o[dn][2 * hf], o[dn][2 * hf + 1]);
+        if (t == 0) {
+          dst[D] = m[hf];
+          dst[D + 1] = total;
+        }
       }
     }
   }
   __syncthreads();
+  if (n_ranks == 1) {  // nobody to meet: finish every output from the four warps' parts
+    for (int item = threadIdx.x; item < rows * D; item += kThreads) {
+      const int r = item / D, d = item % D;
+      float mw[4], M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        mw[w] = all[(w * 16 + r) * PART + D];
+        M = fmaxf(M, mw[w]);
+      }
+      float acc = 0.f, mass = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float weight = mw[w] == -INFINITY ? 0.f : exp2f(mw[w] - M);
+        acc = fmaf(all[(w * 16 + r) * PART + d], weight, acc);
+        mass = fmaf(all[(w * 16 + r) * PART + D + 1], weight, mass);
+      }
+      out[(static_cast<size_t>(b) * q_heads + head0 + r) * D + d] = __float2bfloat16_rn(acc / mass);
+    }
+    return;
+  }
+
+  // The outputs (row r, column d), numbered r * D + d, are finished in runs of 128: run j by CTA
+  // j % n_ranks as its (j / n_ranks)-th. A row lies within one run (D divides 128), so its max and
+  // mass go to one CTA. Every CTA sends each value of its partial to the CTA that finishes it:
+  // received[sender][run][128] for the accumulators, then [sender][16 rows][max, mass].
+  const int runs = (rows * D + 127) / 128;
+  const int runs_each = (runs + n_ranks - 1) / n_ranks;
+  float* received = reinterpret_cast<float*>(smem_raw + 2 * kStages * TILE * sizeof(__nv_bfloat16));
+  const int ml_at = n_ranks * runs_each * 128;
+  cluster_wait();  // every peer has started (all arrived at the top)
   for (int item = threadIdx.x; item < rows * PART; item += kThreads) {
     const int r = item / PART, c = item % PART;
     float mw[4], M = -INFINITY;
@@ -256,44 +297,47 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
       for (int w = 0; w < 4; ++w)
         value += mw[w] == -INFINITY ? 0.f : all[(w * 16 + r) * PART + c] * exp2f(mw[w] - M);
     }
-    mine[item] = value;
+    const int number = r * D + (c < D ? c : 0);
+    const int run = number >> 7;
+    float* theirs = cluster.map_shared_rank(received, run % n_ranks);
+    if (c < D) theirs[(rank * runs_each + run / n_ranks) * 128 + (number & 127)] = value;
+    else theirs[ml_at + (rank * 16 + r) * 2 + (c - D)] = value;
   }
-  cluster.sync();  // every CTA's partial is in its shared memory
+  cluster.sync();  // everything sent to me has arrived
 
-  // Each CTA finishes a slice of the rows * D outputs from all partials of the cluster. The loads
-  // from the other CTAs' shared memory are issued together (unrolled over the largest cluster).
-  constexpr int kMaxRanks = 16;
-  for (int item = rank * kThreads + threadIdx.x; item < rows * D; item += n_ranks * kThreads) {
-    const int r = item / D, d = item % D;
-    float mi[kMaxRanks], ai[kMaxRanks], li[kMaxRanks];
-#pragma unroll
-    for (int u = 0; u < kMaxRanks; ++u) {
-      const bool in = u < n_ranks;
-      const float* part = cluster.map_shared_rank(mine, in ? u : rank) + r * PART;
-      mi[u] = in ? part[D] : -INFINITY;
-      ai[u] = part[d];
-      li[u] = part[D + 1];
-    }
+  for (int mine = 0; mine < runs_each; ++mine) {
+    const int number = ((mine * n_ranks + rank) << 7) + threadIdx.x;
+    if (number >= rows * D) break;
+    const int r = number / D;
     float M = -INFINITY;
-#pragma unroll
-    for (int u = 0; u < kMaxRanks; ++u) M = fmaxf(M, mi[u]);
+    for (int u = 0; u < n_ranks; ++u) M = fmaxf(M, received[ml_at + (u * 16 + r) * 2]);
     float acc = 0.f, mass = 0.f;
-#pragma unroll
-    for (int u = 0; u < kMaxRanks; ++u) {  // a part that saw no key has max -inf and weight 0
-      const float w = mi[u] == -INFINITY ? 0.f : exp2f(mi[u] - M);
-      acc = fmaf(ai[u], w, acc);
-      mass = fmaf(li[u], w, mass);
+    for (int u = 0; u < n_ranks; ++u) {  // a part that saw no key has max -inf and weight 0
+      const float mu = received[ml_at + (u * 16 + r) * 2];
+      const float weight = mu == -INFINITY ? 0.f : exp2f(mu - M);
+      acc = fmaf(received[(u * runs_each + mine) * 128 + threadIdx.x], weight, acc);
+      mass = fmaf(received[ml_at + (u * 16 + r) * 2 + 1], weight, mass);
     }
-    out[(static_cast<size_t>(b) * q_heads + head0 + r) * D + d] = __float2bfloat16_rn(acc / mass);
+    out[(static_cast<size_t>(b) * q_heads + head0 + r) * D + (number % D)] = __float2bfloat16_rn(acc / mass);
   }
-  cluster.sync();  // nobody leaves while its shared memory may still be read
 }
 
-template <int D> int smem_bytes() { return 2 * kStages * kTile * (D + 8) * 2; }
+// Bytes of shared memory: the K/V ring, and for clusters the region that partials are sent into
+// (n CTAs x (ceil(runs / n) x 128 accumulators + 16 rows x (max, mass))), for up to `rows` query
+// heads per kv head in a CTA.
+template <int D> int smem_bytes(int cluster, int rows) {
+  const int ring = 2 * kStages * kTile * (D + 8) * 2;
+  if (cluster <= 1) return ring;
+  const int runs = (rows * D + 127) / 128, runs_each = (runs + cluster - 1) / cluster;
+  return ring + cluster * (runs_each * 128 + 32) * 4;
+}
+
 
 template <int D> int prepare(int cluster) {
   auto kernel = attention_decode_cluster_kernel<D>;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
+  int most = 0;  // over every cluster size and up to 16 query heads per kv head
+  for (int c = 1; c <= 16; ++c) most = max(most, smem_bytes<D>(c, 16));
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (cluster > 8) {
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -303,10 +347,10 @@ template <int D> int prepare(int cluster) {
 }
 
 template <int D> void fill_config(cudaLaunchConfig_t& config, cudaLaunchAttribute* attributes, int pairs,
-                                  int cluster, cudaStream_t stream) {
+                                  int cluster, int rows, cudaStream_t stream) {
   config.gridDim = dim3(pairs * cluster);
   config.blockDim = dim3(kThreads);
-  config.dynamicSmemBytes = smem_bytes<D>();
+  config.dynamicSmemBytes = smem_bytes<D>(cluster, rows);
   config.stream = stream;
   attributes[0].id = cudaLaunchAttributeClusterDimension;
   attributes[0].val.clusterDim.x = cluster;
@@ -314,8 +358,11 @@ template <int D> void fill_config(cudaLaunchConfig_t& config, cudaLaunchAttribut
   attributes[0].val.clusterDim.z = 1;
   // Clusters of more than one CTA are launched without programmatic stream serialization:
   // started early as a dependent of the projection before it, the kernel made the whole decode
-  // step about 10 % slower (measured at batch 8, clusters of 8), so it starts when that kernel
-  // has finished. Single-CTA clusters (large batches) gain from the early start and keep it.
+  // step 10-20 % slower (measured at batch 8, clusters of 6 and 8): its CTAs then start one by one
+  // over 12 us, as that kernel's CTAs leave their SMs, and each still needs its own 12 us (three
+  // dependent loads before the first page arrives, the pages, the meeting of the cluster), so the
+  // last one ends later than if all had started together. Single-CTA clusters (large batches)
+  // gain from the early start and keep it.
   attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
@@ -323,12 +370,12 @@ template <int D> void fill_config(cudaLaunchConfig_t& config, cudaLaunchAttribut
 }
 
 // How many clusters of this size can be resident at once (0: this size cannot be launched).
-template <int D> int resident_clusters(int cluster) {
+template <int D> int resident_clusters(int cluster, int rows) {
   int code = prepare<D>(cluster);
   if (code != 0) return 0;
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attributes[2];
-  fill_config<D>(config, attributes, 1, cluster, nullptr);
+  fill_config<D>(config, attributes, 1, cluster, rows, nullptr);
   config.numAttrs = 1;
   int n = 0;
   if (cudaOccupancyMaxActiveClusters(&n, attention_decode_cluster_kernel<D>, &config) != cudaSuccess) {
@@ -348,7 +395,7 @@ template <int D> int launch(const void* qkv, const int* positions, const float* 
   const int group = q_heads / kv_heads, row_groups = (group + 15) / 16;
   cudaLaunchConfig_t config = {};
   cudaLaunchAttribute attributes[2];
-  fill_config<D>(config, attributes, seqs * kv_heads * row_groups, cluster, stream);
+  fill_config<D>(config, attributes, seqs * kv_heads * row_groups, cluster, min(group, 16), stream);
   cudaError_t e = cudaLaunchKernelEx(
       &config, attention_decode_cluster_kernel<D>, static_cast<const __nv_bfloat16*>(qkv), positions,
       inv_freq, rotary, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages),
@@ -365,12 +412,13 @@ LRM_API int lrm_attention_decode_cluster_supports(int head_dim, int page_size, i
          rotary <= head_dim && rotary % 32 == 0;
 }
 
-// Clusters of `cluster` CTAs that fit on the device at once; 0 when that size cannot be launched.
-LRM_API int lrm_attention_decode_cluster_resident(int head_dim, int cluster) {
-  if (cluster < 1 || cluster > 16) return 0;
-  if (head_dim == 32) return resident_clusters<32>(cluster);
-  if (head_dim == 64) return resident_clusters<64>(cluster);
-  if (head_dim == 128) return resident_clusters<128>(cluster);
+// Clusters of `cluster` CTAs, each with `rows` (1-16) query heads per kv head, that fit on the device
+// at once; 0 when that size cannot be launched.
+LRM_API int lrm_attention_decode_cluster_resident(int head_dim, int cluster, int rows) {
+  if (cluster < 1 || cluster > 16 || rows < 1 || rows > 16) return 0;
+  if (head_dim == 32) return resident_clusters<32>(cluster, rows);
+  if (head_dim == 64) return resident_clusters<64>(cluster, rows);
+  if (head_dim == 128) return resident_clusters<128>(cluster, rows);
   return 0;
 }
 

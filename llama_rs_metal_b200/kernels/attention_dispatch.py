@@ -130,14 +130,16 @@ def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_
                                           _stream()), "attention_paged_rowwise")
 
 
-_cluster_ok = {}
+_cluster_room = {}
 
 
-def _cluster_launchable(head_dim: int, cluster: int) -> bool:
-    key = (head_dim, cluster)
-    if key not in _cluster_ok:
-        _cluster_ok[key] = library.load().lrm_attention_decode_cluster_resident(head_dim, cluster) > 0
-    return _cluster_ok[key]
+def _resident_clusters(head_dim: int, cluster: int, rows: int) -> int:
+    """Clusters of this size, with `rows` query heads per kv head in a CTA, that the device holds
+    at once (the region that partials are sent into grows with both); 0: cannot be launched."""
+    key = (head_dim, cluster, rows)
+    if key not in _cluster_room:
+        _cluster_room[key] = int(library.load().lrm_attention_decode_cluster_resident(head_dim, cluster, rows))
+    return _cluster_room[key]
 
 
 def decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, window) -> bool:
@@ -184,7 +186,7 @@ def decode_cluster_size(seqs: int, kv_heads: int, group: int, head_dim: int, max
     size = max(1, min(int(0.68 * slots / clusters + 0.5), pages, MAX_CLUSTER))
     if pages >= 16 * size:  # long rows of pages per CTA: bandwidth counts more than balance
         size = max(1, min(int(0.85 * slots / clusters + 0.5), pages, MAX_CLUSTER))
-    while size > 1 and (clusters * size > slots or not _cluster_launchable(head_dim, size)):
+    while size > 1 and clusters > _resident_clusters(head_dim, size, min(group, 16)):
         size -= 1
     return size
 

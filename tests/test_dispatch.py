@@ -4,9 +4,16 @@ import pytest
 from llama_rs_metal_b200.kernels import attention_dispatch, gemm_dispatch
 
 
+def _room(head_dim, size, rows):
+    """Clusters a B200 holds at once: the region partials are sent into costs head size 64 its
+    fourth CTA per SM."""
+    per_sm = (4 if size == 1 else 3) if head_dim <= 64 else 2
+    return per_sm * 148 // size
+
+
 @pytest.fixture(autouse=True)
 def every_cluster_size_launchable(monkeypatch):
-    monkeypatch.setattr(attention_dispatch, "_cluster_launchable", lambda head_dim, size: True)
+    monkeypatch.setattr(attention_dispatch, "_resident_clusters", _room)
 
 
 def test_cluster_size_fills_the_device_and_never_exceeds_the_pages():
@@ -25,7 +32,8 @@ def test_cluster_size_fills_the_device_and_never_exceeds_the_pages():
 
 
 def test_cluster_size_respects_what_the_device_can_launch(monkeypatch):
-    monkeypatch.setattr(attention_dispatch, "_cluster_launchable", lambda head_dim, size: size <= 5)
+    monkeypatch.setattr(attention_dispatch, "_resident_clusters",
+                        lambda head_dim, size, rows: _room(head_dim, size, rows) if size <= 5 else 0)
     assert attention_dispatch.decode_cluster_size(1, 8, 4, 64, 4096) == 5
 
 
