@@ -76,10 +76,12 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
   __nv_bfloat16* Vs = Ks + kStages * TILE;
   cg::cluster_group cluster = cg::this_cluster();
   const int n_ranks = static_cast<int>(cluster.num_blocks());
-  // A single-CTA cluster lets the next kernel be scheduled at once (it waits for this one where it
-  // must). With larger clusters an early successor made the whole step 30 % slower: it is
-  // scheduled when this kernel's CTAs have exited.
-  if (n_ranks == 1) pdl_trigger();
+  // This kernel never lets the next one be scheduled before its CTAs exit. With an early
+  // griddepcontrol.launch_dependents (at the top, or after the last page) the output projection,
+  // the norm and the gate/up product are scheduled one after the other while attention still runs
+  // (each of them triggers at once): a 16-layer chain of whole layers at batch 8 then took 54 us
+  // per layer instead of 37 with single-CTA clusters, and the whole decode step 0.97 ms instead of
+  // 0.89 with clusters of 6.
   const int rank = static_cast<int>(cluster.block_rank());
   const int pair = blockIdx.x / n_ranks;
   const int rg = pair % row_groups;

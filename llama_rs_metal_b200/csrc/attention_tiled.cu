@@ -223,7 +223,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     const int* __restrict__ page_table, int table_stride, const int* __restrict__ slots,
     const int* __restrict__ kv_lens, int q_heads, int kv_heads, int row_groups, float scale_log2,
     int window, int n_splits) {
-  pdl_trigger();  // the next kernel may be scheduled at once; it waits for this one where it must
+  // no early griddepcontrol.launch_dependents: the kernels after attention trigger at once in their
+  // turn, and a whole layer's kernels scheduled behind a running attention made decode steps slower
   constexpr int STRIDE = D + 8, TILE = kTile * STRIDE;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
