@@ -66,7 +66,9 @@ def check_status() -> None:
                      14: "probabilities", 15: "weighted values", 16: "a free key/value stage",
                      17: "aligned shared memory", 21: "the query tiles", 22: "a key/value tile", 23: "scores",
                      24: "probabilities", 25: "the output", 26: "a free key/value stage", 27: "aligned shared memory"}
-            kernel = "attention_prefill_pingpong" if code >= 21 else \
+            names.update({31: "a free stage", 32: "operand tiles", 33: "the accumulator", 34: "copies in flight",
+                          35: "a free accumulator"})
+            kernel = "gemm_bf16_umma_pair" if code >= 31 else "attention_prefill_pingpong" if code >= 21 else \
                 "attention_prefill_umma" if code >= 11 else "gemm_bf16_umma"
             raise LlamaError(f"{kernel} gave up waiting for {names.get(code, code)}; its result is invalid")
 
@@ -83,16 +85,43 @@ def _tile_costs(K: int, mode: int):
     return ((128, 128, 1.0), (128, 256, 1.4), (256, 256, 1.4 * (1.55 + epilogue * 32 / k_blocks)), (128, 192, 1.2))
 
 
-def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0) -> int:
-    """0: 128 x 128, 1: 128 x 256, 2: 256 x 256, 3: 128 x 192 output tiles: least rounds over the SMs
-    times cost."""
+PAIR = 4  # tile code of the kernel that runs a 256 x 256 tile on two SMs
+
+
+def _pair_cost(K: int) -> float:
+    """A pair of SMs on a 256 x 256 tile, per round over the pairs, in units of a 128 x 128 tile on
+    one SM: each SM does a 128 x 256 tile's work with a third less operand traffic and a hidden
+    epilogue (measured at 2,048 rows: gate/up 106 us against 117, down 55 against 59, the 8B shape's
+    QKV 78 against 87; at 8,192 rows 10-25 % faster throughout); its start-up (a cluster to place,
+    tensor memory allocated by both CTAs together) weighs more the shorter K is."""
+    return 1.27 + 0.1 * 32 / max(1, -(-K // 64))
+
+
+_pair_room = {}
+
+
+def pair_room() -> int:
+    """Pairs of SMs the two-CTA product can occupy at once (0: not on this device)."""
+    device = torch.cuda.current_device()
+    if device not in _pair_room:
+        _pair_room[device] = 0 if force_tiled else int(library.load().lrm_gemm_bf16_umma_pair_room())
+    return _pair_room[device]
+
+
+def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0, pairs: int = 0) -> int:
+    """0: 128 x 128, 1: 128 x 256, 2: 256 x 256, 3: 128 x 192 output tiles on one SM each, or 4: 256 x
+    256 tiles on `pairs` pairs of SMs (0: not to be had): least rounds over the SMs times cost."""
     if umma_width is not None:
-        return {128: 0, 256: 1, 512: 2, 192: 3}[umma_width]
+        return {128: 0, 256: 1, 512: 2, 192: 3, "pair": PAIR}[umma_width]
     best, best_cost = 0, None
     for index, (rows, columns, cost) in enumerate(_tile_costs(K, mode)):
         rounds = -(-(-(-M // rows) * -(-N // columns)) // SM_COUNT)
         if best_cost is None or rounds * cost < best_cost:
             best, best_cost = index, rounds * cost
+    if pairs > 0 and mode <= 3:
+        rounds = -(-(-(-M // 256) * -(-N // 256)) // pairs)
+        if rounds * _pair_cost(K) < best_cost:
+            best = PAIR
     return best
 
 
@@ -185,7 +214,7 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
     N = weight.shape[0]
     lib = library.load()
     stream_ok, umma_ok = _fast_kernels(x, weight, lib)
-    tile, splits = tile_choice(M, N, K, mode), 1
+    tile, splits = tile_choice(M, N, K, mode, pair_room() if umma_ok and M > 64 else 0), 1
     if stream_ok and umma_ok and M > STREAM_ROWS and not force_stream:
         use_umma, splits = _few_rows_plan(M, N, K, mode)
         stream_ok = not use_umma
@@ -194,6 +223,11 @@ def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: in
         warps = stream_shape[0] if stream_shape is not None else 0
         _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode, warps, 0,
                                               _stream()), "gemm_bf16_stream")
+        return
+    if umma_ok and tile == PAIR:
+        mark_status_dirty()
+        _done(lib.lrm_gemm_bf16_umma_pair(_ptr(x), _ptr(weight), _ptr(out), M, N, K, mode,
+                                          _ptr(_status_word(x.device)), _stream()), "gemm_bf16_umma_pair")
         return
     if umma_ok:
         mark_status_dirty()

@@ -56,6 +56,7 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_gemm_bf16_stream_shaped": lambda a: _gemm(_v(a[3]), _v(a[4]), _v(a[5]), _out_elem(_v(a[6]))),
     "lrm_gemm_bf16_mma": lambda a: _gemm(_v(a[3]), _v(a[4]), _v(a[5]), _out_elem(_v(a[6]))),
     "lrm_gemm_bf16_umma_rows": lambda a: _gemm(_v(a[3]), _v(a[5]), _v(a[6]), _out_elem(_v(a[7]))),
+    "lrm_gemm_bf16_umma_pair": lambda a: _gemm(_v(a[3]), _v(a[4]), _v(a[5]), _out_elem(_v(a[6]))),
     "lrm_gemm_bf16_stream_pick": lambda a: _gemm(_v(a[2]), _v(a[3]), _v(a[4]), 0),
     "lrm_rope_store": lambda a: (2.0 * _v(a[11]) * (_v(a[12]) + 2 * _v(a[13])) * _v(a[14]) * _ELEM[_v(a[1])], 0),
     "lrm_silu_mul": lambda a: (3.0 * _v(a[3]) * _v(a[4]) * _ELEM[_v(a[2])], 0),
@@ -75,7 +76,7 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_sample_gumbel_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
 }
 # entry points that only answer questions and launch nothing
-_QUERIES = ("_supports", "_slices", "_pieces", "_resident", "_floats", "_error", "lrm_set_pdl", "lrm_pick_pieces")
+_QUERIES = ("_supports", "_slices", "_pieces", "_resident", "_floats", "_error", "_room", "lrm_set_pdl", "lrm_pick_pieces")
 
 
 class _Row:

@@ -66,6 +66,12 @@ def test_tile_shape_of_prompt_products():
     assert choice(4096, 3072, 2048, 0) == 1
     assert choice(2048, 2048, 8192, 2) == 1         # 64 large tiles would leave most SMs idle
     assert choice(8192, 2048, 8192, 2) == 2         # long K: the 256 x 256 tile pays
+    # with 74 pairs of SMs to be had, 256 x 256 tiles over pairs where they fill the pairs well
+    assert choice(2048, 16384, 2048, 3, 74) == 4    # 512 tiles: 7 rounds of 74
+    assert choice(2048, 2048, 8192, 2, 74) == 4     # 64 tiles in one round, long K
+    assert choice(2048, 3072, 2048, 0, 74) == 3     # 96 tiles would take two rounds for 1.3 rounds' work
+    assert choice(512, 3072, 2048, 0, 74) == 0      # 24 tiles would leave two thirds of the pairs idle
+    assert choice(8192, 6144, 4096, 0, 74) == 4
     assert choice(8192, 16384, 2048, 3) == 1        # short K and a costly epilogue: it does not
     assert choice(256, 2048) == 0                   # 32 small tiles keep more SMs busy than 16 or 8 larger ones
     assert choice(128, 128) == 0

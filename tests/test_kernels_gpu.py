@@ -591,8 +591,8 @@ UMMA_SHAPES = [(65, 128, 64), (128, 128, 128), (129, 72, 8), (200, 300, 72), (33
                (2048, 512, 256), (70, 16, 2048), (256, 1100, 136), (700, 40000, 72)]
 
 
-@pytest.mark.parametrize("width", [128, 192, 256, 512])
-@pytest.mark.parametrize("M,N,K", UMMA_SHAPES)
+@pytest.mark.parametrize("width", [128, 192, 256, 512, "pair"])
+@pytest.mark.parametrize("M,N,K", UMMA_SHAPES + [(1000, 1100, 520)])
 def test_linear_bfloat16_tensor_core_tiles(ops, monkeypatch, width, M, N, K):
     from llama_rs_metal_b200.kernels import gemm_dispatch
     monkeypatch.setattr(gemm_dispatch, "umma_width", width)
@@ -607,7 +607,7 @@ def test_linear_bfloat16_tensor_core_tiles(ops, monkeypatch, width, M, N, K):
     gemm_dispatch.check_status()
 
 
-@pytest.mark.parametrize("width", [128, 192, 256, 512])
+@pytest.mark.parametrize("width", [128, 192, 256, 512, "pair"])
 @pytest.mark.parametrize("M,I,K", [(70, 136, 64), (300, 520, 200), (128, 8, 16), (513, 20000, 64)])
 def test_linear_bfloat16_tensor_core_silu_gate(ops, monkeypatch, width, M, I, K):
     from llama_rs_metal_b200.kernels import gemm_dispatch
