@@ -10,9 +10,9 @@
 // from L2 per product than a 128 x 256 one, and that traffic is what bounds these products);
 // with MT BN <= 256 two sets of accumulators alternate;
 // tcgen05.commit signals both "stage free" to the loader and "accumulator
-// ready" to the epilogue. Four epilogue warps read their 32 TMEM lanes
-// (tcgen05.ld, one row per thread) while the next tile's MMAs fill the other
-// accumulator, and apply the epilogue:
+// ready" to the epilogue. Eight epilogue warps read their 32 TMEM lanes
+// (tcgen05.ld, one row and half of its columns per thread) while the next tile's MMAs fill the
+// other accumulator, and apply the epilogue:
 //   0 store bfloat16, 1 store float32, 2 add into float32 in place (residual
 //   stream), 3 SiLU gate over alternating blocks of 8 gate / 8 up columns,
 //   4 store float32 partials per K slice.
@@ -36,19 +36,21 @@ namespace {
 
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 
+constexpr int kUmmaThreads = 320;  // loader warp, issuer warp, eight epilogue warps
+
 // status codes (where a wait gave up)
 enum : int { kStuckEmpty = 1, kStuckFull = 2, kStuckAccumulator = 3, kStuckDrain = 4, kStuckTmemFree = 5 };
 
 // Persistent: CTA b works on items b, b + gridDim.x, ...; an item is (K slice, column tile, row
 // tile) with the row tile fastest, so CTAs that run together share a tile of W in L2.
-// Warp 0: TMA loader. Warp 1: MMA issuer (and owner of the tensor memory). Warps 2-5: epilogue.
+// Warp 0: TMA loader. Warp 1: MMA issuer (and owner of the tensor memory). Warps 2-9: epilogue.
 // Where two sets of accumulators fit in the 512 columns of tensor memory they alternate, so the
 // epilogue of one item runs under the MMAs of the next; a 256 x 256 tile fills it alone.
 template <int BN, int STAGES, int MT>
-__global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
+__global__ __launch_bounds__(kUmmaThreads, 1) void gemm_bf16_umma_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
     void* __restrict__ out, int M, int N, int K, int mode, int kb_per_split, int splits,
-    int* __restrict__ status) {
+    int* __restrict__ status, const QkvArgs qkv) {
   constexpr uint32_t A_BYTES = MT * BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t SET = MT * BN;                      // columns of one set of accumulators
   constexpr uint32_t NBUF = 2 * SET <= 512 ? 2 : 1;      // sets that fit in tensor memory
@@ -81,7 +83,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full + a, 1);
-      mbar_init(acc_free + a, 4);
+      mbar_init(acc_free + a, 8);
     }
     *bail = 0;
     mbar_fence_init();
@@ -164,9 +166,9 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
       }
     }
   } else {
-    // ---- epilogue: four warps, one accumulator row per thread; a warp may touch only the
-    // quarter of the tensor memory's lanes given by its index modulo 4
-    const int quarter = warp & 3;
+    // ---- epilogue: eight warps, one accumulator row per thread and half of its columns; a warp
+    // may touch only the quarter of the tensor memory's lanes given by its index modulo 4
+    const int quarter = warp & 3, side = (warp - 2) >> 2;
     uint32_t local = 0;
     for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
       const int m0 = (item % m_tiles) * MT * BM, n0 = ((item / m_tiles) % n_tiles) * BN;
@@ -182,9 +184,17 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
       void* plane = mode == 4 ? static_cast<void*>(static_cast<float*>(out) +
                                                    static_cast<size_t>(item / (m_tiles * n_tiles)) * M * N)
                               : out;
-      if (num_kb > 0) {
+      if (mode == 5) {  // whole heads of a q|k|v projection: rotate, store packed and into the cache
+        // the first of the two warps of a row takes the first half of the tile's heads (rounded up)
+        const int heads = BN / qkv.head_dim, cut = ((heads + 1) >> 1) * qkv.head_dim;
 #pragma unroll 1
-        for (int c = 0; c < MT * BN / 32; ++c) {  // accumulator c / (BN / 32) holds rows 128 (c / (BN / 32)) ...
+        for (int i = 0; i < MT; ++i)
+          store_heads<BN>(tmem_base + acc * SET + i * BN + (static_cast<uint32_t>(quarter * 32) << 16),
+                          m0 + i * BM + quarter * 32 + lane, n0, M, N, qkv, side == 0 ? 0 : cut, side == 0 ? cut : BN);
+      } else if (num_kb > 0) {
+        constexpr int kPieces = MT * BN / 32;
+#pragma unroll 1
+        for (int c = side * (kPieces / 2); c < (side + 1) * (kPieces / 2); ++c) {  // accumulator c / (BN / 32) holds rows 128 (c / (BN / 32)) ...
           const int m = m0 + (c / (BN / 32)) * BM + quarter * 32 + lane;
           uint32_t r[32];
           tmem_load32(tmem_base + acc * SET + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
@@ -204,7 +214,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_kernel(
 // ------------------------------------------------------------------------- host side
 template <int BN, int STAGES, int MT = 1>
 int launch_umma(const void* X, const void* W, void* out, int M, int x_rows, int N, int K, int mode, int splits,
-                int* status, cudaStream_t stream) {
+                int* status, cudaStream_t stream, const QkvArgs& qkv = QkvArgs{}) {
   CUtensorMap map_x, map_w;
   if (!make_map_bf16(&map_x, X, x_rows, K, BM) || !make_map_bf16(&map_w, W, N, K, BN)) return LRM_UNSUPPORTED;
   constexpr int smem = STAGES * (MT * BM * BK * 2 + BN * BK * 2) + 1024 + 256;
@@ -223,8 +233,8 @@ int launch_umma(const void* X, const void* W, void* out, int M, int x_rows, int 
     if (sm_count <= 0) sm_count = 148;
   }
   const int grid = static_cast<int>(items < sm_count ? items : sm_count);
-  LRM_LAUNCH(kernel, dim3(grid), 192, smem, stream, map_x, map_w, out, M, N, K, mode, kb_per_split, real_splits,
-             status);
+  LRM_LAUNCH(kernel, dim3(grid), kUmmaThreads, smem, stream, map_x, map_w, out, M, N, K, mode, kb_per_split, real_splits,
+             status, qkv);
   return 0;
 }
 
@@ -266,6 +276,32 @@ LRM_API int lrm_gemm_bf16_umma_rows(const void* X, const void* W, void* out, int
   if (tile == 2) return launch_umma<256, 3, 2>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
   if (tile == 1) return launch_umma<256, 4>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
   return launch_umma<128, 6>(X, W, out, M, x_rows, N, K, mode, splits, status, stream);
+}
+
+// Epilogue 5: X . W^T is a prompt's fused q|k|v projection; it is rotated and stored as rope_store.cu
+// would store it (see QkvArgs), without a launch of its own. The tile's width must be a whole
+// number of heads; head sizes 64 and 128; rotation of the whole head or none.
+LRM_API int lrm_gemm_bf16_umma_qkv(const void* X, const void* W, int M, int N, int K, int tile, void* q, void* k,
+                                   void* v, void* k_pages, void* v_pages, const int* dest_rows,
+                                   const float* table, int q_heads, int kv_heads, int head_dim, int page_size,
+                                   int* status, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (!lrm_gemm_bf16_umma_supports(M, N, K)) return LRM_UNSUPPORTED;
+  if (status == nullptr || q == nullptr || k == nullptr || v == nullptr || (k_pages != nullptr && dest_rows == nullptr))
+    return LRM_BAD_ARGUMENT;
+  if ((head_dim != 64 && head_dim != 128) || N != (q_heads + 2 * kv_heads) * head_dim) return LRM_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16 ||
+      reinterpret_cast<uintptr_t>(table) % 16)
+    return LRM_UNSUPPORTED;
+  const int width = tile == 0 ? 128 : tile == 3 ? 192 : 256;
+  if (tile < 0 || tile > 3 || width % head_dim != 0) return LRM_BAD_ARGUMENT;
+  const QkvArgs args{static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v),
+                     static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), dest_rows,
+                     reinterpret_cast<const float2*>(table), q_heads, kv_heads, head_dim, page_size};
+  if (tile == 3) return launch_umma<192, 5>(X, W, nullptr, M, M, N, K, 5, 1, status, stream, args);
+  if (tile == 2) return launch_umma<256, 3, 2>(X, W, nullptr, M, M, N, K, 5, 1, status, stream, args);
+  if (tile == 1) return launch_umma<256, 4>(X, W, nullptr, M, M, N, K, 5, 1, status, stream, args);
+  return launch_umma<128, 6>(X, W, nullptr, M, M, N, K, 5, 1, status, stream, args);
 }
 
 LRM_API int lrm_gemm_bf16_umma(const void* X, const void* W, void* out, int M, int N, int K, int mode,

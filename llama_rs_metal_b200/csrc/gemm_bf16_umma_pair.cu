@@ -13,7 +13,7 @@
 // Who does what: in each CTA one thread issues the TMA loads of its halves; they complete on the
 // leader's (CTA 0's) "full" barrier, which expects the bytes of both CTAs. One thread of the
 // leader issues the MMAs for the pair and commits to the "stage free" and "accumulator ready"
-// barriers of both CTAs (tcgen05.commit with a CTA mask). Four epilogue warps per CTA read their
+// barriers of both CTAs (tcgen05.commit with a CTA mask). Eight epilogue warps per CTA read their
 // CTA's accumulator rows and tell the leader's "accumulator free" barrier when done. Tensor
 // memory is allocated and freed by one warp of each CTA together, as cta_group::2 requires.
 // Epilogues as in the single-CTA kernel (0-3; K is never sliced here).
@@ -27,6 +27,7 @@
 namespace {
 
 constexpr int PM = 128, PK = 64, P_UMMA_K = 16;  // rows per CTA, K per stage, K per instruction
+constexpr int kPairThreads = 320;                // loader warp, tensor-memory/issuer warp, eight epilogue warps
 
 enum : int { kPairStuckEmpty = 31, kPairStuckFull = 32, kPairStuckAccumulator = 33, kPairStuckDrain = 34,
              kPairStuckTmemFree = 35 };
@@ -89,11 +90,11 @@ __device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a,
 
 // Pair p (CTAs 2p and 2p + 1) works on items p, p + pairs, ...; an item is a (column tile, row
 // tile) of 256 rows x BN columns with the row tile fastest.
-// Warp 0: TMA loader. Warp 1: tensor memory, and in the leader the MMA issuer. Warps 2-5: epilogue.
+// Warp 0: TMA loader. Warp 1: tensor memory, and in the leader the MMA issuer. Warps 2-9: epilogue.
 template <int BN, int STAGES>
-__global__ __launch_bounds__(192, 1) void gemm_bf16_umma_pair_kernel(
+__global__ __launch_bounds__(kPairThreads, 1) void gemm_bf16_umma_pair_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-    void* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ status) {
+    void* __restrict__ out, int M, int N, int K, int mode, int* __restrict__ status, const QkvArgs qkv) {
   constexpr uint32_t A_BYTES = PM * PK * 2, B_BYTES = (BN / 2) * PK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t ALLOC = 512, SET = 256;  // two sets of accumulators, 256 columns apart
   static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "BN / 2 rows of W per CTA, a multiple of 16");
@@ -124,7 +125,7 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_pair_kernel(
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(acc_full + a, 1);
-      mbar_init(acc_free + a, 8);  // four epilogue warps in each of the two CTAs
+      mbar_init(acc_free + a, 16);  // eight epilogue warps in each of the two CTAs
     }
     *bail = 0;
     mbar_fence_init();
@@ -198,8 +199,9 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_pair_kernel(
       }
     }
   } else {
-    // ---- epilogue: four warps, one accumulator row per thread, this CTA's 128 rows of the tile
-    const int quarter = warp & 3;
+    // ---- epilogue: eight warps, one accumulator row and half of its columns per thread, this
+    // CTA's 128 rows of the tile
+    const int quarter = warp & 3, side = (warp - 2) >> 2;
     uint32_t local = 0;
     for (int item = pair; item < items; item += pairs, ++local) {
       const int m0 = (item % m_tiles) * 2 * PM + static_cast<int>(rank) * PM, n0 = (item / m_tiles) * BN;
@@ -209,11 +211,17 @@ __global__ __launch_bounds__(192, 1) void gemm_bf16_umma_pair_kernel(
         break;
       }
       tc_fence_after();
+      if (mode == 5) {
+        const int heads = BN / qkv.head_dim, cut = ((heads + 1) >> 1) * qkv.head_dim;
+        store_heads<BN>(tmem_base + acc * SET + (static_cast<uint32_t>(quarter * 32) << 16),
+                        m0 + quarter * 32 + lane, n0, M, N, qkv, side == 0 ? 0 : cut, side == 0 ? cut : BN);
+      } else {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_load32(tmem_base + acc * SET + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
-        store_piece(r, out, m0 + quarter * 32 + lane, n0 + c * 32, M, N, mode);
+        for (int c = side * (BN / 64); c < (side + 1) * (BN / 64); ++c) {
+          uint32_t r[32];
+          tmem_load32(tmem_base + acc * SET + (static_cast<uint32_t>(quarter * 32) << 16) + c * 32, r);
+          store_piece(r, out, m0 + quarter * 32 + lane, n0 + c * 32, M, N, mode);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -236,7 +244,7 @@ int pair_config(cudaLaunchConfig_t& config, cudaLaunchAttribute* attributes, int
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem<BN, STAGES>());
   if (e != cudaSuccess) return static_cast<int>(e);
   config.gridDim = dim3(grid);
-  config.blockDim = dim3(192);
+  config.blockDim = dim3(kPairThreads);
   config.dynamicSmemBytes = pair_smem<BN, STAGES>();
   config.stream = stream;
   attributes[0].id = cudaLaunchAttributeClusterDimension;
@@ -271,7 +279,7 @@ template <int BN, int STAGES> int resident_pairs() {
 
 template <int BN, int STAGES>
 int launch_pair(const void* X, const void* W, void* out, int M, int N, int K, int mode, int* status,
-                cudaStream_t stream) {
+                cudaStream_t stream, const QkvArgs& qkv = QkvArgs{}) {
   const int room = resident_pairs<BN, STAGES>();
   if (room <= 0) return LRM_UNSUPPORTED;
   CUtensorMap map_x, map_w;
@@ -283,7 +291,7 @@ int launch_pair(const void* X, const void* W, void* out, int M, int N, int K, in
   int code = pair_config<BN, STAGES>(config, attributes, 2 * pairs, stream);
   if (code != 0) return code;
   cudaError_t e = cudaLaunchKernelEx(&config, gemm_bf16_umma_pair_kernel<BN, STAGES>, map_x, map_w, out, M, N, K,
-                                     mode, status);
+                                     mode, status, qkv);
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
 
@@ -307,4 +315,23 @@ LRM_API int lrm_gemm_bf16_umma_pair(const void* X, const void* W, void* out, int
   if (mode < 0 || mode > 3 || (mode == 3 && N % 16 != 0) || status == nullptr) return LRM_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16) return LRM_UNSUPPORTED;
   return launch_pair<256, 6>(X, W, out, M, N, K, mode, status, stream);
+}
+
+// Epilogue 5 on pairs of SMs (see lrm_gemm_bf16_umma_qkv): head sizes 64 and 128.
+LRM_API int lrm_gemm_bf16_umma_pair_qkv(const void* X, const void* W, int M, int N, int K, void* q, void* k, void* v,
+                                        void* k_pages, void* v_pages, const int* dest_rows, const float* table,
+                                        int q_heads, int kv_heads, int head_dim, int page_size, int* status,
+                                        cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K < 8 || K % 8 != 0 || encode_tiled() == nullptr) return LRM_UNSUPPORTED;
+  if (status == nullptr || q == nullptr || k == nullptr || v == nullptr || (k_pages != nullptr && dest_rows == nullptr))
+    return LRM_BAD_ARGUMENT;
+  if ((head_dim != 64 && head_dim != 128) || N != (q_heads + 2 * kv_heads) * head_dim) return LRM_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(X) % 16 || reinterpret_cast<uintptr_t>(W) % 16 ||
+      reinterpret_cast<uintptr_t>(table) % 16)
+    return LRM_UNSUPPORTED;
+  const QkvArgs args{static_cast<__nv_bfloat16*>(q), static_cast<__nv_bfloat16*>(k), static_cast<__nv_bfloat16*>(v),
+                     static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages), dest_rows,
+                     reinterpret_cast<const float2*>(table), q_heads, kv_heads, head_dim, page_size};
+  return launch_pair<256, 6>(X, W, nullptr, M, N, K, 5, status, stream, args);
 }

@@ -224,3 +224,26 @@ LRM_API int lrm_rope_store(const void* qkv, int dtype, void* q_out, void* k_out,
                                       inv_freq, rotary, tokens, q_heads, kv_heads, d, page_size, stream);
   return LRM_BAD_ARGUMENT;
 }
+
+// (cos, sin) of float(position) * inv_freq[i] for every token of a step and i < half: the table
+// that a product's rotating epilogue reads, the same angles and the same sincosf as above.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ table, int tokens, int half) {
+  pdl_trigger();
+  pdl_wait();
+  const int item = blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= tokens * half) return;
+  const float angle = __fmul_rn(static_cast<float>(positions[item / half]), inv_freq[item % half]);
+  float sn, cs;
+  sincosf(angle, &sn, &cs);
+  table[item] = make_float2(cs, sn);
+}
+
+LRM_API int lrm_rope_table(const int* positions, const float* inv_freq, float* table, int tokens, int half,
+                           cudaStream_t stream) {
+  if (tokens <= 0 || half <= 0) return 0;
+  const int items = tokens * half;
+  LRM_LAUNCH(rope_table_kernel, dim3((items + 255) / 256), 256, 0, stream, positions, inv_freq,
+             reinterpret_cast<float2*>(table), tokens, half);
+  return 0;
+}

@@ -52,6 +52,7 @@ class StepContext:
     # block does right before it passes the part's output through a norm with `folds_pending`;
     # `next_folds_pending` tells a block whether whatever reads the stream after it does so.
     pending: Any = None
+    scratch: Dict[Any, Any] = field(default_factory=dict)  # what kernels' dispatchers keep for the length of a step
     may_defer: bool = False
     next_folds_pending: bool = False
 

@@ -204,7 +204,7 @@ def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slot
 
 # --------------------------------------------------------------------------- one call for a mixer
 def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx, cache, writes_cache: bool,
-           cache_entry: int, scale: float, window):
+           cache_entry: int, scale: float, window, projection=None):
     """A layer's attention for one step: position rotation, cache write and attention, with the
     kernels chosen here for the step's phase, dtype and geometry. -> mixed heads [T, q_heads * d].
 
@@ -214,10 +214,28 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
     rotary: (inverse frequencies float32 [R/2], R) for a split-half rotation applied here, or None
         (no rotation: another scheme already transformed q and k, or there is none).
     ctx: the StepContext; cache: the KeyValueView of `cache_entry`; window: keys a query sees, or None.
+    projection: (x, weight) instead of `projected` (then None) when nothing stands between the
+        projection and the rotation: a prompt's product then rotates and stores in its epilogue.
     """
     from . import ops
     inv_freq, width = rotary if rotary is not None else (None, 0)
     phase = ctx.phase
+    if projection is not None:
+        x, weight = projection
+        if (phase == "prefill" and writes_cache and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+                and width in (0, head_dim)):
+            table = None
+            if inv_freq is not None:   # one table of cosines and sines per step and rotation
+                table = ctx.scratch.get(("rope_table", id(inv_freq)))
+                if table is None:
+                    table = ctx.scratch[("rope_table", id(inv_freq))] = ops.rope_table(ctx.positions, inv_freq)
+            fused = ops.linear_rope_store(x, weight, q_heads, kv_heads, head_dim, table, cache,
+                                          ctx.dest_rows[cache.group] if cache is not None else None)
+            if fused is not None:
+                q, k, v = fused
+                ctx.fresh_kv[cache_entry] = (k, v)
+                return ops.attention_prefill(q, k, v, ctx.cu_seqlens, ctx.seq_of_token, ctx.max_seq_len, scale, window)
+        projected = ops.linear(x, weight)
     if writes_cache:
         if (phase == "decode" and cache is not None and projected.dtype == torch.bfloat16
                 and decode_fused_supported(projected.dtype, head_dim, cache.page_size, width,

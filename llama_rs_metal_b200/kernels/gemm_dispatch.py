@@ -108,13 +108,16 @@ def pair_room() -> int:
     return _pair_room[device]
 
 
-def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0, pairs: int = 0) -> int:
+def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0, pairs: int = 0, multiple_of: int = 1) -> int:
     """0: 128 x 128, 1: 128 x 256, 2: 256 x 256, 3: 128 x 192 output tiles on one SM each, or 4: 256 x
-    256 tiles on `pairs` pairs of SMs (0: not to be had): least rounds over the SMs times cost."""
-    if umma_width is not None:
+    256 tiles on `pairs` pairs of SMs (0: not to be had): least rounds over the SMs times cost, among
+    the tiles whose width is a multiple of `multiple_of` (an epilogue that works on whole heads)."""
+    if umma_width is not None and {128: 128, 256: 256, 512: 256, 192: 192, "pair": 256}[umma_width] % multiple_of == 0:
         return {128: 0, 256: 1, 512: 2, 192: 3, "pair": PAIR}[umma_width]
     best, best_cost = 0, None
     for index, (rows, columns, cost) in enumerate(_tile_costs(K, mode)):
+        if columns % multiple_of:
+            continue
         rounds = -(-(-(-M // rows) * -(-N // columns)) // SM_COUNT)
         if best_cost is None or rounds * cost < best_cost:
             best, best_cost = index, rounds * cost
@@ -206,6 +209,37 @@ def gemm_bf16_slices(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Te
     _done(lib.lrm_gemm_bf16_stream_shaped(_ptr(x), _ptr(weight), _ptr(out), M, N, K, 4, warps, wanted, _stream()),
           "gemm_bf16_stream")
     return out
+
+
+def gemm_bf16_qkv(x: torch.Tensor, weight: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  kv, dest_rows: Optional[torch.Tensor], table: Optional[torch.Tensor]) -> bool:
+    """A prompt's fused q|k|v projection with rotation and stores in the product's epilogue:
+    q [T, Hq, d], k, v [T, Hk, d] packed, and k, v into the paged cache view `kv` at `dest_rows`
+    (both None: no cache). `table`: float32 [T, d/2, 2] (cos, sin), or None for no rotation.
+    False (nothing launched) where only the separate kernels take the shape."""
+    M, K = x.shape
+    N = weight.shape[0]
+    T, Hq, d = q.shape
+    Hk = k.shape[1]
+    lib = library.load()
+    _, umma_ok = _fast_kernels(x, weight, lib)
+    if not umma_ok or no_fused_rope or M <= 64 or d not in (64, 128) or N != (Hq + 2 * Hk) * d:
+        return False
+    tile = tile_choice(M, N, K, 0, pair_room(), multiple_of=d)
+    pages = (_ptr(kv.k), _ptr(kv.v), _ptr(dest_rows), kv.page_size) if kv is not None else (None, None, None, 1)
+    mark_status_dirty()
+    if tile == PAIR:
+        _done(lib.lrm_gemm_bf16_umma_pair_qkv(_ptr(x), _ptr(weight), M, N, K, _ptr(q), _ptr(k), _ptr(v), pages[0],
+                                              pages[1], pages[2], _ptr(table), Hq, Hk, d, pages[3],
+                                              _ptr(_status_word(x.device)), _stream()), "gemm_bf16_umma_pair_qkv")
+    else:
+        _done(lib.lrm_gemm_bf16_umma_qkv(_ptr(x), _ptr(weight), M, N, K, tile, _ptr(q), _ptr(k), _ptr(v), pages[0],
+                                         pages[1], pages[2], _ptr(table), Hq, Hk, d, pages[3],
+                                         _ptr(_status_word(x.device)), _stream()), "gemm_bf16_umma_qkv")
+    return True
+
+
+no_fused_rope = False  # tests: keep rotation and stores in their own launch
 
 
 def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, mode: int) -> None:

@@ -292,6 +292,38 @@ def rope_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
     return q, k, v
 
 
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """float32 [T, R/2, 2]: (cos, sin) of float32(position) * inv_freq, the angles rope_store forms."""
+    _check(positions, "positions", torch.int32, 1)
+    _check(inv_freq, "inv_freq", torch.float32, 1)
+    T, half = positions.numel(), inv_freq.numel()
+    table = torch.empty((T, half, 2), dtype=torch.float32, device=positions.device)
+    _done(_lib().lrm_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(table), T, half, _stream()), "rope_table")
+    return table
+
+
+def linear_rope_store(x: torch.Tensor, weight: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,
+                      table: Optional[torch.Tensor], kv=None, dest_rows: Optional[torch.Tensor] = None):
+    """rope_store(linear(x, weight)) for a prompt in one launch where the tensor-core product takes
+    the shape: (q [T,Hq,d], k [T,Hk,d], v [T,Hk,d]), with k and v also written to the cache view
+    `kv` at `dest_rows`; None where it does not (nothing was launched). `table` from rope_table
+    (rotation of the whole head) or None (no rotation). Bit-equal to the two separate kernels."""
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or x.dim() != 2:
+        return None
+    T = x.shape[0]
+    if table is not None and tuple(table.shape) != (T, head_dim // 2, 2):
+        return None
+    if kv is not None and (kv.k.dtype != torch.bfloat16 or tuple(kv.k.shape[1:]) != (kv_heads, kv.page_size, head_dim)):
+        return None
+    q = torch.empty((T, q_heads, head_dim), dtype=x.dtype, device=x.device)
+    k = torch.empty((T, kv_heads, head_dim), dtype=x.dtype, device=x.device)
+    v = torch.empty((T, kv_heads, head_dim), dtype=x.dtype, device=x.device)
+    from . import gemm_dispatch
+    if not gemm_dispatch.gemm_bf16_qkv(x, weight, q, k, v, kv, dest_rows, table):
+        return None
+    return q, k, v
+
+
 # --------------------------------------------------------------------------- attention
 def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
                       seq_of_token: torch.Tensor, max_seq_len: int, scale: float,

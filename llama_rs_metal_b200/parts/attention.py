@@ -77,13 +77,17 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache, residual):
         entry = ctx.entry
-        projected = (self.qkv if entry.writes_cache else self.q_only)(x)
-        projected = self.before_rotation(projected, ctx, entry.writes_cache)
+        weight = self.qkv if entry.writes_cache else self.q_only
         rotary = self.position.rotary_table() if self.position is not None else None
+        # Nothing stands between projection and rotation unless a variant mixer overrides the hook
+        # or the position scheme is no rotary table: the kernels may then do both in one launch.
+        direct = (type(self).before_rotation is Attention.before_rotation
+                  and (self.position is None or rotary is not None) and x.dtype == weight.weight.dtype)
+        projected = None if direct else self.before_rotation(weight(x), ctx, entry.writes_cache)
         mixed = ops.attend(projected, q_heads=self.num_heads, kv_heads=self.num_kv_heads,
                            head_dim=self.head_dim, rotary=rotary, ctx=ctx, cache=cache,
                            writes_cache=entry.writes_cache, cache_entry=entry.cache, scale=self.scale,
-                           window=self.window)
+                           window=self.window, projection=(x, weight.weight) if direct else None)
         return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
 
     def before_rotation(self, projected, ctx, has_keys: bool):

@@ -11,6 +11,8 @@ from ..registry import register_position_encoding
 from .base import PositionEncoding
 
 
+_shared_frequencies = {}  # (device, frequencies) -> float32 tensor on that device
+
 @register_position_encoding("rope")
 class RotaryEmbedding(PositionEncoding):
     """angle(position, pair i) = position * scale * theta^(-2i/R) / factor[i]
@@ -69,8 +71,14 @@ class RotaryEmbedding(PositionEncoding):
         return out
 
     def bind(self, weights, runtime) -> None:
-        self.inv_freq = torch.tensor(self.inverse_frequencies(), dtype=torch.float64) \
-            .to(torch.float32).to(runtime.device)
+        # layers with the same frequencies share one tensor, so that what is derived from it once
+        # per step (a table of cosines and sines) serves them all
+        frequencies = tuple(self.inverse_frequencies())
+        key = (str(runtime.device), frequencies)
+        if key not in _shared_frequencies:
+            _shared_frequencies[key] = torch.tensor(frequencies, dtype=torch.float64) \
+                .to(torch.float32).to(runtime.device)
+        self.inv_freq = _shared_frequencies[key]
 
     def head_permutation(self) -> Optional[List[int]]:
         if not self.adjacent_pairs:

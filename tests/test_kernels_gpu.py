@@ -198,6 +198,41 @@ def test_rope_store(ops, dtype, Hq, Hk, d, R):
     assert torch.isnan(view.v.float().cpu().permute(0, 2, 1, 3)[untouched]).all()
 
 
+@pytest.mark.parametrize("width", [None, 128, 192, 256, 512, "pair"])
+@pytest.mark.parametrize("Hq,Hk,d,T,rotate", [(6, 2, 64, 300, True), (4, 1, 128, 200, True), (5, 5, 64, 129, False),
+                                               (32, 8, 64, 700, True)])
+def test_projection_with_rotation_and_stores_in_its_epilogue(ops, monkeypatch, width, Hq, Hk, d, T, rotate):
+    """A prompt's q|k|v product that rotates and stores in its epilogue leaves the bits that the
+    product followed by rope_store leaves: q, k, v packed and the cache rows, nothing else written.
+    Every tile shape whose width is a whole number of heads, and the pairs of SMs."""
+    from llama_rs_metal_b200.kernels import gemm_dispatch
+    if width is not None and {128: 128, 192: 192, 256: 256, 512: 256, "pair": 256}[width] % d:
+        pytest.skip("this tile is no whole number of heads")
+    h = 264
+    x, w = rnd(T, h, dtype=torch.bfloat16), rnd((Hq + 2 * Hk) * d, h, dtype=torch.bfloat16, seed=1, scale=0.2)
+    inv = torch.from_numpy(P.rope_inverse_frequencies(dict(rope_theta=10000.0), d)).to(DEV) if rotate else None
+    positions = i32([(7 * t) % 3000 for t in range(T)])
+    dest = [t + 64 * 3 if t % 5 else -1 for t in range(T)]        # some tokens are not kept (a window dropped them)
+    pages = (T + 64 * 3) // 64 + 2
+    fused_view, plain_view = (View(pages, Hk, 64, d, torch.bfloat16) for _ in range(2))
+    monkeypatch.setattr(gemm_dispatch, "umma_width", width)
+    table = ops.rope_table(positions, inv) if rotate else None
+    got = ops.linear_rope_store(x, w, Hq, Hk, d, table, fused_view, i32(dest))
+    gemm_dispatch.check_status()
+    assert got is not None, "the tensor-core product refused a shape it is built for"
+    monkeypatch.setattr(gemm_dispatch, "umma_width", None)
+    want = ops.rope_store(ops.linear(x, w), Hq, Hk, d, inv, d if rotate else 0, positions, kv=plain_view,
+                          dest_rows=i32(dest))
+    for name, a, b in zip("qkv", got, want):
+        assert torch.equal(a, b), f"{name} differs from the separate kernels'"
+    for a, b in ((fused_view.k, plain_view.k), (fused_view.v, plain_view.v)):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), "the cache differs (NaN = never written)"
+    if rotate:   # and the table holds the angles of the plain implementation
+        angles = positions.double().cpu()[:, None] * inv.double().cpu()[None, :]
+        close(table[..., 0], torch.cos(angles), 2e-3, "cosines")   # float32 angle of positions up to 3,000
+        close(table[..., 1], torch.sin(angles), 2e-3, "sines")
+
+
 def test_rope_store_skips_pages_a_window_dropped_and_can_leave_q_unrotated(ops):
     view = View(pages=4, kv_heads=1, page_size=64, d=16, dtype=torch.float32)
     qkv = rnd(2, 3 * 16)
