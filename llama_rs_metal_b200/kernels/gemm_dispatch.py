@@ -88,13 +88,14 @@ def _tile_costs(K: int, mode: int):
 PAIR = 4  # tile code of the kernel that runs a 256 x 256 tile on two SMs
 
 
-def _pair_cost(K: int) -> float:
-    """A pair of SMs on a 256 x 256 tile, per round over the pairs, in units of a 128 x 128 tile on
-    one SM: each SM does a 128 x 256 tile's work with a third less operand traffic and a hidden
-    epilogue (measured at 2,048 rows: gate/up 106 us against 117, down 55 against 59, the 8B shape's
-    QKV 78 against 87; at 8,192 rows 10-25 % faster throughout); its start-up (a cluster to place,
-    tensor memory allocated by both CTAs together) weighs more the shorter K is."""
-    return 1.27 + 0.1 * 32 / max(1, -(-K // 64))
+def _pair_cost(K: int, rounds: int) -> float:
+    """`rounds` rounds of 256 x 256 tiles over the pairs of SMs, in units of a 128 x 128 tile on one
+    SM: each SM does a 128 x 256 tile's work with a third less operand traffic and a hidden
+    epilogue (measured at 2,048 rows: gate/up 104 us against 115, down 60 against 64, the 8B shape's
+    QKV 88 against 97; at 4,096 rows 5-15 % faster than the best single-SM tile throughout); its
+    start-up (a cluster to place, tensor memory allocated by both CTAs together) weighs more the
+    shorter K is."""
+    return 1.27 * rounds + 0.2 * 32 / max(1, -(-K // 64))
 
 
 _pair_room = {}
@@ -116,14 +117,14 @@ def tile_choice(M: int, N: int, K: int = 2048, mode: int = 0, pairs: int = 0, mu
         return {128: 0, 256: 1, 512: 2, 192: 3, "pair": PAIR}[umma_width]
     best, best_cost = 0, None
     for index, (rows, columns, cost) in enumerate(_tile_costs(K, mode)):
-        if columns % multiple_of:
+        if columns % multiple_of or (pairs > 0 and index == 2):  # a pair does what the 256 x 256 tile does, better
             continue
         rounds = -(-(-(-M // rows) * -(-N // columns)) // SM_COUNT)
         if best_cost is None or rounds * cost < best_cost:
             best, best_cost = index, rounds * cost
     if pairs > 0 and mode <= 3:
         rounds = -(-(-(-M // 256) * -(-N // 256)) // pairs)
-        if rounds * _pair_cost(K) < best_cost:
+        if _pair_cost(K, rounds) < best_cost:
             best = PAIR
     return best
 

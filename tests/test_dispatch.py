@@ -72,6 +72,8 @@ def test_tile_shape_of_prompt_products():
     assert choice(2048, 3072, 2048, 0, 74) == 3     # 96 tiles would take two rounds for 1.3 rounds' work
     assert choice(512, 3072, 2048, 0, 74) == 0      # 24 tiles would leave two thirds of the pairs idle
     assert choice(8192, 6144, 4096, 0, 74) == 4
+    assert choice(2048, 2048, 2048, 2, 74) == 1     # one short tile per pair: the pair's start-up is not paid back
+    assert choice(8192, 2048, 8192, 2, 74) == 4     # where pairs are to be had they replace the 256 x 256 tile
     assert choice(8192, 16384, 2048, 3) == 1        # short K and a costly epilogue: it does not
     assert choice(256, 2048) == 0                   # 32 small tiles keep more SMs busy than 16 or 8 larger ones
     assert choice(128, 128) == 0
