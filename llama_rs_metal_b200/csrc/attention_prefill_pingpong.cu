@@ -116,6 +116,9 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
   const uint32_t tmem_o[2] = {tmem_base + NQ * 128, tmem_base + NQ * 128 + D};
+  // Barriers and tensor memory were set up while the kernel that produces q, k and v may still
+  // have been running (sequence bounds are the step's own input); its results are read from here on.
+  pdl_wait();
 
   if (warp == kLoaderWarp) {
     if (lane == 0) {
@@ -352,9 +355,9 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
   const int pairs = (max_seq_len + NQ * BQ - 1) / (NQ * BQ);
   if (seqs > 65535 || pairs > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(q_heads, seqs, pairs);
-  kernel<<<grid, threads_per_cta(NQ), smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
-                                                 q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
-  LRM_LAUNCH_CHECK();
+  LRM_LAUNCH(kernel, grid, dim3(threads_per_cta(NQ)), smem, stream, map_q, map_k, map_v,
+             static_cast<__nv_bfloat16*>(out), cu_seqlens, q_heads, kv_heads, scale * 1.4426950408889634f, window,
+             status);
   return 0;
 }
 

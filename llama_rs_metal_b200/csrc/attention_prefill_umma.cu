@@ -103,6 +103,11 @@ __global__ __launch_bounds__(kThreadsPerCta, D == 64 ? 2 : 1) void attention_pre
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_s = *tmem_slot, tmem_pv = tmem_s + 128, tmem_x = tmem_pv + D;
+  // Barriers and tensor memory were set up while the kernel that produces q, k and v may still
+  // have been running (sequence bounds are the step's own input); its results are read from here on.
+  // (Letting the output projection be scheduled before this kernel's CTAs exit was measured too:
+  // a 2,048-token prompt took 4.85 ms instead of 4.81.)
+  pdl_wait();
 
   if (warp == kSoftmaxWarps) {
     if (lane == 0) {
@@ -327,9 +332,8 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
   if (e != cudaSuccess) return static_cast<int>(e);
   if (seqs > 65535 || (max_seq_len + BQ - 1) / BQ > 65535) return LRM_UNSUPPORTED;
   const dim3 grid(q_heads, seqs, (max_seq_len + BQ - 1) / BQ);
-  kernel<<<grid, kThreadsPerCta, smem, stream>>>(map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out), cu_seqlens,
-                                     q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
-  LRM_LAUNCH_CHECK();
+  LRM_LAUNCH(kernel, grid, dim3(kThreadsPerCta), smem, stream, map_q, map_k, map_v, static_cast<__nv_bfloat16*>(out),
+             cu_seqlens, q_heads, kv_heads, scale * 1.4426950408889634f, window, status);
   return 0;
 }
 
