@@ -217,6 +217,10 @@ def main() -> int:
                         help="skip the correctness gate (profiling runs only; the line then says so)")
     parser.add_argument("--only", choices=["prefill"], default=None,
                         help="run just this part (a small case for profiling); prints a shorter line")
+    parser.add_argument("--timeline", choices=["decode", "prefill"], default=None,
+                        help="print, to stderr, when each kernel of one step started and ended on the device (the "
+                             "CUPTI activity trace that torch.profiler records: kernels inside a replayed graph and "
+                             "their overlap under programmatic launch show as they ran); times nothing else")
     parser.add_argument("--profile", action="store_true",
                         help="time every kernel launch (LRM_PROFILE=1) and print the table to stderr; the "
                              "line's numbers are then those of unfused, uncaptured launches")
@@ -332,7 +336,7 @@ def main() -> int:
         groups = len(session.cache.kv_groups)
         return batch * steps / (done - first), ((7 + groups) * batch + 1) * 4, batch * 4
 
-    def time_prefill(tokens, reps=5):
+    def time_prefill(tokens, reps=9):
         session = model.session(context=context, max_batch=1)
         ids = rng.integers(0, vocab, size=tokens).tolist()
         times = []
@@ -349,6 +353,58 @@ def main() -> int:
         session.runner.check_device_status()
         return statistics.median(times)
 
+    def timeline(what):
+        """One step under the activity trace: per kernel its start since the step's first kernel, its
+        duration and the gap to the kernel before it (negative: they overlapped), then sums by kernel."""
+        from torch.profiler import ProfilerActivity, profile as activity_trace
+        if what == "decode":
+            session = model.session(context=context, max_batch=batch_main)
+            slots = fill(session, start_lengths(batch_main))
+            tokens = rng.integers(0, vocab, size=(24, batch_main))
+            greedy = DevicePick(None, 0, [0] * batch_main)
+            run = lambda i: session.runner.decode_ahead(slots, tokens[i].tolist(), None, greedy)
+            warm, traced = range(16), range(16, 20)
+        else:
+            session = model.session(context=context, max_batch=1)
+            ids = rng.integers(0, vocab, size=PREFILL_TOKENS).tolist()
+
+            def run(i):
+                slot = session.open_slot()
+                session.runner.step([StepEntry(slot, ids, (PREFILL_TOKENS - 1,))])
+                torch.cuda.synchronize()
+                session.close_slot(slot)
+            warm, traced = range(4), range(4, 5)
+        for i in warm:
+            run(i)
+        torch.cuda.synchronize()
+        with activity_trace(activities=[ProfilerActivity.CUDA]) as trace:
+            for i in traced:
+                run(i)
+            torch.cuda.synchronize()
+        events = sorted((e for e in trace.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                        key=lambda e: e.time_range.start)
+        first = max(i for i, e in enumerate(events) if "embed_rows" in e.name)   # the last step traced
+        step = events[first:]
+        origin, before = step[0].time_range.start, step[0].time_range.start
+        print(f"{'start us':>9s} {'us':>7s} {'gap us':>7s}  kernel", file=sys.stderr)
+        for e in step:
+            begin, end = e.time_range.start, e.time_range.end
+            print(f"{begin - origin:9.1f} {end - begin:7.1f} {begin - before:7.1f}  {e.name[:110]}", file=sys.stderr)
+            before = end
+        totals = {}
+        for e in step:
+            calls, us = totals.get(e.name[:90], (0, 0.0))
+            totals[e.name[:90]] = (calls + 1, us + e.time_range.end - e.time_range.start)
+        print(f"one {what} step: {step[-1].time_range.end - origin:.1f} us from first start to last end, "
+              f"{len(step)} kernels; sums of durations (overlapping kernels count twice):", file=sys.stderr)
+        for name, (calls, us) in sorted(totals.items(), key=lambda item: -item[1][1]):
+            print(f"{us:9.1f} us {calls:4d} x  {name}", file=sys.stderr)
+
+    if args.timeline:
+        timeline(args.timeline)
+        print(json.dumps({"timeline": args.timeline, "shape": shape["name"], "layers": layers, "gate": gate,
+                          "note": "the table is on stderr; nothing was timed for the record"}))
+        return 0
     if args.only == "prefill":
         ms = time_prefill(PREFILL_TOKENS, reps=max(1, args.steps))
         flops = prefill_flops(config, PREFILL_TOKENS)
