@@ -150,24 +150,28 @@ def decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, wi
 
 def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> bool:
     """Whether the one-launch cluster kernel or the separate kernels are the faster way through a
-    decode step's attention. A cluster has at most 16 CTAs, so a few sequences with a long context
-    leave each CTA with many pages to walk, while the separate kernels may cut a sequence into as
-    many splits as fill the device. Measured costs: about 8 us fixed for the cluster kernel, 17 us
-    for the three separate launches, and 0.55 us per page a CTA walks (CTAs beyond what the device
-    holds at once wait their turn), and neither way reads the cache faster than about 6 TB/s."""
+    decode step's attention. A cluster has at most 16 CTAs, and a CTA keeps two pages in flight,
+    which is worth 16-20 GB/s at head size 64 (25-30 at 128): a few sequences with a long context leave the
+    cluster kernel with too few CTAs to draw the memory's bandwidth (measured: 112 CTAs 2.1 TB/s,
+    224 CTAs 3.5, 320 CTAs 5.1, from 384 CTAs on 6.0-6.2), while the separate kernels cut a sequence
+    into as many splits as fill the device and read at 6.6 TB/s (6.0 at head size 128), unless there are so many
+    (sequence, head) pairs that each gets only two or three splits (256 pairs and more: 4.7-5.6).
+    Against that stand their three launches: about 17 us before anything else counts, 8 us for the
+    cluster kernel plus 0.35 us per page a CTA walks. Whole decode steps of the 1B shape, cluster
+    kernel against separate kernels, ms: batch 1 at 16,000 keys 0.94 / 0.99, at 64,000 1.72 / 1.24;
+    batch 4: 1.19 / 1.15 and 2.43 / 2.06; batch 8: 1.46 / 1.43 and 3.69 / 3.34; batch 32 at 16,000:
+    3.85 / 4.50; batch 64: 6.92 / 7.29; at 4,000 keys the cluster kernel wins at every batch."""
     if force_cluster_size is not None:
         return True
     pages = max(1, -(-max_kv_len // 64))
     cluster = decode_cluster_size(seqs, kv_heads, group, head_dim, max_kv_len)
-    splits = decode_splits(seqs, kv_heads, group, max_kv_len, 0)
     pairs = seqs * kv_heads * -(-group // 16)
-    slots = (CTAS_PER_SM if head_dim <= 64 else 2) * SM_COUNT       # CTAs resident at once
-    stream = pairs * pages * (4 * 64 * head_dim) / 6.0e6            # us to read every K/V page at 6 TB/s
-
-    def walk(ctas_per_pair: int) -> float:  # more CTAs than fit run in turns
-        return max(stream, 0.55 * -(-pages // ctas_per_pair) * max(1.0, pairs * ctas_per_pair / slots))
-
-    return 8.0 + walk(cluster) <= 17.0 + walk(splits)
+    page_bytes = 4.0 * 64 * head_dim                       # a page of keys and one of values
+    data = pairs * pages * page_bytes                      # bytes; rates below in bytes per us
+    per_cta = 16e3 + 70.0 * head_dim                       # 20 GB/s at head size 64, 25 at 128
+    fused = max(8.0 + 0.35 * -(-pages // cluster), data / min(6.1e6, pairs * cluster * per_cta))
+    separate = max(17.0, data / (5.0e6 if pairs > 128 else 6.6e6 if head_dim <= 64 else 6.0e6) + 3.0)
+    return fused <= separate
 
 
 MAX_CLUSTER = 14  # clusters of 15 and 16 CTAs were measured slower as soon as a few hundred CTAs run

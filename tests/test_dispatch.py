@@ -52,6 +52,9 @@ def test_one_launch_or_three():
     assert fused(64, 8, 4, 64, 32768)              # bound by bandwidth either way: fewer launches win
     assert not fused(1, 8, 4, 64, 32768)           # 14 CTAs per pair would walk 37 pages each
     assert not fused(1, 8, 4, 64, 131072)
+    assert not fused(2, 8, 4, 64, 65536) and not fused(4, 8, 4, 64, 65536)   # too few CTAs for the bandwidth
+    assert fused(8, 8, 4, 64, 8192) and fused(1, 8, 4, 64, 16384)
+    assert fused(32, 8, 4, 64, 16384) and fused(64, 8, 4, 64, 16384)         # many pairs: the splits get too few each
     attention_dispatch.force_cluster_size = 2      # tests pin the cluster size: always the one launch
     try:
         assert fused(1, 8, 4, 64, 131072)
