@@ -164,6 +164,38 @@ def _fast_kernels(x: torch.Tensor, weight: torch.Tensor, lib):
             fast and bool(lib.lrm_gemm_bf16_umma_supports(M, N, K)))
 
 
+def _sliced_plan(M: int, N: int, K: int):
+    """(tile, K slices) for a product of a few hundred rows that goes into the residual stream as
+    planes: 128 x 128 or 128 x 256 tiles, K cut until the items fill the SMs once (no slice shorter
+    than 256), whichever is estimated faster, or (0, 1) where the uncut product added in place is.
+    Measured per 64 of K and item: 0.30 us with 128 x 128 tiles, 0.35 us with 128 x 256 (twice the
+    work), more where few row tiles share a W tile that comes from HBM; a plane more costs its write
+    and the norm's read of it, and the norm adds planes eight at a time. Whole prompt steps of the
+    1B shape, this rule against 128 x 128 tiles only: 768 tokens 2.46 against 2.69 ms, 1,024 tokens
+    2.92 against 3.03, 128 tokens 1.39 against 1.41, 256 and 512 tokens unchanged."""
+    k_blocks = -(-K // 64)
+    best, whole = None, None
+    row_tiles = -(-M // 128)
+    for tile, (columns, per_block) in enumerate(((128, 0.30), (256, 0.35))):
+        # with few row tiles a W tile is fetched from HBM for almost every item: 44 GB/s per SM
+        per_block = max(per_block, columns * 128 / 44e3 / row_tiles)
+        tiles = row_tiles * -(-N // columns)
+        uncut = -(-tiles // SM_COUNT) * k_blocks * per_block       # added in place, no planes
+        whole = uncut if whole is None else min(whole, uncut)
+        fill = max(1, min(k_blocks // 4, SM_COUNT // tiles))
+        for splits in {fill, min(fill, 8)}:                        # the norm adds planes eight at a time
+            per_slice = -(-k_blocks // splits)
+            planes = -(-k_blocks // per_slice)
+            rounds = -(-tiles * planes // SM_COUNT)
+            cost = (rounds * per_slice * per_block + planes * (2.0 * M * N * 4 / 3.5e6)
+                    + 2.0 * (-(-planes // 8) - 1))
+            if planes > 1 and (best is None or cost < best[0]):
+                best = (cost, tile, splits)
+    if best is None or best[0] >= whole:
+        return 0, 1                                               # not worth cutting
+    return best[1], best[2]
+
+
 def gemm_bf16_slices(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Tensor]:
     """x . weight^T as float32 partial products over K slices, [slices, M, N], whose sum in plane
     order is the product; None when this shape is not worth cutting (the caller then adds the
@@ -175,17 +207,16 @@ def gemm_bf16_slices(x: torch.Tensor, weight: torch.Tensor) -> Optional[torch.Te
     if not stream_ok:
         if not umma_ok or M <= 64:
             return None
-        # A short prompt (a few hundred rows): few 128 x 128 tiles and a long K leave most SMs idle
-        # (the 2048 x 8192 product of a 128-token prompt: 16 CTAs, 42 us), so K is cut until the
-        # items fill the SMs once, no slice shorter than 256 (the same product in 9 slices: 12 us).
-        tiles = -(-M // 128) * -(-N // 128)
-        splits = min(-(-K // 64) // 4, SM_COUNT // tiles)
+        # A short prompt (a few hundred rows): few tiles and a long K leave most SMs idle (the 2048 x
+        # 8192 product of a 128-token prompt: 16 CTAs, 42 us), so K is cut until the items fill the
+        # SMs once, no slice shorter than 256 (the same product in 9 slices: 12 us).
+        tile, splits = _sliced_plan(M, N, K)
         planes = lib.lrm_gemm_bf16_umma_slices(K, splits) if splits > 1 else 1
         if planes <= 1:
             return None
         out = torch.empty((planes, M, N), dtype=torch.float32, device=x.device)
         mark_status_dirty()
-        _done(lib.lrm_gemm_bf16_umma_rows(_ptr(x), _ptr(weight), _ptr(out), M, M, N, K, 4, 0, splits,
+        _done(lib.lrm_gemm_bf16_umma_rows(_ptr(x), _ptr(weight), _ptr(out), M, M, N, K, 4, tile, splits,
                                           _ptr(_status_word(x.device)), _stream()), "gemm_bf16_umma")
         return out
     use_umma, splits = False, 1

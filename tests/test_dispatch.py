@@ -95,3 +95,16 @@ def test_few_rows_plan():
     assert use and 2 <= slices <= 64
     assert plan(64, 2048, 8192, 2) == (False, 1)   # added in place: never cut (nothing meets by atomics)
     assert plan(24, 2048, 2048, 4) == (False, 1)   # a small one streams
+
+
+def test_sliced_plan_of_products_with_a_few_hundred_rows():
+    plan = gemm_dispatch._sliced_plan                 # (tile: 0 = 128 x 128, 1 = 128 x 256; K slices)
+    assert plan(128, 2048, 8192) == (0, 8)            # 16 tiles: eight slices fill 128 SMs, and the norm adds eight at a time
+    assert plan(512, 2048, 8192) == (1, 4)            # 32 wide tiles in four slices
+    assert plan(1024, 2048, 8192) == (1, 2)
+    assert plan(2048, 2048, 8192) == (0, 1)           # enough tiles: added in place, no planes
+    assert plan(768, 2048, 2048) == (0, 1)            # short K: the planes would cost more than the idle SMs
+    for M in (65, 100, 300, 900):
+        for N, K in ((2048, 2048), (2048, 8192), (4096, 14336), (520, 1000)):
+            tile, splits = plan(M, N, K)
+            assert tile in (0, 1) and 1 <= splits <= max(1, -(-K // 64) // 4)

@@ -681,7 +681,8 @@ def test_linear_bfloat16_few_rows_on_the_tensor_cores_and_on_the_streaming_kerne
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 300, 8192), (8, 2048, 8192), (8, 2048, 2048), (17, 300, 8192), (40, 2048, 8192),
-                                   (64, 520, 4104), (5, 64, 64), (128, 2048, 8192), (200, 520, 2048), (300, 300, 1000)])
+                                   (64, 520, 4104), (5, 64, 64), (128, 2048, 8192), (200, 520, 2048), (300, 300, 1000),
+                                   (512, 2048, 8192), (700, 1000, 4104)])
 def test_linear_slices_sum_to_the_product_in_a_fixed_order(ops, M, N, K):
     """A narrow product for the residual stream is cut into K slices stored as planes; whoever
     reads the stream next adds them in plane order (here the standalone kernel and the norm's
