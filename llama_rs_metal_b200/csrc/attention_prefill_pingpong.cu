@@ -32,7 +32,7 @@
 
 namespace {
 
-constexpr int BQ = 128, BKV = 128, UMMA_K = 16;
+constexpr int BQ = 128, UMMA_K = 16;
 // warps of a CTA with NQ query tiles: four softmax warps per tile, then the loader, then the issuer
 constexpr int threads_per_cta(int nq) { return (4 * nq + 2) * 32; }
 constexpr float kRescaleStep = 8.0f;                       // log2: O is rescaled when the maximum moved this far
@@ -40,24 +40,30 @@ constexpr float kRescaleStep = 8.0f;                       // log2: O is rescale
 enum : int { kStuckQ = 21, kStuckKV = 22, kStuckScores = 23, kStuckProbabilities = 24, kStuckOutput = 25,
              kStuckStage = 26, kMisaligned = 27 };
 
-// Key/value stages by head size (with head size 64 and one query tile two CTAs fit on an SM).
-template <int D> struct Shape {
-  static constexpr int kStages = D == 64 ? 3 : 2;
+// Key/value stages by head size and keys per tile (BKV): with head size 64, one query tile per CTA
+// and tiles of 64 keys, four CTAs fit on an SM (two stages and 128 columns of tensor memory each).
+template <int D, int BKV> struct Shape {
+  static constexpr int kStages = D == 64 && BKV == 128 ? 3 : 2;
+  static constexpr int kCtasPerSm = BKV == 64 ? 4 : 2;
 };
 
 // Shared memory (1024-byte aligned): Q [2][128][D] | stages of (K [128][D] | V [128][D]) |
 // barriers. A [128][D] tile with D = 128 is two [128][64] blocks of 16 KB one after the other
 // (a swizzle row is 128 bytes = 64 elements).
-template <int D, int NQ>
-__global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attention_prefill_pingpong_kernel(
+template <int D, int NQ, int BKV>
+__global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? Shape<D, BKV>::kCtasPerSm : 1)
+void attention_prefill_pingpong_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
     const int* __restrict__ cu_seqlens, int q_heads, int kv_heads, float scale_log2, int window,
     int* __restrict__ status) {
-  constexpr uint32_t TILE = BQ * D * 2;       // bytes of one [128][D] tile
-  constexpr uint32_t BLOCK = BQ * 64 * 2;     // bytes of one [128][64] block
+  constexpr uint32_t TILE = BQ * D * 2;       // bytes of one [128][D] query tile
+  constexpr uint32_t BLOCK = BQ * 64 * 2;     // bytes of one [128][64] block of it
+  constexpr uint32_t KV_TILE = BKV * D * 2;   // bytes of one [BKV][D] key or value tile
+  constexpr uint32_t KV_BLOCK = BKV * 64 * 2; // bytes of one [BKV][64] block of it
   constexpr int DB = D / 64;                  // 64-column blocks per tile
-  constexpr int STAGES = Shape<D>::kStages;
+  constexpr int STAGES = Shape<D, BKV>::kStages;
+  static_assert(BKV == 128 || (BKV == 64 && NQ == 1), "tiles of 64 keys go with one query tile per CTA");
   constexpr int kLoaderWarp = 4 * NQ, kIssuerWarp = 4 * NQ + 1;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   if ((smem_u32(smem_raw) & 1023u) != 0) {  // the swizzled tiles need it; give up rather than compute nonsense
@@ -65,8 +71,8 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
     return;
   }
   unsigned char* q_tiles = smem_raw;                        // [NQ] tiles
-  unsigned char* kv_tiles = q_tiles + NQ * TILE;            // stage s: K at s * 2 * TILE, V right after
-  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_tiles + STAGES * 2 * TILE);
+  unsigned char* kv_tiles = q_tiles + NQ * TILE;            // stage s: K at s * 2 * KV_TILE, V right after
+  uint64_t* bars = reinterpret_cast<uint64_t*>(kv_tiles + STAGES * 2 * KV_TILE);
   uint64_t* q_full = bars;
   uint64_t* kv_full = bars + 1;               // [STAGES]
   uint64_t* kv_free = kv_full + STAGES;       // [STAGES]
@@ -87,7 +93,7 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt_first = window > 0 ? max(0, q0 - window + 1) / BKV : 0;
   // key tiles per query tile: up to its diagonal tile; the second tile may not exist
-  const int n0 = q0 / BKV - kt_first + 1;
+  const int n0 = (q0 + BQ - 1) / BKV - kt_first + 1;
   const int n1 = NQ == 2 && q0 + BQ < len ? n0 + 1 : 0;
   const int n_tiles = max(n0, n1);
 
@@ -105,7 +111,8 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
     *bail = 0;
     mbar_fence_init();
   }
-  constexpr uint32_t kTmemColumns = NQ == 2 ? 512 : 256;  // a power of two that holds NQ (128 + D) columns
+  // a power of two that holds NQ (BKV + D) columns
+  constexpr uint32_t kTmemColumns = NQ == 2 ? 512 : (BKV + D <= 128 ? 128 : 256);
   if (warp == kIssuerWarp) {
     tmem_alloc(tmem_slot, kTmemColumns);
     tmem_relinquish();
@@ -115,7 +122,7 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tmem_o[2] = {tmem_base + NQ * 128, tmem_base + NQ * 128 + D};
+  const uint32_t tmem_o[2] = {tmem_base + NQ * BKV, tmem_base + NQ * BKV + D};
   // Barriers and tensor memory were set up while the kernel that produces q, k and v may still
   // have been running (sequence bounds are the step's own input); its results are read from here on.
   pdl_wait();
@@ -135,12 +142,12 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
           break;
         }
         const int row = start + (kt_first + j) * BKV;
-        unsigned char* kdst = kv_tiles + s * 2 * TILE;
-        mbar_expect_tx(kv_full + s, 2 * TILE);
+        unsigned char* kdst = kv_tiles + s * 2 * KV_TILE;
+        mbar_expect_tx(kv_full + s, 2 * KV_TILE);
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
-          tma_load_2d(kdst + db * BLOCK, &map_k, kv_full + s, kh * D + db * 64, row);
-          tma_load_2d(kdst + TILE + db * BLOCK, &map_v, kv_full + s, kh * D + db * 64, row);
+          tma_load_2d(kdst + db * KV_BLOCK, &map_k, kv_full + s, kh * D + db * 64, row);
+          tma_load_2d(kdst + KV_TILE + db * KV_BLOCK, &map_v, kv_full + s, kh * D + db * 64, row);
         }
       }
     }
@@ -150,19 +157,20 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
       constexpr uint32_t idesc_s = umma_idesc(BQ, BKV);            // both K-major
       constexpr uint32_t idesc_pv = umma_idesc(BQ, D, true);       // V is MN-major
       auto scores = [&](int i, int j) {  // S_i = Q_i K_j^T
-        const uint32_t qa = smem_u32(q_tiles + i * TILE), ka = smem_u32(kv_tiles + (j % STAGES) * 2 * TILE);
+        const uint32_t qa = smem_u32(q_tiles + i * TILE), ka = smem_u32(kv_tiles + (j % STAGES) * 2 * KV_TILE);
 #pragma unroll
-        for (int k = 0; k < D / UMMA_K; ++k) {
-          const uint32_t off = (k / 4) * BLOCK + (k % 4) * UMMA_K * 2;  // 64-column block, then 32 bytes per step
-          umma_bf16(tmem_s[i], smem_desc(qa + off), smem_desc(ka + off), idesc_s, k > 0 ? 1u : 0u);
+        for (int k = 0; k < D / UMMA_K; ++k) {  // 64-column block, then 32 bytes per step
+          const uint32_t step = (k % 4) * UMMA_K * 2;
+          umma_bf16(tmem_s[i], smem_desc(qa + (k / 4) * BLOCK + step), smem_desc(ka + (k / 4) * KV_BLOCK + step),
+                    idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(s_full + i);
       };
       auto weighted = [&](int i, int j) {  // O_i (+)= P_i V_j, P from tensor memory (8 columns per 16 keys)
-        const uint32_t va = smem_u32(kv_tiles + (j % STAGES) * 2 * TILE + TILE);
+        const uint32_t va = smem_u32(kv_tiles + (j % STAGES) * 2 * KV_TILE + KV_TILE);
 #pragma unroll
         for (int k = 0; k < BKV / UMMA_K; ++k)
-          umma_bf16_a_tmem(tmem_o[i], tmem_s[i] + k * (UMMA_K / 2), smem_desc(va + k * UMMA_K * 128, BLOCK),
+          umma_bf16_a_tmem(tmem_o[i], tmem_s[i] + k * (UMMA_K / 2), smem_desc(va + k * UMMA_K * 128, KV_BLOCK),
                            idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
       };
       bool ok = mbar_wait(q_full, 0, status, kStuckQ) && mbar_wait(kv_full, 0, status, kStuckKV);
@@ -225,15 +233,16 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
       // edge need the mask)
       float mx = -INFINITY;
       {
-        uint32_t sc[4][32];
+        constexpr int kChunks = BKV / 32;
+        uint32_t sc[kChunks][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_load32_async(my_s + c * 32, sc[c]);
+        for (int c = 0; c < kChunks; ++c) tmem_load32_async(my_s + c * 32, sc[c]);
         tmem_load_wait();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tmem_pin(sc[c]);
+        for (int c = 0; c < kChunks; ++c) tmem_pin(sc[c]);
         if (edge) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < kChunks; ++c)
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const int key = key0 + c * 32 + e;
@@ -241,7 +250,7 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
             }
         } else {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
+          for (int c = 0; c < kChunks; ++c)
 #pragma unroll
             for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(sc[c][e]));
         }
@@ -274,10 +283,10 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
       uint32_t sc[2][32];
       tmem_load32_async(my_s, sc[0]);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < BKV / 32; ++c) {
         tmem_load_wait();
         tmem_pin(sc[c & 1]);
-        if (c + 1 < 4) tmem_load32_async(my_s + (c + 1) * 32, sc[(c + 1) & 1]);
+        if (c + 1 < BKV / 32) tmem_load32_async(my_s + (c + 1) * 32, sc[(c + 1) & 1]);
         uint32_t packed[16];
         if (edge) {
 #pragma unroll
@@ -339,7 +348,7 @@ __global__ __launch_bounds__(threads_per_cta(NQ), NQ == 1 ? 2 : 1) void attentio
   if (warp == kIssuerWarp) tmem_dealloc(tmem_base, kTmemColumns);
 }
 
-template <int D, int NQ>
+template <int D, int NQ, int BKV = 128>
 int launch(const void* q, const void* k, const void* v, void* out, const int* cu_seqlens, int tokens,
            int seqs, int max_seq_len, int q_heads, int kv_heads, float scale, int window, int* status,
            cudaStream_t stream) {
@@ -348,8 +357,8 @@ int launch(const void* q, const void* k, const void* v, void* out, const int* cu
       !make_map_bf16(&map_k, k, tokens, static_cast<long long>(kv_heads) * D, BKV) ||
       !make_map_bf16(&map_v, v, tokens, static_cast<long long>(kv_heads) * D, BKV))
     return LRM_UNSUPPORTED;
-  constexpr int smem = (NQ + 2 * Shape<D>::kStages) * BQ * D * 2 + 256;
-  auto kernel = attention_prefill_pingpong_kernel<D, NQ>;
+  constexpr int smem = NQ * BQ * D * 2 + 2 * Shape<D, BKV>::kStages * BKV * D * 2 + 256;
+  auto kernel = attention_prefill_pingpong_kernel<D, NQ, BKV>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return static_cast<int>(e);
   const int pairs = (max_seq_len + NQ * BQ - 1) / (NQ * BQ);
@@ -380,10 +389,17 @@ LRM_API int lrm_attention_prefill_pingpong(const void* q, const void* k, const v
       reinterpret_cast<uintptr_t>(v) % 16 || reinterpret_cast<uintptr_t>(out) % 16)
     return LRM_UNSUPPORTED;
   // Two query tiles per CTA where the head is wide (the tensor core then has work to hide a tile's
-  // softmax under); with head size 64 one tile per CTA and two CTAs per SM (measured: the other
-  // two combinations are slower at every length).
+  // softmax under). With head size 64 one query tile per CTA, key tiles of 64 and four CTAs per SM:
+  // the kernel is bound by the latency of its chain of dependent steps per key tile, and four
+  // chains per SM hide more of it than two (measured against key tiles of 128 and two CTAs per SM:
+  // 681 against 585 TFLOP/s at 32,768 tokens, 125 against 153 us at 4,096, four prompts of 512
+  // tokens 20 against 29 us; two query tiles per CTA are slower at every length). Cutting a long
+  // query tile's key tiles among several CTAs that meet through global memory (the last to arrive
+  // adding the partials up) was measured as well: a single prompt of 2,048 tokens, whose longest
+  // chain of 32 key tiles sets its time, took 67 us instead of 51 with chains of at most 17, and
+  // more the shorter the chains.
   if (d == 64)
-    return launch<64, 1>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
+    return launch<64, 1, 64>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
                          status, stream);
   if (d == 128)
     return launch<128, 2>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,

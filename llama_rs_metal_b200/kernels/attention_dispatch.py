@@ -45,13 +45,17 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
             and lib.lrm_attention_prefill_umma_supports(d)):
         from . import gemm_dispatch
         gemm_dispatch.mark_status_dirty()
-        # Two tcgen05 kernels. The one that keeps probabilities and output in tensor memory and lets
-        # two query tiles take turns wins on long prompts (measured at 32 heads: head size 128 from
-        # 2,048 tokens on, 66 against 90 us, 1,023 against 585 TFLOP/s at 32,768; head size 64 from
-        # 4,096 on, 585 against 530 TFLOP/s at 32,768); the older one, with twice the threads per
-        # row and more, smaller CTAs, on short ones.
-        longest = max_seq_len
-        pingpong = longest >= (1536 if d == 128 else 3072)
+        # Two tcgen05 kernels. The one that keeps probabilities and output in tensor memory wins on
+        # long prompts and on batches of prompts: at head size 128 (two query tiles per CTA taking
+        # turns) from 1,536 tokens on (2,048 tokens 63 against 87 us, 1,023 against 585 TFLOP/s at
+        # 32,768); at head size 64 (four CTAs per SM on key tiles of 64) beyond 2,048 tokens (3,072
+        # tokens 78 against 100 us, 681 against 534 TFLOP/s at 32,768) and whenever several prompts
+        # are packed (four of 512 tokens 20 against 29 us, eight of 128 tokens 9.5 against 11.1). A
+        # single short prompt is bound by the chain of key tiles of its last query tile, which the
+        # older kernel, with two threads per row, walks a little faster (1,024 tokens 24 against 26 us).
+        # (several prompts: the packed tokens are well more than the longest prompt; a short prompt
+        # filled up to whole rows with a few tokens of padding does not count)
+        pingpong = max_seq_len >= 1536 if d == 128 else (max_seq_len > 2048 or 4 * T >= 5 * max_seq_len)
         if prefill_kernel is not None:
             pingpong = prefill_kernel == "pingpong"
         if pingpong:
