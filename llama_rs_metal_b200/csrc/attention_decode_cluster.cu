@@ -31,7 +31,8 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kStages = 3;
+// Pages of the cp.async ring per CTA.
+template <int D> constexpr int stages_of() { return D == 128 ? 2 : 3; }
 
 // The cluster's barrier in two halves: everybody arrives early and waits where it first needs the
 // others (all threads of every CTA execute both).
@@ -68,8 +69,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
     __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ dest_rows,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ page_table, int table_stride,
     const int* __restrict__ slots, const int* __restrict__ kv_lens, int q_heads, int kv_heads,
-    int row_groups, float scale_log2) {
-  constexpr int STRIDE = D + 8, TILE = kTile * STRIDE, PART = D + 2;
+    int row_groups, float scale_log2, const int* __restrict__ order) {
+  constexpr int STRIDE = D + 8, TILE = kTile * STRIDE, PART = D + 2, kStages = stages_of<D>();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ float cs_tab[D / 2], sn_tab[D / 2];
   __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -86,7 +87,8 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
   const int pair = blockIdx.x / n_ranks;
   const int rg = pair % row_groups;
   const int kh = (pair / row_groups) % kv_heads;
-  const int b = pair / (row_groups * kv_heads);
+  const int b_slot = pair / (row_groups * kv_heads);
+  const int b = order != nullptr ? order[b_slot] : b_slot;  // sequences in the order given (longest first)
   const int group = q_heads / kv_heads;
   const int head0 = kh * group + 16 * rg;          // first query head of this cluster
   const int rows = min(16, group - 16 * rg);       // query heads it owns
@@ -328,7 +330,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_cluster_kernel(
 // (n CTAs x (ceil(runs / n) x 128 accumulators + 16 rows x (max, mass))), for up to `rows` query
 // heads per kv head in a CTA.
 template <int D> int smem_bytes(int cluster, int rows) {
-  const int ring = 2 * kStages * kTile * (D + 8) * 2;
+  const int ring = 2 * stages_of<D>() * kTile * (D + 8) * 2;
   if (cluster <= 1) return ring;
   const int runs = (rows * D + 127) / 128, runs_each = (runs + cluster - 1) / cluster;
   return ring + cluster * (runs_each * 128 + 32) * 4;
@@ -391,7 +393,7 @@ template <int D> int launch(const void* qkv, const int* positions, const float* 
                             void* k_pages, void* v_pages, const int* dest_rows, void* out,
                             const int* page_table, int table_stride, const int* slots, const int* kv_lens,
                             int seqs, int q_heads, int kv_heads, float scale, int cluster,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, const int* order = nullptr) {
   int code = prepare<D>(cluster);
   if (code != 0) return code;
   const int group = q_heads / kv_heads, row_groups = (group + 15) / 16;
@@ -402,7 +404,7 @@ template <int D> int launch(const void* qkv, const int* positions, const float* 
       &config, attention_decode_cluster_kernel<D>, static_cast<const __nv_bfloat16*>(qkv), positions,
       inv_freq, rotary, static_cast<__nv_bfloat16*>(k_pages), static_cast<__nv_bfloat16*>(v_pages),
       dest_rows, static_cast<__nv_bfloat16*>(out), page_table, table_stride, slots, kv_lens, q_heads,
-      kv_heads, row_groups, scale * 1.4426950408889634f);
+      kv_heads, row_groups, scale * 1.4426950408889634f, order);
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }
 
@@ -427,12 +429,14 @@ LRM_API int lrm_attention_decode_cluster_resident(int head_dim, int cluster, int
 // qkv: [seqs, (q_heads + 2 kv_heads) * d] bfloat16, this step's fused projection, unrotated.
 // positions, dest_rows, slots, kv_lens: int32 [seqs]; kv_lens counts the new token;
 // dest_rows[b] = page * 64 + row where the new key/value row is stored. out: [seqs, q_heads, d].
+// order: int32 [seqs] or nullptr: the sequences in the order their clusters are to start (the longest
+// first: clusters beyond what the device holds at once then are those of the short sequences).
 LRM_API int lrm_attention_decode_cluster(const void* qkv, const int* positions, const float* inv_freq,
                                          int rotary, void* k_pages, void* v_pages, const int* dest_rows,
                                          void* out, const int* page_table, int table_stride,
                                          const int* slots, const int* kv_lens, int seqs, int q_heads,
                                          int kv_heads, int head_dim, int page_size, float scale,
-                                         int cluster, cudaStream_t stream) {
+                                         int cluster, const int* order, cudaStream_t stream) {
   if (seqs <= 0) return 0;
   if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || cluster < 1 || cluster > 16)
     return LRM_BAD_ARGUMENT;
@@ -441,7 +445,7 @@ LRM_API int lrm_attention_decode_cluster(const void* qkv, const int* positions, 
 #define LRM_CASE(DIM)                                                                                  \
   if (head_dim == DIM)                                                                                 \
     return launch<DIM>(qkv, positions, inv_freq, rotary, k_pages, v_pages, dest_rows, out, page_table, \
-                       table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, cluster, stream);
+                       table_stride, slots, kv_lens, seqs, q_heads, kv_heads, scale, cluster, stream, order);
   LRM_CASE(32)
   LRM_CASE(64)
   LRM_CASE(128)

@@ -53,6 +53,7 @@ class StepContext:
     # `next_folds_pending` tells a block whether whatever reads the stream after it does so.
     pending: Any = None
     scratch: Dict[Any, Any] = field(default_factory=dict)  # what kernels' dispatchers keep for the length of a step
+    kv_fill: int = 4  # mean sequence length in quarters of the longest, rounded up (launch geometry only)
     may_defer: bool = False
     next_folds_pending: bool = False
 
@@ -120,14 +121,14 @@ def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_
 
 
 def context_over(dev: torch.Tensor, runtime: Runtime, phase: str, T: int, B: int, n_want: int,
-                 max_seq_len: int, max_kv_len: int, groups: int = 0) -> StepContext:
+                 max_seq_len: int, max_kv_len: int, groups: int = 0, kv_fill: int = 4) -> StepContext:
     """A StepContext whose arrays are slices of `dev`, a device copy of pack_host's buffer."""
     o = 3 * T
     base = o + 3 * B + 1 + n_want
     return StepContext(
         dest_rows=[dev[base + g * T:base + (g + 1) * T] for g in range(groups)],
         runtime=runtime, phase=phase, num_tokens=T, num_seqs=B, max_seq_len=max_seq_len,
-        max_kv_len=max_kv_len,
+        max_kv_len=max_kv_len, kv_fill=kv_fill,
         token_ids=dev[:T], positions=dev[T:2 * T], seq_of_token=dev[2 * T:3 * T],
         cu_seqlens=dev[o:o + B + 1], slots=dev[o + B + 1:o + 2 * B + 1],
         kv_lens=dev[o + 2 * B + 1:o + 3 * B + 1], wanted_rows=dev[o + 3 * B + 1:o + 3 * B + 1 + n_want])

@@ -72,6 +72,17 @@ def _tell_profiler(before: Sequence[int], counts: Sequence[int], phase: str = ""
         profile.hints["pairs"] = float(sum(n * b + n * (n + 1) // 2 for b, n in zip(before, counts)))
 
 
+def fill_class(lengths) -> int:
+    """How unequal the sequences of a decode step are: their mean length in quarters of the longest,
+    rounded up (4: about equal, 1: one long sequence among short ones). Decode attention sizes its
+    clusters by it; it is part of a captured step's geometry."""
+    longest = int(max(lengths)) if len(lengths) else 0
+    if longest <= 0:
+        return 4
+    mean = float(sum(int(n) for n in lengths)) / len(lengths)
+    return max(1, min(4, -(-int(4 * mean) // longest)))
+
+
 def length_bucket(n: int) -> int:
     """Launch geometry of decode attention depends on the longest sequence only through this."""
     bucket = 256
@@ -90,7 +101,7 @@ class _StepGraph:
     RING = 4
 
     def __init__(self, runner: "StepRunner", phase: str, tokens: int, seqs: int, wanted: int, max_seq_len: int,
-                 max_kv_len: int, choice=None):
+                 max_kv_len: int, choice=None, kv_fill: int = 4):
         rt = runner.runtime
         self.batch, self.choice = seqs, choice
         groups = len(runner.cache.kv_groups)
@@ -100,7 +111,7 @@ class _StepGraph:
         total = self.keys_at + 2 * max(wanted, 1)
         self.static = torch.zeros(total, dtype=torch.int32, device=rt.device)
         self.keys = self.static[self.keys_at:self.keys_at + 2 * wanted].view(torch.int64)
-        self.ctx = context_over(self.static, rt, phase, tokens, seqs, wanted, max_seq_len, max_kv_len, groups)
+        self.ctx = context_over(self.static, rt, phase, tokens, seqs, wanted, max_seq_len, max_kv_len, groups, kv_fill)
         self.pinned = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.ids: Optional[torch.Tensor] = None  # int32 [B]: the chosen tokens (graphs with a `choice`)
         self.events = [torch.cuda.Event() for _ in range(self.RING)]
@@ -243,8 +254,10 @@ class StepRunner:
         host, T, B, n_want, max_seq_len, max_kv_len = pack_host(entries, before, dest_rows, pad_to)
         if pad_to:  # the geometry of every step that fills the same rows
             max_seq_len = max_kv_len = -(-max_seq_len // 64) * 64
+        kv_fill = 4
         if phase == "decode":  # the geometry a captured step would have
             max_kv_len = length_bucket(max_kv_len)
+            kv_fill = fill_class([b + n for b, n in zip(before, counts)])
         choice, keys = None, None
         if picker is not None:
             choice = (picker.temperature, picker.seed)
@@ -252,7 +265,7 @@ class StepRunner:
                 if len(picker.keys) != n_want:
                     raise InvalidError("one sampling key per wanted place")
                 keys = picker.keys
-        key = (phase, T, B, n_want, max_seq_len, max_kv_len, choice)
+        key = (phase, T, B, n_want, max_seq_len, max_kv_len, choice, kv_fill)
         if pad_to and self.use_graphs and key in self._prompt_shapes_seen:
             graph = self._graph_of(key)  # a geometry that came before: captured once, replayed since
             graph.upload(host, keys)
@@ -266,7 +279,7 @@ class StepRunner:
             dev = torch.from_numpy(host).pin_memory().to(rt.device, non_blocking=True)
         else:
             dev = torch.from_numpy(host).to(rt.device)
-        ctx = context_over(dev, rt, phase, T, B, n_want, max_seq_len, max_kv_len, len(dest_rows))
+        ctx = context_over(dev, rt, phase, T, B, n_want, max_seq_len, max_kv_len, len(dest_rows), kv_fill)
         start = ops.launch_count()
         if picker is None:
             result = self.model.forward(ctx, self.cache)
@@ -340,7 +353,7 @@ class StepRunner:
             return None
         host, before = prepared
         try:
-            logits = self._replay(host, batch, int(before.max()) + 1, wanted, borrow)
+            logits = self._replay(host, batch, int(before.max()) + 1, wanted, borrow, fill_class(before + 1))
         except Exception:
             self.poisoned = True
             raise
@@ -388,7 +401,7 @@ class StepRunner:
         host, before = prepared
         try:
             choice = (picker.temperature, picker.seed) if hasattr(picker, "temperature") else None
-            graph = self._graph_for(batch, int(before.max()) + 1, choice)
+            graph = self._graph_for(batch, int(before.max()) + 1, choice, fill_class(before + 1))
             graph.upload(host, picker.keys if choice is not None and picker.temperature is not None else None)
             if tokens is None:
                 graph.static[:batch].copy_(previous.device_ids)  # the ids chosen by the step before
@@ -417,11 +430,11 @@ class StepRunner:
         all_rows = [StepEntry(e.slot, e.tokens, (0,)) for e in entries]
         host, _, _, _, _, max_kv_len = pack_host(all_rows, before, dest_rows)
         wanted = [b for b, e in enumerate(entries) for _ in e.want]
-        return self._replay(host, batch, max_kv_len, wanted, borrow)
+        return self._replay(host, batch, max_kv_len, wanted, borrow, fill_class([b + 1 for b in before]))
 
     def _replay(self, host: np.ndarray, batch: int, max_kv_len: int, wanted: List[int],
-                borrow: bool) -> torch.Tensor:
-        graph = self._graph_for(batch, max_kv_len)
+                borrow: bool, kv_fill: int = 4) -> torch.Tensor:
+        graph = self._graph_for(batch, max_kv_len, None, kv_fill)
         graph.upload(host)
         self._launch(graph)
         logits = graph.logits
@@ -430,13 +443,14 @@ class StepRunner:
             return logits.index_select(0, index)
         return logits if borrow else logits.clone()
 
-    def _graph_for(self, batch: int, max_kv_len: int, choice=None) -> _StepGraph:
+    def _graph_for(self, batch: int, max_kv_len: int, choice=None, kv_fill: int = 4) -> _StepGraph:
         bucket = length_bucket(max_kv_len)
-        return self._graph_of(("decode", batch, batch, batch, 1, bucket, choice))
+        return self._graph_of(("decode", batch, batch, batch, 1, bucket, choice, kv_fill))
 
     def _graph_of(self, key: Tuple) -> _StepGraph:
         """The captured step of geometry `key` = (phase, tokens, sequences, wanted rows, longest
-        portion, longest sequence, how tokens are chosen); made on first use."""
+        portion, longest sequence, how tokens are chosen, how unequal the sequences are); made on
+        first use."""
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = _StepGraph(self, *key)

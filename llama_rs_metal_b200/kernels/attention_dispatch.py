@@ -152,7 +152,8 @@ def decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, wi
             and bool(library.load().lrm_attention_decode_cluster_supports(head_dim, page_size, rotary)))
 
 
-def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> bool:
+def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int,
+                         fill: int = 4) -> bool:
     """Whether the one-launch cluster kernel or the separate kernels are the faster way through a
     decode step's attention. A cluster has at most 16 CTAs, and a CTA keeps two pages in flight,
     which is worth 16-20 GB/s at head size 64 (25-30 at 128): a few sequences with a long context leave the
@@ -168,7 +169,7 @@ def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, ma
     if force_cluster_size is not None:
         return True
     pages = max(1, -(-max_kv_len // 64))
-    cluster = decode_cluster_size(seqs, kv_heads, group, head_dim, max_kv_len)
+    cluster = decode_cluster_size(seqs, kv_heads, group, head_dim, max_kv_len, fill)
     pairs = seqs * kv_heads * -(-group // 16)
     page_bytes = 4.0 * 64 * head_dim                       # a page of keys and one of values
     data = pairs * pages * page_bytes                      # bytes; rates below in bytes per us
@@ -181,33 +182,41 @@ def decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_dim: int, ma
 MAX_CLUSTER = 14  # clusters of 15 and 16 CTAs were measured slower as soon as a few hundred CTAs run
 
 
-def decode_cluster_size(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int) -> int:
+def decode_cluster_size(seqs: int, kv_heads: int, group: int, head_dim: int, max_kv_len: int, fill: int = 4) -> int:
     """CTAs per (sequence, kv head): any size up to MAX_CLUSTER (not only powers of two). Measured
     over batches of 1-32 and 600-8,000 keys, the kernel is fastest with about 400 CTAs in all at
     head size 64 (under 3 per SM, of the 4 that fit), about 500 when each walks many pages; more
-    than fit at once cost a second round."""
+    than fit at once cost a second round. `fill`: the sequences' mean length in quarters of the
+    longest (4: about equal). Unequal sequences are handed out longest first, so the clusters that
+    wait for room are those of the short sequences, and a size more pays: 16 sequences of 64-4,096
+    keys, 1B shape: 1.20 ms per step with clusters of 4 against 1.25 with 3; 3B shape: 3.05-3.06 with
+    5 or 4 against 3.16 with 3 (and 1.24-1.27 / 3.18 without the ordering, whatever the size)."""
     if force_cluster_size is not None:
         return force_cluster_size
     clusters = seqs * kv_heads * -(-group // 16)
     pages = max(1, -(-max_kv_len // 64))
-    slots = (CTAS_PER_SM if head_dim <= 64 else 2) * SM_COUNT
+    slots = (CTAS_PER_SM if head_dim <= 64 else 3) * SM_COUNT
     size = max(1, min(int(0.68 * slots / clusters + 0.5), pages, MAX_CLUSTER))
     if pages >= 16 * size:  # long rows of pages per CTA: bandwidth counts more than balance
         size = max(1, min(int(0.85 * slots / clusters + 0.5), pages, MAX_CLUSTER))
     while size > 1 and clusters > _resident_clusters(head_dim, size, min(group, 16)):
         size -= 1
+    if fill < 4 and seqs > 1 and size < min(pages, MAX_CLUSTER):
+        # as many more clusters may wait their turn as the short sequences leave room for
+        if clusters * fill <= 4 * _resident_clusters(head_dim, size + 1, min(group, 16)):
+            size += 1
     return size
 
 
 def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slots, kv_lens, max_kv_len: int,
-                 q_heads: int, scale: float) -> None:
+                 q_heads: int, scale: float, order=None, fill: int = 4) -> None:
     B = qkv.shape[0]
     d = kv.head_dim
-    cluster = decode_cluster_size(B, kv.kv_heads, q_heads // kv.kv_heads, d, max_kv_len)
+    cluster = decode_cluster_size(B, kv.kv_heads, q_heads // kv.kv_heads, d, max_kv_len, fill if order is not None else 4)
     _done(library.load().lrm_attention_decode_cluster(
         _ptr(qkv), _ptr(positions), _ptr(inv_freq), rotary, _ptr(kv.k), _ptr(kv.v), _ptr(dest_rows), _ptr(out),
         _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots), _ptr(kv_lens), B, q_heads, kv.kv_heads, d,
-        kv.page_size, ctypes.c_float(scale), cluster, _stream()), "attention_decode_cluster")
+        kv.page_size, ctypes.c_float(scale), cluster, _ptr(order), _stream()), "attention_decode_cluster")
 
 
 # --------------------------------------------------------------------------- one call for a mixer
@@ -249,11 +258,14 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
                 and decode_fused_supported(projected.dtype, head_dim, cache.page_size, width,
                                            window or cache.window)
                 and decode_prefers_fused(projected.shape[0], kv_heads, q_heads // kv_heads, head_dim,
-                                         ctx.max_kv_len)):
+                                         ctx.max_kv_len, ctx.kv_fill)):
             # rotation, cache write, attention and the merge of the splits in one launch
+            order = ctx.scratch.get("longest_first")   # once per step: every layer reads the same lengths
+            if order is None and projected.shape[0] > 1:
+                order = ctx.scratch["longest_first"] = ops.order_by_length(ctx.kv_lens)
             return ops.attention_decode_fused(projected, q_heads, inv_freq, width, ctx.positions, cache,
                                               ctx.dest_rows[cache.group], ctx.slots, ctx.kv_lens,
-                                              ctx.max_kv_len, scale)
+                                              ctx.max_kv_len, scale, order, ctx.kv_fill)
         prefill = phase == "prefill"
         q, k, v = ops.rope_store(projected, q_heads, kv_heads, head_dim, inv_freq, width, ctx.positions,
                                  kv=cache, dest_rows=ctx.dest_rows[cache.group] if cache is not None else None,

@@ -387,6 +387,14 @@ def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token
     return out
 
 
+def order_by_length(lengths: torch.Tensor) -> torch.Tensor:
+    """int32 [n]: indices of `lengths` from the largest to the smallest (ties: lower index first)."""
+    _check(lengths, "lengths", torch.int32, 1)
+    order = torch.empty_like(lengths)
+    _done(_lib().lrm_order_by_length(_ptr(lengths), _ptr(order), lengths.numel(), _stream()), "order_by_length")
+    return order
+
+
 def attention_decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, window) -> bool:
     from . import attention_dispatch
     return attention_dispatch.decode_fused_supported(dtype, head_dim, page_size, rotary, window)
@@ -400,10 +408,13 @@ def attention_decode_prefers_fused(seqs: int, kv_heads: int, group: int, head_di
 
 def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[torch.Tensor], rotary: int,
                            positions: torch.Tensor, kv, dest_rows: torch.Tensor, slots: torch.Tensor,
-                           kv_lens: torch.Tensor, max_kv_len: int, scale: float) -> torch.Tensor:
+                           kv_lens: torch.Tensor, max_kv_len: int, scale: float,
+                           order: Optional[torch.Tensor] = None, fill: int = 4) -> torch.Tensor:
     """A decode step's attention from its fused, unrotated [B, (Hq+2Hk)*d] projection: rotates q and
     the new k, stores the new k and v at `dest_rows`, attends over the cache (kv_lens counts the new
-    token) and merges the splits, in one launch. -> [B, Hq*d]"""
+    token) and merges the splits, in one launch. -> [B, Hq*d]. `order` (order_by_length(kv_lens)):
+    the sequences' work is handed out longest first, which matters when lengths are unequal;
+    `fill`: their mean length in quarters of the longest (launch geometry only)."""
     _check(qkv, "qkv", torch.bfloat16, 2)
     d, Hk = kv.head_dim, kv.kv_heads
     if qkv.shape[1] != (q_heads + 2 * Hk) * d or q_heads % Hk:
@@ -428,8 +439,12 @@ def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[t
         raise UnsupportedError("attention_decode_fused: geometry not supported; use rope_store and attention_decode")
     out = _activation(B, q_heads * d, qkv.dtype, qkv.device)
     from . import attention_dispatch
+    if order is not None:
+        _check(order, "order", torch.int32, 1)
+        if order.numel() != B:
+            raise InvalidError("attention_decode_fused: one entry of order per sequence")
     attention_dispatch.decode_fused(qkv, positions, inv_freq, rotary, kv, dest_rows, out, slots, kv_lens,
-                                    max_kv_len, q_heads, scale)
+                                    max_kv_len, q_heads, scale, order, fill)
     return out
 
 

@@ -108,3 +108,15 @@ def test_sliced_plan_of_products_with_a_few_hundred_rows():
         for N, K in ((2048, 2048), (2048, 8192), (4096, 14336), (520, 1000)):
             tile, splits = plan(M, N, K)
             assert tile in (0, 1) and 1 <= splits <= max(1, -(-K // 64) // 4)
+
+
+def test_unequal_sequences_get_a_cluster_size_more():
+    from llama_rs_metal_b200.engine.step import fill_class
+    assert fill_class([100, 100, 99]) == 4 and fill_class([4000, 2000, 2100]) == 3
+    assert fill_class([4000, 100, 100, 100]) == 2 and fill_class([8000] + [10] * 31) == 1
+    assert fill_class([]) == 4 and fill_class([7]) == 4
+    size = attention_dispatch.decode_cluster_size
+    assert size(16, 8, 4, 64, 4096) == 3 and size(16, 8, 4, 64, 4096, fill=3) == 4   # 512 CTAs: some wait their turn
+    assert size(8, 8, 4, 64, 4096, fill=3) == 7
+    assert size(1, 8, 4, 64, 4096, fill=1) == 14                                        # one sequence is never unequal
+    assert size(64, 8, 4, 64, 4096, fill=2) == 1                                        # 1,024 CTAs would be two full rounds
