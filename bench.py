@@ -334,7 +334,7 @@ def main() -> int:
         done = time.perf_counter()
         first = stamps[batch - 1]           # every request's first token (the prefill's) is out
         groups = len(session.cache.kv_groups)
-        return batch * steps / (done - first), ((7 + groups) * batch + 1) * 4, batch * 4
+        return batch * steps / (done - first), ((8 + groups) * batch + 1) * 4, batch * 4
 
     def time_prefill(tokens, reps=9):
         session = model.session(context=context, max_batch=1)

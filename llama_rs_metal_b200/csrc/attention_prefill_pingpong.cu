@@ -44,7 +44,7 @@ enum : int { kStuckQ = 21, kStuckKV = 22, kStuckScores = 23, kStuckProbabilities
 // and tiles of 64 keys, four CTAs fit on an SM (two stages and 128 columns of tensor memory each).
 template <int D, int BKV> struct Shape {
   static constexpr int kStages = D == 64 && BKV == 128 ? 3 : 2;
-  static constexpr int kCtasPerSm = BKV == 64 ? 4 : 2;
+  static constexpr int kCtasPerSm = BKV == 64 && D == 64 ? 4 : 2;
 };
 
 // Shared memory (1024-byte aligned): Q [2][128][D] | stages of (K [128][D] | V [128][D]) |
@@ -401,6 +401,12 @@ LRM_API int lrm_attention_prefill_pingpong(const void* q, const void* k, const v
   if (d == 64)
     return launch<64, 1, 64>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
                          status, stream);
+  // Head size 128: up to 2,304 tokens one query tile per CTA, key tiles of 64 and two CTAs per SM
+  // (four prompts of 512 tokens 33 against 42 us, one of 2,048 tokens 61 against 63); beyond, two
+  // query tiles per CTA taking turns (954 against 790 TFLOP/s at 32,768 tokens).
+  if (d == 128 && max_seq_len <= 2304)
+    return launch<128, 1, 64>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
+                              status, stream);
   if (d == 128)
     return launch<128, 2>(q, k, v, out, cu_seqlens, tokens, seqs, max_seq_len, q_heads, kv_heads, scale, window,
                           status, stream);

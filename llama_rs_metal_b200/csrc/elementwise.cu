@@ -112,26 +112,3 @@ LRM_API int lrm_cast(const void* src, int src_dtype, void* dst, int dst_dtype, l
   return 0;
 }
 
-// order[r] = the index of the r-th longest entry of `lengths` (ties: the lower index first). Decode
-// attention hands its sequences out in this order, so that the longest ones start first and the
-// short ones fill the gaps they leave. n^2 comparisons: a batch has at most a few hundred entries.
-__global__ void order_by_length_kernel(const int* __restrict__ lengths, int* __restrict__ order, int n) {
-  pdl_trigger();
-  pdl_wait();
-  const int b = blockIdx.x * blockDim.x + threadIdx.x;
-  if (b >= n) return;
-  const int mine = lengths[b];
-  int rank = 0;
-  for (int j = 0; j < n; ++j) {
-    const int other = lengths[j];
-    rank += (other > mine || (other == mine && j < b)) ? 1 : 0;
-  }
-  order[rank] = b;
-}
-
-LRM_API int lrm_order_by_length(const int* lengths, int* order, int n, cudaStream_t stream) {
-  if (n <= 0) return 0;
-  LRM_LAUNCH(order_by_length_kernel, dim3((n + 127) / 128), 128, 0, stream, lengths, order, n);
-  return 0;
-}
-

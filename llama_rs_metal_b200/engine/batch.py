@@ -2,7 +2,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Sequence, Tuple
+from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -54,6 +54,9 @@ class StepContext:
     pending: Any = None
     scratch: Dict[Any, Any] = field(default_factory=dict)  # what kernels' dispatchers keep for the length of a step
     kv_fill: int = 4  # mean sequence length in quarters of the longest, rounded up (launch geometry only)
+    # int32 [B]: the sequences by falling length after this step (ties by number), brought with the
+    # step's other arrays so that a kernel may read it before it waits for the kernels ahead of it
+    longest_first: Optional[torch.Tensor] = None
     may_defer: bool = False
     next_folds_pending: bool = False
 
@@ -74,7 +77,11 @@ class StepContext:
 def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_rows=(), pad_to: int = 0):
     """The step's int32 arrays in one host buffer, laid out as
     [token ids T | positions T | sequence of token T | cu_seqlens B+1 | slots B | kv lengths B |
-     wanted rows n | destination rows T per key/value group].
+     sequences longest first B | wanted rows n | destination rows T per key/value group].
+
+    The order by length is made here, on the host, because kernels read it before they wait for
+    the kernels ahead of them: only what a copy brought before the step's first kernel is safe
+    to read there.
 
     With `pad_to` > the step's tokens (a prompt step only) the step is filled up to that many
     rows with a sequence of padding of its own: token 0 at positions 0, 1, ..., stored nowhere
@@ -86,15 +93,15 @@ def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_
     padding = max(0, pad_to - real_T)
     T, B = real_T + padding, real_B + (1 if padding else 0)
     n_want = sum(len(e.want) for e in entries)
-    base = 3 * T + (B + 1) + 2 * B + n_want
+    base = 3 * T + (B + 1) + 3 * B + n_want
     host = np.empty(base + T * len(dest_rows), dtype=np.int32)
     for g, rows in enumerate(dest_rows):
         host[base + g * T:base + g * T + real_T] = rows
         host[base + g * T + real_T:base + (g + 1) * T] = -1
     token_ids, positions, seq_of = host[:T], host[T:2 * T], host[2 * T:3 * T]
     o = 3 * T
-    cu, slots, kv_lens, wanted = host[o:o + B + 1], host[o + B + 1:o + 2 * B + 1], \
-        host[o + 2 * B + 1:o + 3 * B + 1], host[o + 3 * B + 1:base]
+    cu, slots, kv_lens, longest_first, wanted = host[o:o + B + 1], host[o + B + 1:o + 2 * B + 1], \
+        host[o + 2 * B + 1:o + 3 * B + 1], host[o + 3 * B + 1:o + 4 * B + 1], host[o + 4 * B + 1:base]
     if padding:
         token_ids[real_T:] = 0
         positions[real_T:] = np.arange(padding, dtype=np.int32)
@@ -117,6 +124,7 @@ def pack_host(entries: Sequence[StepEntry], lengths_before: Sequence[int], dest_
             w += 1
         at += n
         cu[b + 1] = at
+    longest_first[:] = np.argsort(-kv_lens, kind="stable")
     return host, T, B, n_want, max(counts), int(kv_lens.max())
 
 
@@ -124,14 +132,15 @@ def context_over(dev: torch.Tensor, runtime: Runtime, phase: str, T: int, B: int
                  max_seq_len: int, max_kv_len: int, groups: int = 0, kv_fill: int = 4) -> StepContext:
     """A StepContext whose arrays are slices of `dev`, a device copy of pack_host's buffer."""
     o = 3 * T
-    base = o + 3 * B + 1 + n_want
+    base = o + 4 * B + 1 + n_want
     return StepContext(
         dest_rows=[dev[base + g * T:base + (g + 1) * T] for g in range(groups)],
         runtime=runtime, phase=phase, num_tokens=T, num_seqs=B, max_seq_len=max_seq_len,
         max_kv_len=max_kv_len, kv_fill=kv_fill,
         token_ids=dev[:T], positions=dev[T:2 * T], seq_of_token=dev[2 * T:3 * T],
         cu_seqlens=dev[o:o + B + 1], slots=dev[o + B + 1:o + 2 * B + 1],
-        kv_lens=dev[o + 2 * B + 1:o + 3 * B + 1], wanted_rows=dev[o + 3 * B + 1:o + 3 * B + 1 + n_want])
+        kv_lens=dev[o + 2 * B + 1:o + 3 * B + 1], longest_first=dev[o + 3 * B + 1:o + 4 * B + 1],
+        wanted_rows=dev[o + 4 * B + 1:base])
 
 
 def pack_step(entries: Sequence[StepEntry], lengths_before: Sequence[int], runtime: Runtime,

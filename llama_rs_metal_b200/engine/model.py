@@ -147,6 +147,10 @@ class DecoderModel:
         """Embedding, the scheduled blocks and the final norm on the wanted rows; None when no
         row is wanted (the cache is filled all the same)."""
         plan = self.plan
+        # what dispatchers kept belongs to one run of the step: a context that runs again (a
+        # captured step, once before and once under capture) must compute it again from its arrays
+        ctx.scratch.clear()
+        ctx.fresh_kv.clear()
         hidden = ops.embed_rows(self.embedding, ctx.token_ids, plan.embedding_scale)
         wanted = ctx.wanted_rows.numel() > 0
         schedule = plan.schedule

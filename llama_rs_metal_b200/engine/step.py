@@ -105,7 +105,7 @@ class _StepGraph:
         rt = runner.runtime
         self.batch, self.choice = seqs, choice
         groups = len(runner.cache.kv_groups)
-        self.size = (3 + groups) * tokens + 3 * seqs + 1 + wanted  # pack_host's layout
+        self.size = (3 + groups) * tokens + 4 * seqs + 1 + wanted  # pack_host's layout
         # behind it, 8-byte aligned: one int64 key per wanted row for the noise of temperature sampling
         self.keys_at = self.size + (self.size & 1)
         total = self.keys_at + 2 * max(wanted, 1)
@@ -322,7 +322,7 @@ class StepRunner:
         before, dest_rows = grown
         cache.sync()
         groups = len(dest_rows)
-        host = np.empty((7 + groups) * batch + 1, dtype=np.int32)
+        host = np.empty((8 + groups) * batch + 1, dtype=np.int32)
         order = np.arange(batch + 1, dtype=np.int32)
         host[0:batch] = tokens
         host[batch:2 * batch] = before
@@ -330,9 +330,10 @@ class StepRunner:
         host[3 * batch:4 * batch + 1] = order
         host[4 * batch + 1:5 * batch + 1] = slots
         host[5 * batch + 1:6 * batch + 1] = before + 1
-        host[6 * batch + 1:7 * batch + 1] = order[:batch]
+        host[6 * batch + 1:7 * batch + 1] = np.argsort(-before, kind="stable")
+        host[7 * batch + 1:8 * batch + 1] = order[:batch]
         for g, rows in enumerate(dest_rows):
-            host[(7 + g) * batch + 1:(8 + g) * batch + 1] = rows
+            host[(8 + g) * batch + 1:(9 + g) * batch + 1] = rows
         return host, before
 
     def _decode_vectorized(self, entries: List[StepEntry], borrow: bool) -> Optional[torch.Tensor]:

@@ -53,9 +53,10 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
         # are packed (four of 512 tokens 20 against 29 us, eight of 128 tokens 9.5 against 11.1). A
         # single short prompt is bound by the chain of key tiles of its last query tile, which the
         # older kernel, with two threads per row, walks a little faster (1,024 tokens 24 against 26 us).
+        # Packed prompts go to the newer kernel at head size 128 too (four of 512 tokens 33 against 46 us).
         # (several prompts: the packed tokens are well more than the longest prompt; a short prompt
         # filled up to whole rows with a few tokens of padding does not count)
-        pingpong = max_seq_len >= 1536 if d == 128 else (max_seq_len > 2048 or 4 * T >= 5 * max_seq_len)
+        pingpong = (max_seq_len >= 1536 if d == 128 else max_seq_len > 2048) or 4 * T >= 5 * max_seq_len
         if prefill_kernel is not None:
             pingpong = prefill_kernel == "pingpong"
         if pingpong:
@@ -260,9 +261,8 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
                 and decode_prefers_fused(projected.shape[0], kv_heads, q_heads // kv_heads, head_dim,
                                          ctx.max_kv_len, ctx.kv_fill)):
             # rotation, cache write, attention and the merge of the splits in one launch
-            order = ctx.scratch.get("longest_first")   # once per step: every layer reads the same lengths
-            if order is None and projected.shape[0] > 1:
-                order = ctx.scratch["longest_first"] = ops.order_by_length(ctx.kv_lens)
+            # the order comes with the step's arrays: the kernel reads it before it waits
+            order = ctx.longest_first if projected.shape[0] > 1 else None
             return ops.attention_decode_fused(projected, q_heads, inv_freq, width, ctx.positions, cache,
                                               ctx.dest_rows[cache.group], ctx.slots, ctx.kv_lens,
                                               ctx.max_kv_len, scale, order, ctx.kv_fill)

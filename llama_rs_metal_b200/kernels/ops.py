@@ -387,14 +387,6 @@ def attention_extend(q: torch.Tensor, kv, cu_seqlens: torch.Tensor, seq_of_token
     return out
 
 
-def order_by_length(lengths: torch.Tensor) -> torch.Tensor:
-    """int32 [n]: indices of `lengths` from the largest to the smallest (ties: lower index first)."""
-    _check(lengths, "lengths", torch.int32, 1)
-    order = torch.empty_like(lengths)
-    _done(_lib().lrm_order_by_length(_ptr(lengths), _ptr(order), lengths.numel(), _stream()), "order_by_length")
-    return order
-
-
 def attention_decode_fused_supported(dtype, head_dim: int, page_size: int, rotary: int, window) -> bool:
     from . import attention_dispatch
     return attention_dispatch.decode_fused_supported(dtype, head_dim, page_size, rotary, window)
@@ -412,8 +404,9 @@ def attention_decode_fused(qkv: torch.Tensor, q_heads: int, inv_freq: Optional[t
                            order: Optional[torch.Tensor] = None, fill: int = 4) -> torch.Tensor:
     """A decode step's attention from its fused, unrotated [B, (Hq+2Hk)*d] projection: rotates q and
     the new k, stores the new k and v at `dest_rows`, attends over the cache (kv_lens counts the new
-    token) and merges the splits, in one launch. -> [B, Hq*d]. `order` (order_by_length(kv_lens)):
-    the sequences' work is handed out longest first, which matters when lengths are unequal;
+    token) and merges the splits, in one launch. -> [B, Hq*d]. `order` (int32 [B], made on the host and
+    copied before the step, because the kernel reads it before it waits for the kernels ahead of
+    it): the sequences' work is handed out in this order, longest first when lengths are unequal;
     `fill`: their mean length in quarters of the longest (launch geometry only)."""
     _check(qkv, "qkv", torch.bfloat16, 2)
     d, Hk = kv.head_dim, kv.kv_heads

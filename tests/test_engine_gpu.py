@@ -1035,7 +1035,7 @@ def test_short_prompt_steps_are_filled_to_whole_rows_and_replayed_from_a_graph(e
     runner, cache, _ = open_runner(engine, model_dirs["D"], dtype)
     assert runner.pads_prompts
     sets = [[helpers.random_tokens(400 + 10 * s + i, n, vocab) for i, n in enumerate(lengths)]
-            for s, lengths in enumerate(([5, 70, 33], [9, 66, 30], [5, 70, 33], [1, 127, 0][:2]))]
+            for s, lengths in enumerate(([5, 70, 33], [9, 66, 30], [5, 70, 33], [33, 70, 5], [1, 127]))]
     sets[2] = sets[0]
     outs = []
     for prompts in sets:
@@ -1055,7 +1055,9 @@ def test_short_prompt_steps_are_filled_to_whole_rows_and_replayed_from_a_graph(e
             cache.close_slot(sl)
         outs.append(out)
     prompt_graphs = [k for k in runner._graphs if k[0] == "prefill"]
-    # wanted rows differ between the sets (108, 105, 108, 128 logits), so three geometries were seen;
-    # the third set repeats the first one's and replays a graph
+    # wanted rows differ between the sets (108, 105, 108, 108, 128 logits), so three geometries were
+    # seen; the third set repeats the first one's and is captured, the fourth has that geometry with
+    # other lengths and replays the graph: whatever a step derives from its positions (the table of
+    # rotation angles) has to be derived inside the graph
     assert len(prompt_graphs) == 1 and prompt_graphs[0][1] == 128
     assert torch.equal(outs[2], outs[0])                           # replayed = uncaptured, bit for bit

@@ -144,12 +144,6 @@ def test_silu_mul_blocks(ops, dtype, block):
     close(ops.silu_mul(gu.contiguous(), block), want, TOL[dtype] / 2, "silu_mul")
 
 
-def test_order_by_length(ops):
-    for lengths in ([5], [3, 3, 3], [1, 9, 2, 9, 0, 7], list(range(300)), [7] * 130 + [8]):
-        got = ops.order_by_length(i32(lengths)).tolist()
-        assert got == sorted(range(len(lengths)), key=lambda b: (-lengths[b], b))
-
-
 def test_add_and_cast(ops):
     x, d = rnd(9, 77), rnd(9, 77, dtype=torch.bfloat16, seed=5)
     want = x.double().cpu() + d.double().cpu()
@@ -497,8 +491,7 @@ def test_attention_decode_fused_rotates_stores_attends_and_merges(ops, Hq, Hk, d
     finally:
         attention_dispatch.force_cluster_size = None
     # handing the sequences out longest first changes who starts when, not what anyone computes
-    order = ops.order_by_length(i32(lengths))
-    assert order.tolist() == sorted(range(B), key=lambda b: (-lengths[b], b))
+    order = i32(sorted(range(B), key=lambda b: (-lengths[b], b)))
     attention_dispatch.force_cluster_size = cluster
     try:
         again = ops.attention_decode_fused(qkv, Hq, inv_dev, rotary, i32(positions), view, i32(dest), i32(slots),
