@@ -76,7 +76,7 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_sample_gumbel_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
 }
 # entry points that only answer questions and launch nothing
-_QUERIES = ("_supports", "_slices", "_pieces", "_resident", "_floats", "_error", "_room", "lrm_set_pdl", "lrm_pick_pieces")
+_QUERIES = ("_supports", "_slices", "_pieces", "_resident", "_floats", "_error", "_room", "lrm_set_pdl", "lrm_set_norm_ranks", "lrm_pick_pieces")
 
 
 class _Row:

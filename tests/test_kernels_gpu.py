@@ -69,6 +69,41 @@ def test_rms_norm_folds_partial_sums_into_the_residual(ops):
     close(y, P.rms_norm(total, torch.ones(136, dtype=F64), 1e-5), 1e-5, "norm of folded")
 
 
+@pytest.mark.parametrize("ranks,rows,hidden,slices", [(0, 16, 3072, 6), (0, 64, 2048, 9), (2, 3, 1032, 1),
+                                                     (4, 5, 2052, 3), (8, 2, 4104, 10), (4, 7, 8192, 2)])
+def test_rms_norm_with_a_row_cut_among_the_ctas_of_a_cluster(ops, ranks, rows, hidden, slices):
+    """Few rows with slices to fold and a bfloat16 output: the row is cut among the CTAs of a
+    cluster, which exchange their shares of the sum of squares (ranks 0: the kernel's own rule
+    chooses it at these sizes). The folded residual is bit-equal to the one-CTA kernel's."""
+    from llama_rs_metal_b200.kernels import library
+    lib = library.load()
+    x = rnd(rows, hidden, scale=2.0)
+    parts = rnd(slices, rows, hidden, seed=4)
+    w = rnd(hidden, dtype=torch.bfloat16, seed=9) + 1.0
+    total = x.double().cpu() + parts.double().cpu().sum(0)
+    want = P.rms_norm(total, w.double().cpu(), 1e-5)
+    lib.lrm_set_norm_ranks(1)
+    try:
+        x_one = x.clone()
+        y_one = ops.rms_norm(x_one, w, 1e-5, torch.bfloat16, partials=parts)
+        lib.lrm_set_norm_ranks(ranks)
+        x_cut = x.clone()
+        y_cut = ops.rms_norm(x_cut, w, 1e-5, torch.bfloat16, partials=parts)
+        picked = ops.rms_norm(x_cut, w, 1e-5, torch.bfloat16, rows=i32([rows - 1, 0]))
+        # float32 output never takes the cluster: its bits must not depend on the number of rows
+        y32_cut = ops.rms_norm(x.clone(), w, 1e-5, torch.float32, partials=parts)
+        lib.lrm_set_norm_ranks(1)
+        y32_one = ops.rms_norm(x.clone(), w, 1e-5, torch.float32, partials=parts)
+    finally:
+        lib.lrm_set_norm_ranks(0)
+    assert torch.equal(x_cut, x_one)
+    close(x_cut, total, 1e-6, "residual after fold")
+    close(y_cut, want, TOL[torch.bfloat16] / 2, "norm of folded, cut among a cluster")
+    close(y_one, want, TOL[torch.bfloat16] / 2, "norm of folded, one CTA per row")
+    close(picked, want[[rows - 1, 0]], TOL[torch.bfloat16] / 2, "listed rows")
+    assert torch.equal(y32_cut, y32_one)
+
+
 # --------------------------------------------------------------------------- matrix products
 SHAPES = [(1, 1, 1), (1, 130, 68), (3, 63, 15), (17, 64, 129), (65, 200, 256), (130, 7, 40), (4, 307, 68)]
 
