@@ -46,9 +46,9 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
         from . import gemm_dispatch
         gemm_dispatch.mark_status_dirty()
         # Two tcgen05 kernels. The one that keeps probabilities and output in tensor memory wins on
-        # long prompts and on batches of prompts: at head size 128 (two query tiles per CTA taking
-        # turns) from 1,536 tokens on (2,048 tokens 63 against 87 us, 1,023 against 585 TFLOP/s at
-        # 32,768); at head size 64 (four CTAs per SM on key tiles of 64) beyond 2,048 tokens (3,072
+        # long prompts and on batches of prompts: at head size 128 (one query tile per CTA on key tiles
+        # of 64 up to 2,304 tokens, two query tiles taking turns beyond) from 1,536 tokens on (2,048
+        # tokens 60 against 86 us, 953 against 582 TFLOP/s at 32,768); at head size 64 (four CTAs per SM on key tiles of 64) beyond 2,048 tokens (3,072
         # tokens 78 against 100 us, 681 against 534 TFLOP/s at 32,768) and whenever several prompts
         # are packed (four of 512 tokens 20 against 29 us, eight of 128 tokens 9.5 against 11.1). A
         # single short prompt is bound by the chain of key tiles of its last query tile, which the
