@@ -55,6 +55,20 @@ def test_whole_model_parity_at_benchmark_widths(engine, folders, which, dtype):
     print(f"{which} {dtype}: worst error {worst:.3e} of the largest logit")
 
 
+def test_whole_model_parity_with_norm_rows_cut_among_clusters(engine, folders):
+    """The norm that cuts a row among the CTAs of a cluster is chosen for few long rows with many
+    planes to fold (decode batches at the larger shapes). Here it is forced for every bfloat16 norm,
+    so that prompts, batches, decoding and captured steps of a whole model go through it."""
+    from llama_rs_metal_b200.kernels import library
+    lib = library.load()
+    lib.lrm_set_norm_ranks(8)
+    try:
+        worst = helpers.parity_with_plain(engine, folders["1b"], "bfloat16", prompt_lengths=(70, 33, 9), decode_steps=6)
+    finally:
+        lib.lrm_set_norm_ranks(0)
+    print(f"1b bfloat16 with cluster norms: worst error {worst:.3e} of the largest logit")
+
+
 def test_a_smaller_model_can_share_a_larger_models_weights(engine, folders, tmp_path):
     """The loader skips stored tensors nobody asked for, so a 1-layer model reads its tensors out
     of the 2-layer folder's file (how bench.py's gate gets a short model out of the long one)."""
