@@ -210,6 +210,11 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--shape", default="1b", choices=sorted(SHAPES))
     parser.add_argument("--batch", type=int, default=None, help="batch of the main number (default: the shape's)")
+    parser.add_argument("--context", type=int, default=None,
+                        help="another context length than the shape's (further sizes: the requests then generate "
+                             "to this length and are timed at their midpoints)")
+    parser.add_argument("--prefill-tokens", type=int, default=None,
+                        help="length of the prompt of the prefill figure (default 2,048), up to the context")
     parser.add_argument("--layers", type=int, default=None,
                         help="fewer layers than the shape has (both numbers are named in config)")
     parser.add_argument("--no-points", action="store_true", help="skip the other batch sizes, prefill and CPU extras")
@@ -249,7 +254,8 @@ def main() -> int:
     full_layers = shape["config"]["num_hidden_layers"]
     layers = args.layers or full_layers
     config = dict(shape["config"], num_hidden_layers=layers)
-    context, batch_main = shape["context"], args.batch or shape["batch"]
+    context, batch_main = args.context or shape["context"], args.batch or shape["batch"]
+    prefill_tokens = min(args.prefill_tokens or PREFILL_TOKENS, context)
     peaks, peak_source = load_peaks()
     engine = Engine(0)
     gate = "skipped (--no-gate)"
@@ -369,11 +375,11 @@ def main() -> int:
             warm, traced = range(16), range(16, 20)
         else:
             session = model.session(context=context, max_batch=1)
-            ids = rng.integers(0, vocab, size=PREFILL_TOKENS).tolist()
+            ids = rng.integers(0, vocab, size=prefill_tokens).tolist()
 
             def run(i):
                 slot = session.open_slot()
-                session.runner.step([StepEntry(slot, ids, (PREFILL_TOKENS - 1,))])
+                session.runner.step([StepEntry(slot, ids, (prefill_tokens - 1,))])
                 torch.cuda.synchronize()
                 session.close_slot(slot)
             warm, traced = range(4), range(4, 5)
@@ -409,9 +415,10 @@ def main() -> int:
                           "note": "the table is on stderr; nothing was timed for the record"}))
         return 0
     if args.only == "prefill":
-        ms = time_prefill(PREFILL_TOKENS, reps=max(1, args.steps))
-        flops = prefill_flops(config, PREFILL_TOKENS)
-        print(json.dumps({"metric": "prefill tok/s, one 2048-token prompt", "value": round(PREFILL_TOKENS / (ms * 1e-3), 1),
+        ms = time_prefill(prefill_tokens, reps=max(1, args.steps))
+        flops = prefill_flops(config, prefill_tokens)
+        print(json.dumps({"metric": f"prefill tok/s, one {prefill_tokens}-token prompt",
+                          "value": round(prefill_tokens / (ms * 1e-3), 1),
                           "unit": "tok/s", "ms": round(ms, 3), "layers": layers, "shape": shape["name"],
                           "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4), "peaks": peak_source,
                           "gate": gate}))
@@ -447,9 +454,9 @@ def main() -> int:
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
     }
     if not args.no_points:
-        ms = time_prefill(PREFILL_TOKENS)
-        flops = prefill_flops(config, PREFILL_TOKENS)
-        line["prefill"] = {"value": round(PREFILL_TOKENS / (ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+        ms = time_prefill(prefill_tokens)
+        flops = prefill_flops(config, prefill_tokens)
+        line["prefill"] = {"value": round(prefill_tokens / (ms * 1e-3), 1), "tokens": prefill_tokens,
                            "ms": round(ms, 3), "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
         points = {}
         for batch in shape["points"]:
