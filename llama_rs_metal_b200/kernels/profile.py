@@ -57,6 +57,10 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_gemm_bf16_mma": lambda a: _gemm(_v(a[3]), _v(a[4]), _v(a[5]), _out_elem(_v(a[6]))),
     "lrm_gemm_bf16_umma_rows": lambda a: _gemm(_v(a[3]), _v(a[5]), _v(a[6]), _out_elem(_v(a[7]))),
     "lrm_gemm_bf16_umma_pair": lambda a: _gemm(_v(a[3]), _v(a[4]), _v(a[5]), _out_elem(_v(a[6]))),
+    # the fused q|k|v projection of a prompt: the product, its bfloat16 result stored packed and k, v again in the cache
+    "lrm_gemm_bf16_umma_qkv": lambda a: _gemm(_v(a[2]), _v(a[3]), _v(a[4]), 2),
+    "lrm_gemm_bf16_umma_pair_qkv": lambda a: _gemm(_v(a[2]), _v(a[3]), _v(a[4]), 2),
+    "lrm_rope_table": lambda a: (_v(a[3]) * _v(a[4]) * 8.0 + _v(a[3]) * 4.0, 0),
     "lrm_gemm_bf16_stream_pick": lambda a: _gemm(_v(a[2]), _v(a[3]), _v(a[4]), 0),
     "lrm_rope_store": lambda a: (2.0 * _v(a[11]) * (_v(a[12]) + 2 * _v(a[13])) * _v(a[14]) * _ELEM[_v(a[1])], 0),
     "lrm_silu_mul": lambda a: (3.0 * _v(a[3]) * _v(a[4]) * _ELEM[_v(a[2])], 0),
@@ -64,6 +68,8 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     # prompts: q, k, v, out once; 4 flops per (query, key, head dimension) pair of the causal triangle
     "lrm_attention_prefill_umma": lambda a: (2.0 * _v(a[5]) * 2 * (_v(a[8]) + _v(a[9])) * _v(a[10]),
                                              4.0 * hints["pairs"] * _v(a[8]) * _v(a[10])),
+    "lrm_attention_prefill_pingpong": lambda a: (2.0 * _v(a[5]) * 2 * (_v(a[8]) + _v(a[9])) * _v(a[10]),
+                                                 4.0 * hints["pairs"] * _v(a[8]) * _v(a[10])),
     "lrm_attention_prefill_tiled": lambda a: (0, 4.0 * hints["pairs"] * _v(a[7]) * _v(a[9])),
     "lrm_attention_packed_rowwise": lambda a: (0, 4.0 * hints["pairs"] * _v(a[8]) * _v(a[10])),
     # over the cache: every cached key and value of the live sequences once
